@@ -1,0 +1,158 @@
+/*
+ * symplex_b200 — C ABI of the B200 (sm_100a) dense-matmul kernel library.
+ *
+ * Everything SympleX's host code (Rust `extern "C"`, pyo3, ctypes, C++) needs in order to run its
+ * tiled dense matmul and the elementwise epilogues fused into it on a B200. Plain pointers and sizes
+ * only. Unless a function says otherwise it returns 0 on success or one of the negative
+ * SYMPLEX_ERR_* codes; nothing throws across this boundary and there is no CPU fallback: without a
+ * usable GPU every compute entry point fails with SYMPLEX_ERR_DRIVER (void entry points leave C
+ * untouched and record the error for symplex_b200_last_error()).
+ */
+#ifndef SYMPLEX_B200_H
+#define SYMPLEX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Failure classes; same split as the reference's CudaError enum
+ * (rust-engine/src/cuda_backend.rs:35-50). TIMEOUT is new: a bounded device-side wait expired. */
+#define SYMPLEX_OK 0
+#define SYMPLEX_ERR_DRIVER (-1)
+#define SYMPLEX_ERR_INVALID (-2)
+#define SYMPLEX_ERR_OOM (-3)
+#define SYMPLEX_ERR_EXEC (-4)
+#define SYMPLEX_ERR_TIMEOUT (-5)
+
+/* Element types: values of the reference's ScalarType (rust-engine/src/types.rs:110-116). */
+#define SYMPLEX_DT_F32 9
+#define SYMPLEX_DT_BF16 11
+
+/* Matrix layouts: values of the reference's MatrixLayout (rust-engine/src/types.rs:177-181). */
+#define SYMPLEX_ROW_MAJOR 0
+#define SYMPLEX_COL_MAJOR 1
+
+/* Activations that fold into the matmul: the set accepted by is_activation /
+ * matches_matmul_bias_activation (rust-engine/src/fusion_engine.rs:261-266,1587-1623). */
+#define SYMPLEX_ACT_NONE 0
+#define SYMPLEX_ACT_RELU 1
+#define SYMPLEX_ACT_GELU 2 /* tanh form, python/symplex/_array.py:359-360 */
+#define SYMPLEX_ACT_SIGMOID 3
+#define SYMPLEX_ACT_TANH 4
+#define SYMPLEX_ACT_SILU 5
+
+/*
+ * One (optionally strided-batched) GEMM with a fused epilogue:
+ *     C = act(alpha * A.B + beta * R + bias)        A:[M,K] row-major, C,R:[M,N] row-major
+ * in_dtype F32 computes on tensor cores with the 3xTF32 split (fp32-level accuracy); BF16 multiplies
+ * bf16 inputs with fp32 accumulation. bias is fp32[N] broadcast over rows, or NULL. Leading
+ * dimensions / batch strides are in elements; 0 selects the packed default.
+ * Covers the fused chains of the reference's fusion vocabulary: [MatMul,Add], [MatMul,act],
+ * [MatMul,Add,act], [MatMul,Mul,Add,act] and FUSED_GEMM = alpha.A.B + beta.C
+ * (rust-engine/src/fusion_engine.rs:1587-1623, include/symplex/optimizer/egraph.h:74-77).
+ */
+typedef struct symplex_gemm_desc {
+  int64_t M, N, K;
+  int32_t batch;      /* number of independent problems, >= 1 */
+  int32_t in_dtype;   /* SYMPLEX_DT_F32 or SYMPLEX_DT_BF16 (A and B) */
+  int32_t out_dtype;  /* SYMPLEX_DT_F32 or SYMPLEX_DT_BF16 (C and R) */
+  int32_t b_layout;   /* SYMPLEX_ROW_MAJOR: B is [K,N]; SYMPLEX_COL_MAJOR: B is stored as [N,K] */
+  int64_t lda, ldb, ldc;
+  int64_t a_batch_stride, b_batch_stride, c_batch_stride;
+  float alpha, beta;
+  int32_t activation; /* SYMPLEX_ACT_* */
+  int32_t tile_n;     /* advisory tile hint like the reference's tile_m/n/k keys: 0 = auto, 64/128/256 */
+} symplex_gemm_desc;
+
+/* Fill a descriptor with defaults (batch 1, row-major B, alpha 1, beta 0, no activation). */
+void symplex_b200_gemm_desc_init(symplex_gemm_desc* d, int64_t M, int64_t N, int64_t K, int32_t in_dtype,
+                                 int32_t out_dtype);
+
+/* ---- device-pointer entry points (new; the reference has no device-resident API) ------------- */
+
+/* Bytes of scratch the GEMM described by `d` needs (operand planes for the fp32 path, padded copies
+ * of operands that are not 16-byte aligned; 0 if none). */
+size_t symplex_b200_gemm_workspace_bytes(const symplex_gemm_desc* d);
+
+/* Asynchronous GEMM on `stream` (a cudaStream_t, NULL = default stream) with device pointers.
+ * Scratch comes from a grow-only per-device pool owned by the library. `residual` may be NULL. */
+int symplex_b200_gemm(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
+                      const void* residual, void* stream);
+
+/* Same, with caller-provided scratch of at least symplex_b200_gemm_workspace_bytes(d) bytes
+ * (256-byte aligned device memory); never allocates. */
+int symplex_b200_gemm_ws(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
+                         const void* residual, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Synchronise `stream` and return the device-side status of the launches since the last call:
+ * 0, SYMPLEX_ERR_TIMEOUT or SYMPLEX_ERR_EXEC. */
+int symplex_b200_sync_status(void* stream);
+
+/* Message for the most recent failure on the calling thread (static storage; never NULL). */
+const char* symplex_b200_last_error(void);
+
+/* ---- host-pointer drop-ins ------------------------------------------------------------------- */
+
+/* General form of the reference's cuda_matmul (rust-engine/src/cuda_backend.rs:1344-1385): host
+ * buffers in, host buffer out, copies inside. Device buffers are cached per thread; nothing is
+ * re-compiled per call. */
+int symplex_b200_gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
+                           const void* residual);
+
+/* _symplex_core.cuda_matmul / symplex_engine.cuda_matmul_raw (python/src/lib.rs:1836-1849,
+ * rust-engine/src/lib.rs:1589-1592): fp32 row-major host matrices, returns 0 or -1. */
+int64_t symplex_cuda_matmul(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k);
+
+/* _symplex_core.parallel_matmul / jit_parallel_matmul (python/src/lib.rs:1029-1062) and the Rust
+ * functions behind them (rust-engine/src/x86_emitter.rs:1877-1919): same contract, returns 0
+ * (also for a zero dimension, which is a no-op) or a negative SYMPLEX_ERR_* code. */
+int64_t symplex_parallel_matmul(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k);
+int64_t symplex_jit_parallel_matmul(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k);
+
+/* The JIT kernel ABI of exec_matmul (rust-engine/src/x86_emitter.rs:70-77): returns 0. */
+int64_t symplex_exec_matmul(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k);
+
+/* The 7-argument fused kernel ABI of exec_fused_matmul_bias_relu
+ * (rust-engine/src/x86_emitter.rs:90-100,634-770): C = max(A.B + bias[N], 0). */
+int64_t symplex_exec_fused_matmul_bias_relu(const float* a, const float* b, float* c, int64_t m, int64_t n,
+                                            int64_t k, const float* bias);
+
+/* libsymplex_kernels.so entry points (kernels/matmul.c:7-18,82-101): C is fully overwritten. */
+void symplex_matmul_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K);
+void symplex_matmul_tiled_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K);
+
+/* The thin GEMM ABI that JIT-compiled TensorMatMul traces call
+ * (rust-engine/src/phase3_jit.rs:431-445,660-669): alpha 1, beta 0, natural leading dimensions. */
+void blas_sgemm(const float* a, const float* b, float* c, size_t m, size_t n, size_t k);
+void cache_tiled_sgemm_thin(const float* a, const float* b, float* c, size_t m, size_t n, size_t k);
+
+/* ---- device queries -------------------------------------------------------------------------- */
+
+/* CudaRuntime::is_available / _symplex_core.cuda_available (rust-engine/src/cuda_backend.rs:1078-1100,
+ * python/src/lib.rs:1715): 1 if device 0 exists and is an sm_100 part, else 0. */
+int symplex_cuda_available(void);
+
+/* Fields of _symplex_core.cuda_device_info (python/src/lib.rs:1721-1753). */
+typedef struct symplex_device_info {
+  char name[256];
+  int32_t compute_capability_major, compute_capability_minor;
+  uint64_t total_memory_bytes;
+  int32_t num_sms;
+  int32_t num_cuda_cores;
+  int32_t warp_size;
+  int32_t max_threads_per_block;
+  int32_t max_shared_memory_per_block;
+  int32_t clock_mhz;
+} symplex_device_info;
+int symplex_cuda_device_info(symplex_device_info* out);
+
+/* Kernels launched by this library on the calling process since load (all threads). */
+uint64_t symplex_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SYMPLEX_B200_H */

@@ -1,0 +1,273 @@
+/*
+ * CPU ORACLE — TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * A plain-C restatement of the arithmetic of SympleX's CPU matmul path, used only by the tests,
+ * the smoke check and the benchmark's cpu_baseline / reference arm to check and to time against.
+ * Nothing in the shipped library links, loads or calls this file.
+ *
+ * The reference's executable matmul lives in Rust (rust-engine/src/x86_emitter.rs) and cannot be
+ * built where this was written (no rustc), so each function below restates, element by element and
+ * rounding by rounding, what the machine code emitted by the reference computes. IEEE-754 fp32
+ * fused multiply-add is fmaf(); separately rounded multiply and add are written as two statements
+ * and this file must be compiled with -ffp-contract=off so the compiler keeps them apart.
+ *
+ * Pinning: checked by tests/test_oracle.py against every known-answer vector the reference's own
+ * tests hold for this path (2x2 product, I4.B = B, the (7i+13)%97 / (11i+17)%89 pattern against a
+ * scalar triple loop, gelu(0)=0) and against the reference's own kernels/matmul.c compiled unchanged
+ * into oracle/_ref/. bf16-input, GELU-fused and batched results have no vector in the reference:
+ * parity for those is unpinned by the reference and rests on this restatement alone.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#if defined(_OPENMP)
+#include <omp.h>
+#endif
+
+/* ---- the AVX-512 size-baked JIT kernel --------------------------------------------------------
+ * rust-engine/src/x86_emitter.rs:437-631 (compile_matmul_avx512):
+ *   columns j < 16*floor(N/16): acc = 0; for k ascending: acc = fma(A[i,k], B[k,j], acc)
+ *     (vfmadd231ps on 64-column blocks :487-551 and on 16-column blocks :554-577 - same per-element
+ *      arithmetic, every lane is an independent k-sequential FMA chain);
+ *   the last N mod 16 columns :580-617: acc = 0; for k: t = A[i,k]*B[k,j] (mulss); acc = acc + t (addss).
+ * Rows are independent; `threads` only splits rows for speed and never changes a result. */
+void oracle_matmul_jit_order(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                             int threads) {
+  const int64_t n_fma = (N / 16) * 16;
+  (void)threads;
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+  for (int64_t i = 0; i < M; ++i) {
+    const float* a = A + i * K;
+    float* c = C + i * N;
+    /* blocks of 64 accumulators keep B rows streaming, as the kernel's 4 ZMM accumulators do */
+    for (int64_t j0 = 0; j0 < n_fma; j0 += 64) {
+      const int64_t w = (n_fma - j0) < 64 ? (n_fma - j0) : 64;
+      float acc[64];
+      for (int64_t j = 0; j < w; ++j) acc[j] = 0.0f;
+      for (int64_t k = 0; k < K; ++k) {
+        const float aik = a[k];
+        const float* b = B + k * N + j0;
+        for (int64_t j = 0; j < w; ++j) acc[j] = fmaf(aik, b[j], acc[j]);
+      }
+      for (int64_t j = 0; j < w; ++j) c[j0 + j] = acc[j];
+    }
+    for (int64_t j = n_fma; j < N; ++j) {
+      float acc = 0.0f;
+      for (int64_t k = 0; k < K; ++k) {
+        float t = B[k * N + j] * a[k];
+        acc = acc + t;
+      }
+      c[j] = acc;
+    }
+  }
+}
+
+/* ---- the BLIS-style blocked kernel ------------------------------------------------------------
+ * rust-engine/src/x86_emitter.rs:1616-1875: MC = NC = KC = 128. For each KC block of k (ascending,
+ * :1724) the micro-kernel builds p = fma chain from 0 over the block's k (:1658-1673) and then does
+ * C = C + p (:1676-1700). C starts at 0 (:1852-1854). Packing, MR/NR edges and zero padding do not
+ * change any element's arithmetic. Row blocks are independent (rayon, :1861). */
+void oracle_matmul_blis_order(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                              int threads) {
+  const int64_t KC = 128, NB = 128;
+  (void)threads;
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
+#endif
+  for (int64_t i = 0; i < M; ++i) {
+    const float* a = A + i * K;
+    float* c = C + i * N;
+    for (int64_t j = 0; j < N; ++j) c[j] = 0.0f;
+    for (int64_t j0 = 0; j0 < N; j0 += NB) {
+      const int64_t w = (N - j0) < NB ? (N - j0) : NB;
+      for (int64_t k0 = 0; k0 < K; k0 += KC) {
+        const int64_t kc = (K - k0) < KC ? (K - k0) : KC;
+        float p[128];
+        for (int64_t j = 0; j < w; ++j) p[j] = 0.0f;
+        for (int64_t k = 0; k < kc; ++k) {
+          const float aik = a[k0 + k];
+          const float* b = B + (k0 + k) * N + j0;
+          for (int64_t j = 0; j < w; ++j) p[j] = fmaf(aik, b[j], p[j]);
+        }
+        for (int64_t j = 0; j < w; ++j) c[j0 + j] = c[j0 + j] + p[j];
+      }
+    }
+  }
+}
+
+/* ---- dispatcher ---------------------------------------------------------------------------------
+ * rust-engine/src/x86_emitter.rs:1899-1919 (jit_parallel_matmul) on an AVX-512 host: the size-baked
+ * JIT kernel when N >= 64, otherwise the BLIS-blocked kernel. Zero dimension: C is left untouched. */
+void oracle_jit_parallel_matmul(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                                int threads) {
+  if (M == 0 || N == 0 || K == 0) return;
+  if (N >= 64)
+    oracle_matmul_jit_order(A, B, C, M, N, K, threads);
+  else
+    oracle_matmul_blis_order(A, B, C, M, N, K, threads);
+}
+
+/* rust-engine/src/x86_emitter.rs:1877-1897 (parallel_matmul) on an AVX2-or-better host. */
+void oracle_parallel_matmul(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                            int threads) {
+  if (M == 0 || N == 0 || K == 0) return;
+  oracle_matmul_blis_order(A, B, C, M, N, K, threads);
+}
+
+/* ---- fused MatMul + Bias + ReLU -----------------------------------------------------------------
+ * rust-engine/src/x86_emitter.rs:634-770: C zeroed; i-k-j with C updated through memory.
+ * The 8-wide loop runs while the byte offset is < 4N-32 (:690-691), i.e. for column blocks starting
+ * below N-8: those columns use vfmadd231ps (one rounding); all later columns - always including the
+ * last 8 - use mulss + addss (two roundings) (:703-716). Then C = max(C + bias[j], 0) (:722-759). */
+void oracle_fused_matmul_bias_relu(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                                   const float* bias) {
+  int64_t vec_end = 0;
+  while (vec_end < N - 8) vec_end += 8;
+  for (int64_t i = 0; i < M; ++i) {
+    float* c = C + i * N;
+    for (int64_t j = 0; j < N; ++j) c[j] = 0.0f;
+    for (int64_t k = 0; k < K; ++k) {
+      const float aik = A[i * K + k];
+      const float* b = B + k * N;
+      for (int64_t j = 0; j < vec_end; ++j) c[j] = fmaf(aik, b[j], c[j]);
+      for (int64_t j = vec_end; j < N; ++j) {
+        float t = b[j] * aik;
+        c[j] = c[j] + t;
+      }
+    }
+    for (int64_t j = 0; j < N; ++j) {
+      float s = c[j] + bias[j];
+      c[j] = s > 0.0f ? s : 0.0f;
+    }
+  }
+}
+
+/* ---- the plain C kernel ---------------------------------------------------------------------------
+ * kernels/matmul.c:7-18: zero C, then i-k-j "C += a*b" with separately rounded multiply and add
+ * (what the source says; the reference's own build may contract or reassociate under -ffast-math,
+ * which is why oracle/_ref/ holds that file compiled as-is for comparison). */
+void oracle_matmul_c_order(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K) {
+  for (int64_t i = 0; i < M * N; ++i) C[i] = 0.0f;
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t k = 0; k < K; ++k) {
+      const float aik = A[i * K + k];
+      for (int64_t j = 0; j < N; ++j) {
+        float t = aik * B[k * N + j];
+        C[i * N + j] = C[i * N + j] + t;
+      }
+    }
+}
+
+/* matmul_bench.rs:16-27 (scalar_matmul): i-j-k, sum += a*b in fp32, two roundings. */
+void oracle_scalar_matmul(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K) {
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) {
+      float sum = 0.0f;
+      for (int64_t k = 0; k < K; ++k) {
+        float t = A[i * K + k] * B[k * N + j];
+        sum = sum + t;
+      }
+      C[i * N + j] = sum;
+    }
+}
+
+/* ---- operand conversions ------------------------------------------------------------------------ */
+
+/* fp32 -> bf16 with round-to-nearest-even, returned widened back to fp32 ("bf16-rounded inputs"). */
+float oracle_bf16_round(float x) {
+  uint32_t u;
+  memcpy(&u, &x, 4);
+  if ((u & 0x7f800000u) == 0x7f800000u) { /* inf / nan: keep class */
+    u &= 0xffff0000u;
+    if ((u & 0x7fffffffu) == 0x7f800000u || (u & 0x007f0000u)) { /* inf, or nan with a kept payload bit */
+    } else {
+      u |= 0x00400000u;
+    }
+  } else {
+    u += 0x7fffu + ((u >> 16) & 1u);
+    u &= 0xffff0000u;
+  }
+  float r;
+  memcpy(&r, &u, 4);
+  return r;
+}
+void oracle_bf16_round_array(const float* in, float* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) out[i] = oracle_bf16_round(in[i]);
+}
+/* bf16 bit patterns <-> fp32 */
+void oracle_bf16_bits_to_f32(const uint16_t* in, float* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    uint32_t u = (uint32_t)in[i] << 16;
+    memcpy(&out[i], &u, 4);
+  }
+}
+void oracle_f32_to_bf16_bits(const float* in, uint16_t* out, int64_t n) {
+  for (int64_t i = 0; i < n; ++i) {
+    float r = oracle_bf16_round(in[i]);
+    uint32_t u;
+    memcpy(&u, &r, 4);
+    out[i] = (uint16_t)(u >> 16);
+  }
+}
+
+/* ---- epilogues ------------------------------------------------------------------------------------
+ * Activations as the reference defines them, evaluated in fp32:
+ *   relu    max(x, 0)                                         python/symplex/_array.py:355-356
+ *   gelu    0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))   python/symplex/_array.py:358-360
+ *   sigmoid 1 / (1 + exp(-x))                                 python/symplex/_array.py:362-363,
+ *                                                             rust-engine/src/x86_emitter.rs:1991 (opcode 14)
+ *   tanh    tanh(x)                                           rust-engine/src/x86_emitter.rs:1990 (opcode 13)
+ *   silu    x * sigmoid(x)                                    (OpType::SiLU, rust-engine/src/fusion_engine.rs:261-266)
+ * Order of the fused chain [MatMul, Mul, Add, act] (rust-engine/src/fusion_engine.rs:1611-1618):
+ *   y = act(alpha * acc + beta * r + bias[j]). */
+float oracle_activation(float x, int act) {
+  switch (act) {
+    case 1: return x > 0.0f ? x : 0.0f;
+    case 2: {
+      const float c = 0.7978845608028654f; /* sqrt(2/pi) */
+      float u = c * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.0f + tanhf(u));
+    }
+    case 3: return 1.0f / (1.0f + expf(-x));
+    case 4: return tanhf(x);
+    case 5: return x / (1.0f + expf(-x));
+    default: return x;
+  }
+}
+
+void oracle_epilogue(float* C, int64_t M, int64_t N, float alpha, float beta, const float* residual,
+                     const float* bias, int act) {
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) {
+      float v = C[i * N + j] * alpha;
+      if (residual) v += beta * residual[i * N + j];
+      if (bias) v += bias[j];
+      C[i * N + j] = oracle_activation(v, act);
+    }
+}
+
+/* Selected rows of C = A.B in JIT order: row r of the output is row rows[r] of the full product.
+ * Exact for a row-partitioned contraction; lets the tests check the large configurations on a
+ * sample of rows in seconds. */
+void oracle_matmul_jit_order_rows(const float* A, const float* B, float* Crows, const int64_t* rows, int64_t nrows,
+                                  int64_t N, int64_t K, int threads) {
+  (void)threads;
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(dynamic, 1) num_threads(threads > 0 ? threads : 1)
+#endif
+  for (int64_t r = 0; r < nrows; ++r)
+    oracle_matmul_jit_order(A + rows[r] * K, B, Crows + r * N, 1, N, K, 1);
+}
+
+int oracle_max_threads(void) {
+#if defined(_OPENMP)
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}

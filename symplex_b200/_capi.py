@@ -1,0 +1,110 @@
+"""ctypes binding of ``libsymplex_b200.so`` (declarations: ``include/symplex_b200.h``).
+
+The shared library is the product; this module only loads it and describes its C ABI to Python.
+There is no fallback: if the library is missing, ``load()`` raises with the build command.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsymplex_b200.so")
+
+OK, ERR_DRIVER, ERR_INVALID, ERR_OOM, ERR_EXEC, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5
+DT_F32, DT_BF16 = 9, 11
+ROW_MAJOR, COL_MAJOR = 0, 1
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_SIGMOID, ACT_TANH, ACT_SILU = range(6)
+ACTIVATIONS = {
+    None: ACT_NONE, "none": ACT_NONE, "relu": ACT_RELU, "gelu": ACT_GELU,
+    "sigmoid": ACT_SIGMOID, "tanh": ACT_TANH, "silu": ACT_SILU,
+}
+
+
+class GemmDesc(ctypes.Structure):
+    """``symplex_gemm_desc``."""
+    _fields_ = [
+        ("M", c_int64), ("N", c_int64), ("K", c_int64),
+        ("batch", c_int32), ("in_dtype", c_int32), ("out_dtype", c_int32), ("b_layout", c_int32),
+        ("lda", c_int64), ("ldb", c_int64), ("ldc", c_int64),
+        ("a_batch_stride", c_int64), ("b_batch_stride", c_int64), ("c_batch_stride", c_int64),
+        ("alpha", c_float), ("beta", c_float),
+        ("activation", c_int32), ("tile_n", c_int32),
+    ]
+
+
+class DeviceInfo(ctypes.Structure):
+    """``symplex_device_info``."""
+    _fields_ = [
+        ("name", c_char * 256),
+        ("compute_capability_major", c_int32), ("compute_capability_minor", c_int32),
+        ("total_memory_bytes", c_uint64),
+        ("num_sms", c_int32), ("num_cuda_cores", c_int32), ("warp_size", c_int32),
+        ("max_threads_per_block", c_int32), ("max_shared_memory_per_block", c_int32),
+        ("clock_mhz", c_int32),
+    ]
+
+
+_F32P = c_void_p  # raw addresses; callers pass ints (numpy ``.ctypes.data`` / torch ``.data_ptr()``)
+
+# name -> (restype, argtypes): every symbol include/symplex_b200.h declares.
+SIGNATURES = {
+    "symplex_b200_gemm_desc_init": (None, [ctypes.POINTER(GemmDesc), c_int64, c_int64, c_int64, c_int32, c_int32]),
+    "symplex_b200_gemm_workspace_bytes": (c_size_t, [ctypes.POINTER(GemmDesc)]),
+    "symplex_b200_gemm": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "symplex_b200_gemm_ws": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_size_t, c_void_p]),
+    "symplex_b200_sync_status": (c_int, [c_void_p]),
+    "symplex_b200_last_error": (c_char_p, []),
+    "symplex_b200_gemm_host": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "symplex_cuda_matmul": (c_int64, [_F32P, _F32P, _F32P, c_int64, c_int64, c_int64]),
+    "symplex_parallel_matmul": (c_int64, [_F32P, _F32P, _F32P, c_int64, c_int64, c_int64]),
+    "symplex_jit_parallel_matmul": (c_int64, [_F32P, _F32P, _F32P, c_int64, c_int64, c_int64]),
+    "symplex_exec_matmul": (c_int64, [_F32P, _F32P, _F32P, c_int64, c_int64, c_int64]),
+    "symplex_exec_fused_matmul_bias_relu": (c_int64, [_F32P, _F32P, _F32P, c_int64, c_int64, c_int64, _F32P]),
+    "symplex_matmul_f32": (None, [_F32P, _F32P, _F32P, c_int64, c_int64, c_int64]),
+    "symplex_matmul_tiled_f32": (None, [_F32P, _F32P, _F32P, c_int64, c_int64, c_int64]),
+    "blas_sgemm": (None, [_F32P, _F32P, _F32P, c_size_t, c_size_t, c_size_t]),
+    "cache_tiled_sgemm_thin": (None, [_F32P, _F32P, _F32P, c_size_t, c_size_t, c_size_t]),
+    "symplex_cuda_available": (c_int, []),
+    "symplex_cuda_device_info": (c_int, [ctypes.POINTER(DeviceInfo)]),
+    "symplex_b200_launch_count": (c_uint64, []),
+}
+
+_lib = None
+
+
+class SymplexB200Error(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"symplex_b200 error {code}: {message}")
+        self.code = code
+
+
+def load() -> ctypes.CDLL:
+    """Load the library (once) and attach the signatures. Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m symplex_b200.build` "
+            "(nvcc, sm_100a). There is no CPU fallback.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library out of sync
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().symplex_b200_last_error().decode("utf-8", "replace")
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise SymplexB200Error(int(code), last_error())

@@ -1,0 +1,536 @@
+// C-ABI layer of libsymplex_b200.so: descriptor validation, scratch planning, operand preparation,
+// kernel dispatch, and the host-pointer drop-ins for the reference's matmul entry points.
+// Declarations and the reference interfaces they replace: include/symplex_b200.h.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/symplex_b200.h"
+#include "host_api.h"
+
+namespace sx {
+
+// ------------------------------------------------------------------ errors / counters
+static thread_local char g_err[512] = "no error";
+static std::atomic<uint64_t> g_launches{0};
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static int cuda_fail(cudaError_t e, const char* what) {
+  const int code = (e == cudaErrorMemoryAllocation) ? SX_ERR_OOM
+                   : (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver || e == cudaErrorInitializationError)
+                       ? SX_ERR_DRIVER
+                       : SX_ERR_EXEC;
+  return fail(code, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define SX_CUDA(call)                                   \
+  do {                                                  \
+    cudaError_t e__ = (call);                           \
+    if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+  } while (0)
+
+// ------------------------------------------------------------------ tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess ||
+        qr != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+int encode_tensor_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, const uint64_t dims[3],
+                         const uint64_t strides_bytes[2], const uint32_t box[3]) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(SX_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t d[3] = {dims[0], dims[1], dims[2]};
+  cuuint64_t s[2] = {strides_bytes[0], strides_bytes[1]};
+  cuuint32_t b[3] = {box[0], box[1], box[2]};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = fn(out, dt, 3, const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(SX_ERR_INVALID, "cuTensorMapEncodeTiled failed (%d): dims %llu,%llu,%llu strides %llu,%llu box %u,%u,%u",
+                (int)r, (unsigned long long)d[0], (unsigned long long)d[1], (unsigned long long)d[2],
+                (unsigned long long)s[0], (unsigned long long)s[1], b[0], b[1], b[2]);
+  return SX_OK;
+}
+
+// ------------------------------------------------------------------ per-device state
+struct DeviceState {
+  std::mutex mu;
+  bool ready = false;
+  int num_sms = 0;
+  int* status = nullptr;  // device word written by kernels that unwind
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+};
+static DeviceState g_dev[16];
+
+static int device_state(DeviceState** out) {
+  int dev = 0;
+  SX_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 16) return fail(SX_ERR_INVALID, "device ordinal %d out of range", dev);
+  DeviceState& st = g_dev[dev];
+  std::lock_guard<std::mutex> lk(st.mu);
+  if (!st.ready) {
+    int major = 0;
+    SX_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return fail(SX_ERR_DRIVER, "device %d is sm_%d0, this library needs sm_100", dev, major);
+    SX_CUDA(cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev));
+    SX_CUDA(cudaMalloc(&st.status, sizeof(int)));
+    SX_CUDA(cudaMemset(st.status, 0, sizeof(int)));
+    st.ready = true;
+  }
+  *out = &st;
+  return SX_OK;
+}
+
+static int pool_scratch(DeviceState* st, size_t bytes, void** out) {
+  std::lock_guard<std::mutex> lk(st->mu);
+  if (bytes > st->scratch_bytes) {
+    if (st->scratch) {
+      SX_CUDA(cudaDeviceSynchronize());
+      SX_CUDA(cudaFree(st->scratch));
+      st->scratch = nullptr;
+      st->scratch_bytes = 0;
+    }
+    const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    SX_CUDA(cudaMalloc(&st->scratch, want));
+    st->scratch_bytes = want;
+  }
+  *out = st->scratch;
+  return SX_OK;
+}
+
+// ------------------------------------------------------------------ planning
+static inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
+static inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+struct Plan {
+  long long M, N, K;
+  int batch;
+  bool f32_in, bf16_out, b_col;
+  long long lda, ldb, ldc, a_bs, b_bs, c_bs;
+  long long b_rows, b_cols;  // B as stored: [b_rows, b_cols]
+  // scratch
+  bool a_prep, b_prep;
+  long long a_ldp, b_ldp;  // leading dimension of the prepared copies
+  size_t a_off, b_off, total;
+};
+
+static int make_plan(const symplex_gemm_desc* d, const void* A, const void* B, Plan* p) {
+  if (d == nullptr) return fail(SX_ERR_INVALID, "null descriptor");
+  if (d->M < 0 || d->N < 0 || d->K < 0 || d->batch < 0) return fail(SX_ERR_INVALID, "negative dimension");
+  if (d->M > 0x7fffffffLL || d->N > 0x7fffffffLL || d->K > 0x7fffffffLL)
+    return fail(SX_ERR_INVALID, "dimension exceeds 2^31-1");
+  if (d->in_dtype != SYMPLEX_DT_F32 && d->in_dtype != SYMPLEX_DT_BF16)
+    return fail(SX_ERR_INVALID, "in_dtype %d not supported (F32=9, BF16=11)", d->in_dtype);
+  if (d->out_dtype != SYMPLEX_DT_F32 && d->out_dtype != SYMPLEX_DT_BF16)
+    return fail(SX_ERR_INVALID, "out_dtype %d not supported (F32=9, BF16=11)", d->out_dtype);
+  if (d->b_layout != SYMPLEX_ROW_MAJOR && d->b_layout != SYMPLEX_COL_MAJOR)
+    return fail(SX_ERR_INVALID, "b_layout %d not supported", d->b_layout);
+  if (d->activation < SYMPLEX_ACT_NONE || d->activation > SYMPLEX_ACT_SILU)
+    return fail(SX_ERR_INVALID, "activation %d not supported", d->activation);
+  if (d->tile_n != 0 && d->tile_n != 64 && d->tile_n != 128 && d->tile_n != 256)
+    return fail(SX_ERR_INVALID, "tile_n must be 0, 64, 128 or 256");
+  p->M = d->M; p->N = d->N; p->K = d->K;
+  p->batch = d->batch;
+  p->f32_in = d->in_dtype == SYMPLEX_DT_F32;
+  p->bf16_out = d->out_dtype == SYMPLEX_DT_BF16;
+  p->b_col = d->b_layout == SYMPLEX_COL_MAJOR;
+  p->b_rows = p->b_col ? d->N : d->K;
+  p->b_cols = p->b_col ? d->K : d->N;
+  p->lda = d->lda ? d->lda : d->K;
+  p->ldb = d->ldb ? d->ldb : p->b_cols;
+  p->ldc = d->ldc ? d->ldc : d->N;
+  if (p->lda < d->K || p->ldb < p->b_cols || p->ldc < d->N) return fail(SX_ERR_INVALID, "leading dimension too small");
+  p->a_bs = d->a_batch_stride ? d->a_batch_stride : d->M * p->lda;
+  p->b_bs = d->b_batch_stride ? d->b_batch_stride : p->b_rows * p->ldb;
+  p->c_bs = d->c_batch_stride ? d->c_batch_stride : d->M * p->ldc;
+  size_t off = 0;
+  if (p->f32_in) {
+    p->a_prep = p->b_prep = true;
+    p->a_ldp = round_up(d->K, 4);
+    p->b_ldp = round_up(p->b_cols, 4);
+    p->a_off = off;
+    off = align256(off + (size_t)p->batch * 2 * d->M * p->a_ldp * 4);
+    p->b_off = off;
+    off = align256(off + (size_t)p->batch * 2 * p->b_rows * p->b_ldp * 4);
+  } else {
+    auto misaligned = [](const void* ptr, long long ld, long long bs) {
+      return (ld % 8) != 0 || (bs % 8) != 0 || (reinterpret_cast<uintptr_t>(ptr) % 16) != 0;
+    };
+    p->a_prep = misaligned(A, p->lda, p->a_bs);
+    p->b_prep = misaligned(B, p->ldb, p->b_bs);
+    p->a_ldp = round_up(d->K, 8);
+    p->b_ldp = round_up(p->b_cols, 8);
+    p->a_off = off;
+    if (p->a_prep) off = align256(off + (size_t)p->batch * d->M * p->a_ldp * 2);
+    p->b_off = off;
+    if (p->b_prep) off = align256(off + (size_t)p->batch * p->b_rows * p->b_ldp * 2);
+  }
+  p->total = off;
+  return SX_OK;
+}
+
+static void debug_desc_override(TcGemmArgs* g) {
+  const char* e = getenv("SYMPLEX_B200_DESC_B");
+  if (e == nullptr) return;
+  unsigned lbo = 0, sbo = 0, ks = 0;
+  if (sscanf(e, "%u,%u,%u", &lbo, &sbo, &ks) == 3) {
+    g->dbg_lbo = lbo;
+    g->dbg_sbo = sbo;
+    g->dbg_kstep = ks;
+  }
+}
+
+static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, const void* B, void* C,
+                    const float* bias, const void* residual, void* ws, DeviceState* st, cudaStream_t stream) {
+  if (p.M == 0 || p.N == 0 || p.batch == 0) return SX_OK;  // nothing to write
+  uint8_t* w = static_cast<uint8_t*>(ws);
+  TcGemmArgs g{};
+  g.M = p.M; g.N = p.N; g.batch = p.batch;
+  g.out_bf16 = p.bf16_out;
+  g.b_mn = !p.b_col;
+  g.C = C; g.ldc = p.ldc; g.c_batch_stride = p.c_bs;
+  g.bias = bias; g.residual = residual;
+  g.alpha = d->alpha; g.beta = d->beta; g.act = d->activation;
+  g.status = st->status;
+  g.num_sms = st->num_sms;
+  // K == 0 is an empty sum: run one zero-padded k-block so the epilogue still writes act(beta R + bias).
+  g.K = p.K;
+  if (p.f32_in) {
+    float* Ap = reinterpret_cast<float*>(w + p.a_off);
+    float* Bp = reinterpret_cast<float*>(w + p.b_off);
+    if (p.K > 0) {
+      int rc = launch_split_tf32(static_cast<const float*>(A), p.lda, p.a_bs, Ap, (int)p.M, (int)p.K, (int)p.a_ldp,
+                                 p.batch, stream);
+      if (rc != SX_OK) return fail(rc, "split_tf32(A) launch failed");
+      rc = launch_split_tf32(static_cast<const float*>(B), p.ldb, p.b_bs, Bp, (int)p.b_rows, (int)p.b_cols,
+                             (int)p.b_ldp, p.batch, stream);
+      if (rc != SX_OK) return fail(rc, "split_tf32(B) launch failed");
+      g_launches += 2;
+    }
+    g.kind = 1;
+    g.nseg = 3;
+    g.a_plane[0] = 0; g.b_plane[0] = 0;  // hi * hi
+    g.a_plane[1] = 0; g.b_plane[1] = 1;  // hi * lo
+    g.a_plane[2] = 1; g.b_plane[2] = 0;  // lo * hi
+    g.a_planes = 2; g.b_planes = 2;
+    g.za = 2 * p.batch; g.zb = 2 * p.batch;
+    g.A = Ap; g.lda = p.a_ldp; g.a_plane_stride = p.M * p.a_ldp;
+    g.B = Bp; g.ldb = p.b_ldp; g.b_plane_stride = p.b_rows * p.b_ldp;
+  } else {
+    const void* Ause = A;
+    const void* Buse = B;
+    long long lda = p.lda, ldb = p.ldb, a_bs = p.a_bs, b_bs = p.b_bs;
+    if (p.a_prep && p.K > 0) {
+      int rc = launch_repack_16(A, p.lda, p.a_bs, w + p.a_off, p.a_ldp, (int)p.M, (int)p.K, p.batch, stream);
+      if (rc != SX_OK) return fail(rc, "repack(A) launch failed");
+      ++g_launches;
+      Ause = w + p.a_off; lda = p.a_ldp; a_bs = p.M * p.a_ldp;
+    }
+    if (p.b_prep && p.K > 0) {
+      int rc = launch_repack_16(B, p.ldb, p.b_bs, w + p.b_off, p.b_ldp, (int)p.b_rows, (int)p.b_cols, p.batch, stream);
+      if (rc != SX_OK) return fail(rc, "repack(B) launch failed");
+      ++g_launches;
+      Buse = w + p.b_off; ldb = p.b_ldp; b_bs = p.b_rows * p.b_ldp;
+    }
+    g.kind = 0;
+    g.nseg = 1;
+    g.a_planes = 1; g.b_planes = 1;
+    g.za = p.batch; g.zb = p.batch;
+    g.A = Ause; g.lda = lda; g.a_plane_stride = a_bs;
+    g.B = Buse; g.ldb = ldb; g.b_plane_stride = b_bs;
+  }
+  int forced = d->tile_n;
+  if (const char* e = getenv("SYMPLEX_B200_TILE")) forced = atoi(e);
+  g.bn = pick_bn(p.M, p.N, p.batch, st->num_sms, forced);
+  debug_desc_override(&g);
+  if (p.K == 0) {
+    return fail(SX_ERR_INVALID, "K == 0 is not supported by the device entry points");
+  }
+  int rc = launch_gemm_tc(g, stream);
+  if (rc != SX_OK) {
+    if (rc == SX_ERR_INVALID && strncmp(g_err, "cuTensorMap", 11) != 0)
+      return fail(rc, "operands are not TMA compatible (alignment) or tile %d invalid", g.bn);
+    if (rc == SX_ERR_EXEC) return fail(rc, "GEMM kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return rc;
+  }
+  ++g_launches;
+  return SX_OK;
+}
+
+// ------------------------------------------------------------------ host-pointer path
+struct HostCtx {
+  cudaStream_t stream = nullptr;
+  void* buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // A, B, C, bias, residual
+  size_t cap[5] = {0, 0, 0, 0, 0};
+  int dev = -1;
+};
+static thread_local HostCtx t_host;
+
+static int host_buf(int i, size_t bytes, void** out) {
+  HostCtx& h = t_host;
+  if (bytes > h.cap[i]) {
+    if (h.buf[i]) {
+      SX_CUDA(cudaStreamSynchronize(h.stream));
+      SX_CUDA(cudaFree(h.buf[i]));
+      h.buf[i] = nullptr;
+      h.cap[i] = 0;
+    }
+    const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    SX_CUDA(cudaMalloc(&h.buf[i], want));
+    h.cap[i] = want;
+  }
+  *out = h.buf[i];
+  return SX_OK;
+}
+
+static int gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
+                     const void* residual) {
+  Plan p;
+  int rc = make_plan(d, nullptr, nullptr, &p);  // device copies made here are always aligned
+  if (rc != SX_OK) return rc;
+  if (p.M == 0 || p.N == 0 || p.batch == 0) return SX_OK;
+  if (A == nullptr || B == nullptr || C == nullptr) return fail(SX_ERR_INVALID, "null matrix pointer");
+  DeviceState* st = nullptr;
+  rc = device_state(&st);
+  if (rc != SX_OK) return rc;
+  HostCtx& h = t_host;
+  int dev = 0;
+  SX_CUDA(cudaGetDevice(&dev));
+  if (h.stream == nullptr || h.dev != dev) {
+    SX_CUDA(cudaStreamCreateWithFlags(&h.stream, cudaStreamNonBlocking));
+    h.dev = dev;
+    for (int i = 0; i < 5; ++i) { h.buf[i] = nullptr; h.cap[i] = 0; }
+  }
+  const size_t in_elt = p.f32_in ? 4 : 2, out_elt = p.bf16_out ? 2 : 4;
+  // Extent of each host operand including batch strides.
+  const size_t a_bytes = ((size_t)(p.batch - 1) * p.a_bs + (size_t)(p.M - 1) * p.lda + p.K) * in_elt;
+  const size_t b_bytes = ((size_t)(p.batch - 1) * p.b_bs + (size_t)(p.b_rows - 1) * p.ldb + p.b_cols) * in_elt;
+  const size_t c_bytes = ((size_t)(p.batch - 1) * p.c_bs + (size_t)(p.M - 1) * p.ldc + p.N) * out_elt;
+  if (p.K == 0) {
+    return fail(SX_ERR_INVALID, "K == 0 is not supported");
+  }
+  void *dA, *dB, *dC, *dbias = nullptr, *dR = nullptr;
+  if ((rc = host_buf(0, a_bytes, &dA)) != SX_OK) return rc;
+  if ((rc = host_buf(1, b_bytes, &dB)) != SX_OK) return rc;
+  if ((rc = host_buf(2, c_bytes, &dC)) != SX_OK) return rc;
+  SX_CUDA(cudaMemcpyAsync(dA, A, a_bytes, cudaMemcpyHostToDevice, h.stream));
+  SX_CUDA(cudaMemcpyAsync(dB, B, b_bytes, cudaMemcpyHostToDevice, h.stream));
+  if (bias) {
+    if ((rc = host_buf(3, (size_t)p.N * 4, &dbias)) != SX_OK) return rc;
+    SX_CUDA(cudaMemcpyAsync(dbias, bias, (size_t)p.N * 4, cudaMemcpyHostToDevice, h.stream));
+  }
+  if (residual) {
+    if ((rc = host_buf(4, c_bytes, &dR)) != SX_OK) return rc;
+    SX_CUDA(cudaMemcpyAsync(dR, residual, c_bytes, cudaMemcpyHostToDevice, h.stream));
+  }
+  if (p.ldc != p.N || (p.batch > 1 && p.c_bs != p.M * p.ldc)) {
+    // Strided C: keep the bytes between rows that the kernel does not write.
+    SX_CUDA(cudaMemcpyAsync(dC, C, c_bytes, cudaMemcpyHostToDevice, h.stream));
+  }
+  void* ws = nullptr;
+  if (p.total) {
+    if ((rc = pool_scratch(st, p.total, &ws)) != SX_OK) return rc;
+  }
+  rc = run_gemm(d, p, dA, dB, dC, static_cast<const float*>(dbias), dR, ws, st, h.stream);
+  if (rc != SX_OK) return rc;
+  SX_CUDA(cudaMemcpyAsync(C, dC, c_bytes, cudaMemcpyDeviceToHost, h.stream));
+  int status = 0;
+  SX_CUDA(cudaMemcpyAsync(&status, st->status, sizeof(int), cudaMemcpyDeviceToHost, h.stream));
+  SX_CUDA(cudaStreamSynchronize(h.stream));
+  if (status != 0) {
+    cudaMemsetAsync(st->status, 0, sizeof(int), h.stream);
+    cudaStreamSynchronize(h.stream);
+    return fail(SX_ERR_TIMEOUT, "device-side wait timed out (status %d); the output is not valid", status);
+  }
+  return SX_OK;
+}
+
+static int64_t sgemm_host(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k) {
+  if (m == 0 || n == 0 || k == 0) return 0;  // the reference returns before touching C
+  if (m < 0 || n < 0 || k < 0) return fail(SX_ERR_INVALID, "negative dimension");
+  symplex_gemm_desc d;
+  symplex_b200_gemm_desc_init(&d, m, n, k, SYMPLEX_DT_F32, SYMPLEX_DT_F32);
+  return gemm_host(&d, a, b, c, nullptr, nullptr);
+}
+
+}  // namespace sx
+
+// =================================================================== extern "C"
+using namespace sx;
+
+extern "C" {
+
+void symplex_b200_gemm_desc_init(symplex_gemm_desc* d, int64_t M, int64_t N, int64_t K, int32_t in_dtype,
+                                 int32_t out_dtype) {
+  if (!d) return;
+  memset(d, 0, sizeof(*d));
+  d->M = M; d->N = N; d->K = K;
+  d->batch = 1;
+  d->in_dtype = in_dtype;
+  d->out_dtype = out_dtype;
+  d->b_layout = SYMPLEX_ROW_MAJOR;
+  d->alpha = 1.0f;
+  d->beta = 0.0f;
+  d->activation = SYMPLEX_ACT_NONE;
+}
+
+size_t symplex_b200_gemm_workspace_bytes(const symplex_gemm_desc* d) {
+  Plan p;
+  // Pointer alignment is unknown here: size for the case where both bf16 operands need a padded copy.
+  if (make_plan(d, reinterpret_cast<const void*>(1), reinterpret_cast<const void*>(1), &p) != SX_OK) return 0;
+  return p.total;
+}
+
+int symplex_b200_gemm(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
+                      const void* residual, void* stream) {
+  Plan p;
+  int rc = make_plan(d, A, B, &p);
+  if (rc != SX_OK) return rc;
+  if (p.M == 0 || p.N == 0 || p.batch == 0) return SX_OK;
+  if (!A || !B || !C) return fail(SX_ERR_INVALID, "null matrix pointer");
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != SX_OK) return rc;
+  void* ws = nullptr;
+  if (p.total && (rc = pool_scratch(st, p.total, &ws)) != SX_OK) return rc;
+  return run_gemm(d, p, A, B, C, bias, residual, ws, st, static_cast<cudaStream_t>(stream));
+}
+
+int symplex_b200_gemm_ws(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
+                         const void* residual, void* workspace, size_t workspace_bytes, void* stream) {
+  Plan p;
+  int rc = make_plan(d, A, B, &p);
+  if (rc != SX_OK) return rc;
+  if (p.M == 0 || p.N == 0 || p.batch == 0) return SX_OK;
+  if (!A || !B || !C) return fail(SX_ERR_INVALID, "null matrix pointer");
+  if (p.total > workspace_bytes || (p.total && workspace == nullptr))
+    return fail(SX_ERR_INVALID, "workspace too small: need %zu bytes, got %zu", p.total, workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(SX_ERR_INVALID, "workspace must be 256-byte aligned");
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != SX_OK) return rc;
+  return run_gemm(d, p, A, B, C, bias, residual, workspace, st, static_cast<cudaStream_t>(stream));
+}
+
+int symplex_b200_sync_status(void* stream) {
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc != SX_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int status = 0;
+  SX_CUDA(cudaMemcpyAsync(&status, st->status, sizeof(int), cudaMemcpyDeviceToHost, s));
+  SX_CUDA(cudaStreamSynchronize(s));
+  if (status != 0) {
+    SX_CUDA(cudaMemsetAsync(st->status, 0, sizeof(int), s));
+    SX_CUDA(cudaStreamSynchronize(s));
+    return fail(SX_ERR_TIMEOUT, "device-side wait timed out (status %d)", status);
+  }
+  return SX_OK;
+}
+
+const char* symplex_b200_last_error(void) { return g_err; }
+
+int symplex_b200_gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
+                           const void* residual) {
+  return gemm_host(d, A, B, C, bias, residual);
+}
+
+int64_t symplex_cuda_matmul(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k) {
+  return sgemm_host(a, b, c, m, n, k) == 0 ? 0 : -1;
+}
+int64_t symplex_parallel_matmul(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k) {
+  return sgemm_host(a, b, c, m, n, k);
+}
+int64_t symplex_jit_parallel_matmul(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k) {
+  return sgemm_host(a, b, c, m, n, k);
+}
+int64_t symplex_exec_matmul(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k) {
+  return sgemm_host(a, b, c, m, n, k);
+}
+int64_t symplex_exec_fused_matmul_bias_relu(const float* a, const float* b, float* c, int64_t m, int64_t n,
+                                            int64_t k, const float* bias) {
+  if (m == 0 || n == 0) return 0;
+  if (m < 0 || n < 0 || k <= 0) return fail(SX_ERR_INVALID, "bad dimension");
+  symplex_gemm_desc d;
+  symplex_b200_gemm_desc_init(&d, m, n, k, SYMPLEX_DT_F32, SYMPLEX_DT_F32);
+  d.activation = SYMPLEX_ACT_RELU;
+  return gemm_host(&d, a, b, c, bias, nullptr);
+}
+
+void symplex_matmul_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K) {
+  if (M > 0 && N > 0 && K == 0) {  // kernels/matmul.c zeroes C before accumulating
+    memset(C, 0, (size_t)M * N * sizeof(float));
+    return;
+  }
+  (void)sgemm_host(A, B, C, M, N, K);
+}
+void symplex_matmul_tiled_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K) {
+  symplex_matmul_f32(A, B, C, M, N, K);
+}
+void blas_sgemm(const float* a, const float* b, float* c, size_t m, size_t n, size_t k) {
+  symplex_matmul_f32(a, b, c, (int64_t)m, (int64_t)n, (int64_t)k);
+}
+void cache_tiled_sgemm_thin(const float* a, const float* b, float* c, size_t m, size_t n, size_t k) {
+  symplex_matmul_f32(a, b, c, (int64_t)m, (int64_t)n, (int64_t)k);
+}
+
+int symplex_cuda_available(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    return 0;
+  }
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, 0) != cudaSuccess) return 0;
+  return major == 10 ? 1 : 0;
+}
+
+int symplex_cuda_device_info(symplex_device_info* out) {
+  if (!out) return fail(SX_ERR_INVALID, "null output");
+  memset(out, 0, sizeof(*out));
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n < 1) {
+    cudaGetLastError();
+    return fail(SX_ERR_DRIVER, "no CUDA device: %s", e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+  }
+  cudaDeviceProp pr;
+  SX_CUDA(cudaGetDeviceProperties(&pr, 0));
+  strncpy(out->name, pr.name, sizeof(out->name) - 1);
+  out->compute_capability_major = pr.major;
+  out->compute_capability_minor = pr.minor;
+  out->total_memory_bytes = pr.totalGlobalMem;
+  out->num_sms = pr.multiProcessorCount;
+  out->num_cuda_cores = pr.multiProcessorCount * 128;  // 4 x 32 fp32 lanes per SM on sm_100
+  out->warp_size = pr.warpSize;
+  out->max_threads_per_block = pr.maxThreadsPerBlock;
+  out->max_shared_memory_per_block = (int32_t)pr.sharedMemPerBlock;
+  int khz = 0;
+  cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, 0);
+  out->clock_mhz = khz / 1000;
+  return SX_OK;
+}
+
+uint64_t symplex_b200_launch_count(void) { return g_launches.load(); }
+
+}  // extern "C"

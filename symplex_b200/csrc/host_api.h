@@ -1,0 +1,69 @@
+// Internal host-side interfaces between the launchers (one per .cu file) and the C-ABI layer.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace sx {
+
+// Status codes returned through the C ABI. They mirror the failure classes of the reference's
+// CudaError enum (rust-engine/src/cuda_backend.rs:35-50); TIMEOUT has no counterpart there.
+enum : int {
+  SX_OK = 0,
+  SX_ERR_DRIVER = -1,   // DriverError / NoGpuFound
+  SX_ERR_INVALID = -2,  // InvalidParam
+  SX_ERR_OOM = -3,      // OutOfMemory
+  SX_ERR_EXEC = -4,     // ExecutionError
+  SX_ERR_TIMEOUT = -5,  // a bounded device-side wait expired
+};
+
+// Arguments of one tensor-core GEMM launch on device-resident, TMA-compatible operands
+// (16-byte aligned base pointers, leading dimensions that are multiples of 16 bytes).
+struct TcGemmArgs {
+  int kind;      // 0: bf16 inputs (kind::f16), 1: fp32 containers read as tf32 (kind::tf32)
+  int out_bf16;  // output dtype: 0 fp32, 1 bf16
+  int b_mn;      // 1: B is row-major [K,N] (N contiguous); 0: B is [N,K] (K contiguous)
+  int bn;        // tile width: 256, 128 or 64
+  long long M, N, K;
+  int batch;
+  int nseg;
+  int a_plane[3], b_plane[3];
+  int a_planes, b_planes;  // planes per batch entry
+  int za, zb;              // total planes in the A / B allocations (batch * planes)
+  const void* A;
+  long long lda, a_plane_stride;  // elements
+  const void* B;
+  long long ldb, b_plane_stride;
+  void* C;
+  long long ldc, c_batch_stride;
+  const float* bias;
+  const void* residual;
+  float alpha, beta;
+  int act;
+  int* status;
+  int num_sms;
+  int group_m;
+  uint32_t dbg_lbo, dbg_sbo, dbg_kstep;  // 0 = use the library's values
+};
+
+int launch_gemm_tc(const TcGemmArgs& a, cudaStream_t stream);
+int pick_bn(long long M, long long N, int batch, int num_sms, int forced);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
+int encode_tensor_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, const uint64_t dims[3],
+                         const uint64_t strides_bytes[2], const uint32_t box[3]);
+
+// Operand preparation kernels (prep_kernels.cu).
+// fp32 [batch][rows][cols] (leading dimension ld_in) -> planes [batch][2][rows][cols_p]:
+// plane 0 = tf32-rounded value, plane 1 = tf32-rounded remainder; columns >= cols are zero.
+int launch_split_tf32(const float* in, long long ld_in, long long batch_stride_in, float* out, int rows, int cols,
+                      int cols_p, int batch, cudaStream_t stream);
+// Copy a 2-byte-element matrix into a buffer whose leading dimension is ld_out (zero padded).
+int launch_repack_16(const void* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
+                     int rows, int cols, int batch, cudaStream_t stream);
+// fp32 -> bf16 (round to nearest even), same shape conventions as launch_repack_16.
+int launch_f32_to_bf16(const float* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
+                       int rows, int cols, int batch, cudaStream_t stream);
+
+}  // namespace sx

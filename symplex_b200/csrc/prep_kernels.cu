@@ -1,0 +1,115 @@
+// Operand preparation for the tensor-core GEMM: HBM-bound elementwise passes.
+//
+//  * split_tf32: the 3xTF32 scheme represents an fp32 value x as hi + lo with hi = tf32(x) and
+//    lo = tf32(x - hi); the GEMM then accumulates hi*hi + hi*lo + lo*hi in fp32 on the tensor cores.
+//  * repack_16 / f32_to_bf16: bring operands whose leading dimension or base address is not a
+//    multiple of 16 bytes into a TMA-compatible padded buffer.
+#include <cuda_bf16.h>
+
+#include "host_api.h"
+
+namespace sx {
+
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// One thread produces 4 consecutive output columns of both planes (16-byte stores).
+__global__ void __launch_bounds__(256)
+split_tf32_kernel(const float* __restrict__ in, long long ld_in, long long batch_stride_in, float* __restrict__ out,
+                  int rows, int cols, int cols_p, int batch) {
+  const int c4n = cols_p >> 2;
+  const long long per_mat = (long long)rows * c4n;
+  const long long total = per_mat * batch;
+  const bool vec_in = (ld_in % 4 == 0) && (batch_stride_in % 4 == 0) && (reinterpret_cast<uintptr_t>(in) % 16 == 0);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(i / per_mat);
+    const long long rm = i - (long long)b * per_mat;
+    const int r = (int)(rm / c4n);
+    const int c = (int)(rm - (long long)r * c4n) * 4;
+    const float* src = in + (long long)b * batch_stride_in + (long long)r * ld_in + c;
+    float x[4];
+    if (vec_in && c + 4 <= cols) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+      x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) x[j] = (c + j < cols) ? __ldg(src + j) : 0.0f;
+    }
+    float hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      hi[j] = tf32_round(x[j]);
+      lo[j] = tf32_round(x[j] - hi[j]);
+    }
+    float* o_hi = out + (((long long)b * 2 + 0) * rows + r) * cols_p + c;
+    float* o_lo = out + (((long long)b * 2 + 1) * rows + r) * cols_p + c;
+    *reinterpret_cast<float4*>(o_hi) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<float4*>(o_lo) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+  }
+}
+
+template <typename InT, bool kToBf16>
+__global__ void __launch_bounds__(256)
+repack_kernel(const InT* __restrict__ in, long long ld_in, long long batch_stride_in, uint16_t* __restrict__ out,
+              long long ld_out, int rows, int cols, int batch) {
+  const long long per_mat = (long long)rows * ld_out;
+  const long long total = per_mat * batch;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(i / per_mat);
+    const long long rm = i - (long long)b * per_mat;
+    const int r = (int)(rm / ld_out);
+    const int c = (int)(rm - (long long)r * ld_out);
+    uint16_t v = 0;
+    if (c < cols) {
+      const InT x = in[(long long)b * batch_stride_in + (long long)r * ld_in + c];
+      if constexpr (kToBf16) {
+        __nv_bfloat16 h = __float2bfloat16_rn(x);
+        v = *reinterpret_cast<uint16_t*>(&h);
+      } else {
+        v = x;
+      }
+    }
+    out[i] = v;
+  }
+}
+
+static int grid_for(long long work_items) {
+  long long blocks = (work_items + 255) / 256;
+  const long long cap = 148 * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+int launch_split_tf32(const float* in, long long ld_in, long long batch_stride_in, float* out, int rows, int cols,
+                      int cols_p, int batch, cudaStream_t stream) {
+  if (cols_p % 4 != 0 || cols_p < cols) return SX_ERR_INVALID;
+  const long long items = (long long)rows * (cols_p / 4) * batch;
+  split_tf32_kernel<<<grid_for(items), 256, 0, stream>>>(in, ld_in, batch_stride_in, out, rows, cols, cols_p, batch);
+  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+}
+
+int launch_repack_16(const void* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
+                     int rows, int cols, int batch, cudaStream_t stream) {
+  const long long items = (long long)rows * ld_out * batch;
+  repack_kernel<uint16_t, false><<<grid_for(items), 256, 0, stream>>>(
+      static_cast<const uint16_t*>(in), ld_in, batch_stride_in, static_cast<uint16_t*>(out), ld_out, rows, cols,
+      batch);
+  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+}
+
+int launch_f32_to_bf16(const float* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
+                       int rows, int cols, int batch, cudaStream_t stream) {
+  const long long items = (long long)rows * ld_out * batch;
+  repack_kernel<float, true><<<grid_for(items), 256, 0, stream>>>(in, ld_in, batch_stride_in,
+                                                                   static_cast<uint16_t*>(out), ld_out, rows, cols,
+                                                                   batch);
+  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+}
+
+}  // namespace sx
