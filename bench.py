@@ -1,0 +1,448 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path: `python bench.py --gpus N --steps K --warmup W [--impl reference]`.
+
+Default workload = BASELINE config 5, the row-sharded bf16 GEMM A[65536,8192] x B[8192,8192] -> bf16 C,
+rows of A split evenly over the N GPUs, C all-gathered over NVLink (N = 1: the same GEMM on one GPU,
+no collective). Total work is fixed as N grows ("scaling": "strong"). One step = one full product.
+
+Prints ONE JSON line (rank 0). `value` is device-resident throughput (inputs in HBM, CUDA events, max over
+ranks); `e2e` is the same product through the host-buffer entry points with the pinned-host -> device and
+device -> host copies inside the timed region. `roofline` describes the GEMM kernel alone, `cpu_baseline`
+the reference's CPU path timed on this box's host cores on a bounded row sample.
+
+`--impl reference` times the reference's own CPU implementation of the path instead (its C kernel compiled
+unchanged when available, else the oracle port), on a bounded row sample of the same workload per step.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (M, N, K, batch, in, out, b_layout, activation, bias, description)
+    "cfg5_row_sharded_bf16_65536x8192x8192": dict(M=65536, N=8192, K=8192, batch=1, dt="bf16", out="bf16", b_col=False,
+                                                  act=None, bias=False, sharded=True),
+    "headline_bf16_8192_cube_bias_gelu": dict(M=8192, N=8192, K=8192, batch=1, dt="bf16", out="bf16", b_col=False,
+                                              act="gelu", bias=True, sharded=False),
+    "cfg1_fp32_512_cube": dict(M=512, N=512, K=512, batch=1, dt="f32", out="f32", b_col=False, act=None, bias=False,
+                               sharded=False),
+    "cfg2_bf16_4096_cube_colmajor_b": dict(M=4096, N=4096, K=4096, batch=1, dt="bf16", out="f32", b_col=True, act=None,
+                                           bias=False, sharded=False),
+    "cfg2_fp32_4096_cube_colmajor_b": dict(M=4096, N=4096, K=4096, batch=1, dt="f32", out="f32", b_col=True, act=None,
+                                           bias=False, sharded=False),
+    "cfg3_fused_gelu_mlp_8192x4096x16384": dict(M=8192, N=16384, K=4096, batch=1, dt="bf16", out="bf16", b_col=False,
+                                                act="gelu", bias=True, sharded=False),
+    "cfg4_batched_fp32_2048x64_cube": dict(M=64, N=64, K=64, batch=2048, dt="f32", out="f32", b_col=False, act=None,
+                                           bias=False, sharded=False),
+}
+DEFAULT_WORKLOAD = "cfg5_row_sharded_bf16_65536x8192x8192"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (None where no capture of that workload exists).
+NCU_TRAFFIC_BYTES = {}
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p, "of measured"
+    return dict(FALLBACK_PEAKS), "of fallback"
+
+
+def flops_of(w):
+    return 2.0 * w["M"] * w["N"] * w["K"] * w["batch"]
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.unlink(self.file.name)
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # "under load" = samples in the upper half of the observed power range
+        lo, hi = min(power), max(power)
+        loaded = [s for s, p in zip(sm, power) if p >= lo + 0.5 * (hi - lo)] or sm
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": hi}
+
+
+# ----------------------------------------------------------------------------- CPU reference timing
+def _load_cpu_reference():
+    """(callable(A, B, C, M, N, K), kind, cores, name): the reference's CPU matmul for this path."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from oracle_loader import load_oracle, load_ref_kernels
+    ref = load_ref_kernels()
+    if ref is not None:
+        def run(A, B, C, M, N, K):
+            ref.symplex_matmul_f32(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K)
+        return run, "reference", 1, "kernels/matmul.c:symplex_matmul_f32 compiled unchanged (single-threaded code)"
+    orc = load_oracle()
+
+    def run(A, B, C, M, N, K):
+        orc.lib.oracle_jit_parallel_matmul(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K, 1)
+    return run, "port", 1, "oracle port of jit_parallel_matmul (the reference's AVX-512 JIT path is single-threaded)"
+
+
+def cpu_sample(w, rows):
+    """Seeded operands of a `rows`-row slice of the workload (fp32; bf16 workloads use bf16-rounded values)."""
+    import numpy as np
+    rng = np.random.default_rng(0)
+    M = min(rows, w["M"])
+    A = rng.standard_normal((M, w["K"])).astype(np.float32)
+    B = rng.standard_normal((w["K"], w["N"])).astype(np.float32)
+    if w["dt"] == "bf16":
+        import torch
+        A = torch.from_numpy(A).to(torch.bfloat16).float().numpy()
+        B = torch.from_numpy(B).to(torch.bfloat16).float().numpy()
+    return A, B, np.zeros((M, w["N"]), np.float32)
+
+
+def time_cpu_reference(w, rows, steps, warmup):
+    run, kind, cores, name = _load_cpu_reference()
+    A, B, C = cpu_sample(w, rows)
+    M = A.shape[0]
+    for _ in range(warmup):
+        run(A, B, C, M, w["N"], w["K"])
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run(A, B, C, M, w["N"], w["K"])
+    dt = (time.perf_counter() - t0) / max(1, steps)
+    tflops = 2.0 * M * w["N"] * w["K"] / dt / 1e12
+    sample = f"{M} of {w['M']} rows of A (all of B), one problem of {w['batch']}; {name}"
+    return tflops, dt, kind, cores, sample
+
+
+def cpu_rows_for(w, seconds=3.0, gflops_guess=5.0):
+    per_row = 2.0 * w["N"] * w["K"]
+    rows = int(seconds * gflops_guess * 1e9 / per_row)
+    return max(1, min(w["M"], rows))
+
+
+# ----------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="symplex_b200", choices=["symplex_b200", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--chunks", type=int, default=None, help="row chunks per rank for the all-gather pipeline")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl != "reference":
+        args.warmup = 3  # timing rule: at least 3 warm-up steps
+
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    config = {"workload": args.workload, "M": w["M"], "N": w["N"], "K": w["K"], "batch": w["batch"],
+              "inputs": w["dt"], "output": w["out"], "b_layout": "col_major" if w["b_col"] else "row_major",
+              "epilogue": ("bias+" if w["bias"] else "") + (w["act"] or "none"),
+              "partition": f"rows of A over {args.gpus} GPU(s), B replicated, C all-gathered" if w["sharded"]
+              else "replicas only"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        rows = cpu_rows_for(w)
+        tflops, dt, kind, cores, sample = time_cpu_reference(w, rows, args.steps, max(1, args.warmup))
+        line = {"impl": "reference", "metric": "gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+                "scaling": "strong" if w["sharded"] else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": config,
+                "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+                "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line), flush=True)
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    import symplex_b200 as sx
+    from symplex_b200 import _capi
+    from symplex_b200.sharding import RowShardedGemm
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _capi.load()
+    peaks, peak_note = load_peaks()
+
+    tdt = torch.bfloat16 if w["dt"] == "bf16" else torch.float32
+    odt = torch.bfloat16 if w["out"] == "bf16" else torch.float32
+    M, N, K, batch = w["M"], w["N"], w["K"], w["batch"]
+    g = torch.Generator(device=dev).manual_seed(1234)  # same B on every rank
+    b_shape = (N, K) if w["b_col"] else (K, N)
+    scale = 0.02 if w["act"] == "gelu" else 1.0
+    if batch > 1:
+        Bm = (torch.randn((batch,) + b_shape, device=dev, generator=g) * scale).to(tdt)
+    else:
+        Bm = (torch.randn(b_shape, device=dev, generator=g) * scale).to(tdt)
+    bias = (torch.randn(N, device=dev, generator=g) * scale) if w["bias"] else None
+    b_layout = sx.COL_MAJOR if w["b_col"] else sx.ROW_MAJOR
+
+    sharded = w["sharded"]
+    if sharded:
+        op = RowShardedGemm(M, N, K, chunks=args.chunks, activation=w["act"], b_layout=b_layout)
+        m_loc = M // op.world
+        ga = torch.Generator(device=dev).manual_seed(100 + rank)
+        A = (torch.randn(m_loc, K, device=dev, generator=ga) * scale).to(tdt)
+        C = torch.empty(M, N, device=dev, dtype=odt)
+        config["chunks"] = op.chunks
+
+        def step():
+            op(A, Bm, bias=bias, out=C)
+        launches_per_step_flops = flops_of(w) / max(1, op.world) / op.chunks
+    else:
+        ga = torch.Generator(device=dev).manual_seed(100 + rank)
+        a_shape = (batch, M, K) if batch > 1 else (M, K)
+        # small problems: rotate over several operand sets so each step reads cold data (larger than L2 in total)
+        bytes_per_set = (M * K + K * N) * batch * (2 if w["dt"] == "bf16" else 4) + M * N * batch * (2 if w["out"] == "bf16" else 4)
+        nsets = 1 if bytes_per_set > 256e6 else int(min(64, 512e6 // bytes_per_set + 1))
+        As = [(torch.randn(a_shape, device=dev, generator=ga) * scale).to(tdt) for _ in range(nsets)]
+        Bs = [Bm] + [(torch.randn_like(Bm.float()) * scale).to(tdt) for _ in range(nsets - 1)]
+        Cs = [torch.empty((batch, M, N) if batch > 1 else (M, N), device=dev, dtype=odt) for _ in range(nsets)]
+        counter = [0]
+        config["l2"] = ("inputs larger than L2" if nsets == 1 else f"rotating over {nsets} operand sets "
+                        f"({nsets * bytes_per_set / 1e6:.0f} MB > L2) so every step reads cold data")
+
+        def step():
+            i = counter[0] % nsets
+            counter[0] += 1
+            sx.gemm(As[i], Bs[i], bias=bias, activation=w["act"], out=Cs[i], b_layout=b_layout)
+        launches_per_step_flops = flops_of(w)
+    if sharded:
+        config["l2"] = "inputs larger than L2 (per GPU: A %.0f MiB, B %.0f MiB, C %.0f MiB)" % (
+            A.numel() * A.element_size() / 2**20, Bm.numel() * Bm.element_size() / 2**20,
+            C.numel() * C.element_size() / 2**20)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sx.sync_status()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = lib.symplex_b200_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    launches = lib.symplex_b200_launch_count() - launches0
+    sx.sync_status()
+
+    # per-launch duration of the GEMM kernel alone (no collective), CUDA events on the launching stream
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sharded:
+        blk = (M // op.world) // op.chunks
+        Ak, Ck = A[:blk], C[:blk]
+
+        def kernel_only():
+            sx.gemm(Ak, Bm, bias=bias, activation=w["act"], out=Ck, b_layout=b_layout)
+    else:
+        kernel_only = step
+    kernel_only()
+    torch.cuda.synchronize()
+    kreps = max(3, min(args.steps, 10))
+    k0.record()
+    for _ in range(kreps):
+        kernel_only()
+    k1.record()
+    torch.cuda.synchronize()
+    kernel_ms = k0.elapsed_time(k1) / kreps
+    clocks = sampler.stop() if sampler else None
+
+    t = torch.tensor([elapsed_ms, float(launches)], device=dev, dtype=torch.float64)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        elapsed_ms = tmax[0].item()
+        launches = int(tsum[1].item())
+    ms_per_step = elapsed_ms / args.steps
+    replicas = 1 if sharded else world
+    value = flops_of(w) * replicas / (ms_per_step * 1e-3) / 1e12
+
+    # ---------------- end to end through the host-buffer entry points (pinned host memory)
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, w, sx, lib, torch, dist, dev, rank, world, Bm, bias, b_layout, tdt, odt,
+                      op if sharded else None, scale)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    achieved = launches_per_step_flops / (kernel_ms * 1e-3) / 1e12
+    tensor_bound = w["dt"] == "bf16" or w["K"] >= 1024
+    if w["dt"] == "bf16":
+        peak = float(peaks["bf16_tflops"])
+        peak_desc = f"bf16 dense burst, {peak_note}"
+    else:
+        peak = float(peaks["bf16_tflops"]) / 6.0
+        peak_desc = f"derived 3xTF32 ceiling = bf16 burst / 2 / 3, {peak_note}"
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "kernel_ms": kernel_ms, "peak_kind": peak_desc,
+                "flops_per_launch": launches_per_step_flops}
+    if not tensor_bound:
+        algo_bytes = ((M * K + K * N) * 4 + M * N * 4) * batch
+        ach = algo_bytes / (kernel_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": ach, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
+                    "frac": ach / float(peaks["hbm_gbs"]), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                    "kernel_ms": kernel_ms, "peak_kind": f"HBM copy, {peak_note}", "bytes_per_launch": algo_bytes,
+                    "note": "kernel_ms covers the split pre-pass and the GEMM of one step"}
+
+    cpu_baseline = None
+    if not args.no_cpu_baseline and world == 1:
+        tfl, dt, kind, cores, sample = time_cpu_reference(w, cpu_rows_for(w, seconds=4.0), steps=3, warmup=1)
+        cpu_baseline = {"value": tfl, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample}
+
+    line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if sharded else "weak", "vs_baseline": None,
+            "dtype": "bf16" if w["dt"] == "bf16" else "f32 (3xTF32 on tensor cores)", "data": "synthetic",
+            "config": config, "frac_of_bf16_peak": value / (args.gpus * float(peaks["bf16_tflops"])),
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_e2e(args, w, sx, lib, torch, dist, dev, rank, world, Bm, bias, b_layout, tdt, odt, op, scale):
+    """Same product with host buffers: pinned host -> device copies, compute, device -> host read, every step."""
+    M, N, K, batch = w["M"], w["N"], w["K"], w["batch"]
+    steps = max(2, min(args.steps, 5))
+    in_b = 2 if w["dt"] == "bf16" else 4
+    out_b = 2 if w["out"] == "bf16" else 4
+    m_loc = M // world if op is not None else M
+    hA = torch.empty((batch, m_loc, K) if batch > 1 else (m_loc, K), dtype=tdt).pin_memory()
+    hA.copy_((torch.randn(hA.shape, device=dev) * scale).to(tdt))
+    hB = Bm.cpu().pin_memory()
+    hbias = bias.cpu().pin_memory() if bias is not None else None
+    hC = torch.empty((batch, m_loc, N) if batch > 1 else (m_loc, N), dtype=odt).pin_memory()
+    h2d = hA.numel() * in_b + hB.numel() * in_b + (N * 4 if bias is not None else 0)
+    d2h = hC.numel() * out_b
+
+    if op is None or world == 1:
+        d = sx.make_desc(M, N, K, sx.DT_BF16 if w["dt"] == "bf16" else sx.DT_F32,
+                         sx.DT_BF16 if w["out"] == "bf16" else sx.DT_F32, batch=batch, b_layout=b_layout,
+                         activation=w["act"])
+
+        def host_step():
+            sx.gemm_host(d, hA.data_ptr(), hB.data_ptr(), hC.data_ptr(), hbias.data_ptr() if hbias is not None else None)
+    else:
+        dA = torch.empty(hA.shape, device=dev, dtype=tdt)
+        dB = torch.empty(hB.shape, device=dev, dtype=tdt)
+        dC = torch.empty(M, N, device=dev, dtype=odt)
+        idx = op.local_row_index().to(dev)
+
+        def host_step():
+            dA.copy_(hA, non_blocking=True)
+            dB.copy_(hB, non_blocking=True)
+            op(dA, dB, bias=bias, out=dC)
+            for c, (row0, nrows) in enumerate(op.blocks):  # this rank's rows of C go back to its host buffer
+                hC[c * nrows:(c + 1) * nrows].copy_(dC[row0:row0 + nrows], non_blocking=True)
+            torch.cuda.synchronize()
+
+    host_step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        host_step()
+    torch.cuda.synchronize()
+    dt = torch.tensor([(time.perf_counter() - t0) / steps], device=dev, dtype=torch.float64)
+    tot = torch.tensor([float(h2d), float(d2h)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    replicas = 1 if op is not None else world
+    return {"value": flops_of(w) * replicas / dt.item() / 1e12, "unit": "TFLOP/s", "ms_per_step": dt.item() * 1e3,
+            "h2d_bytes_per_step": int(tot[0].item()), "d2h_bytes_per_step": int(tot[1].item()), "steps": steps,
+            "api": "symplex_b200_gemm_host (C ABI, pinned host buffers)" if (op is None or world == 1)
+            else "RowShardedGemm with pinned host shards per rank"}
+
+
+if __name__ == "__main__":
+    sys.exit(main())

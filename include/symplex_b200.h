@@ -17,6 +17,9 @@
 #ifdef __cplusplus
 extern "C" {
 #endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library is built with hidden visibility; these are its exports */
+#endif
 
 /* Failure classes; same split as the reference's CudaError enum
  * (rust-engine/src/cuda_backend.rs:35-50). TIMEOUT is new: a bounded device-side wait expired. */
@@ -152,6 +155,9 @@ int symplex_cuda_device_info(symplex_device_info* out);
 /* Kernels launched by this library on the calling process since load (all threads). */
 uint64_t symplex_b200_launch_count(void);
 
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
 #ifdef __cplusplus
 }
 #endif

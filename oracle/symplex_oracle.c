@@ -23,9 +23,43 @@
 #include <stdlib.h>
 #include <string.h>
 
-#if defined(_OPENMP)
-#include <omp.h>
-#endif
+#include <pthread.h>
+#include <unistd.h>
+
+/* ---- row-parallel driver (pthreads) -------------------------------------------------------------
+ * Rows of C are independent in every kernel below, so splitting rows over threads changes speed only,
+ * never a result. It mirrors how the reference parallelises (rayon over row blocks,
+ * rust-engine/src/x86_emitter.rs:1861). */
+typedef void (*row_fn)(void* ctx, int64_t r0, int64_t r1);
+typedef struct { row_fn fn; void* ctx; int64_t r0, r1; } row_job;
+static void* row_thread(void* arg) {
+  row_job* j = (row_job*)arg;
+  j->fn(j->ctx, j->r0, j->r1);
+  return NULL;
+}
+static void parallel_rows(row_fn fn, void* ctx, int64_t rows, int threads) {
+  if (threads < 1) threads = 1;
+  if (threads > 256) threads = 256;
+  if ((int64_t)threads > rows) threads = rows > 0 ? (int)rows : 1;
+  if (threads == 1) { fn(ctx, 0, rows); return; }
+  pthread_t tid[256];
+  row_job job[256];
+  int started = 0;
+  for (int t = 0; t < threads; ++t) {
+    job[t].fn = fn; job[t].ctx = ctx;
+    job[t].r0 = rows * t / threads;
+    job[t].r1 = rows * (t + 1) / threads;
+    if (t == threads - 1 || pthread_create(&tid[t], NULL, row_thread, &job[t]) != 0) {
+      /* last slice (or a failed spawn) runs here, covering everything that is left */
+      job[t].r1 = rows;
+      fn(ctx, job[t].r0, job[t].r1);
+      break;
+    }
+    ++started;
+  }
+  for (int t = 0; t < started; ++t) pthread_join(tid[t], NULL);
+}
+typedef struct { const float* A; const float* B; float* C; int64_t M, N, K; const int64_t* rows; } mm_ctx;
 
 /* ---- the AVX-512 size-baked JIT kernel --------------------------------------------------------
  * rust-engine/src/x86_emitter.rs:437-631 (compile_matmul_avx512):
@@ -34,14 +68,12 @@
  *      arithmetic, every lane is an independent k-sequential FMA chain);
  *   the last N mod 16 columns :580-617: acc = 0; for k: t = A[i,k]*B[k,j] (mulss); acc = acc + t (addss).
  * Rows are independent; `threads` only splits rows for speed and never changes a result. */
-void oracle_matmul_jit_order(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
-                             int threads) {
+static void jit_order_rows(void* vctx, int64_t r0, int64_t r1) {
+  const mm_ctx* x = (const mm_ctx*)vctx;
+  const float* A = x->A; const float* B = x->B; float* C = x->C;
+  const int64_t N = x->N, K = x->K;
   const int64_t n_fma = (N / 16) * 16;
-  (void)threads;
-#if defined(_OPENMP)
-#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
-#endif
-  for (int64_t i = 0; i < M; ++i) {
+  for (int64_t i = r0; i < r1; ++i) {
     const float* a = A + i * K;
     float* c = C + i * N;
     /* blocks of 64 accumulators keep B rows streaming, as the kernel's 4 ZMM accumulators do */
@@ -66,20 +98,23 @@ void oracle_matmul_jit_order(const float* A, const float* B, float* C, int64_t M
     }
   }
 }
+void oracle_matmul_jit_order(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                             int threads) {
+  mm_ctx x = {A, B, C, M, N, K, NULL};
+  parallel_rows(jit_order_rows, &x, M, threads);
+}
 
 /* ---- the BLIS-style blocked kernel ------------------------------------------------------------
  * rust-engine/src/x86_emitter.rs:1616-1875: MC = NC = KC = 128. For each KC block of k (ascending,
  * :1724) the micro-kernel builds p = fma chain from 0 over the block's k (:1658-1673) and then does
  * C = C + p (:1676-1700). C starts at 0 (:1852-1854). Packing, MR/NR edges and zero padding do not
  * change any element's arithmetic. Row blocks are independent (rayon, :1861). */
-void oracle_matmul_blis_order(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
-                              int threads) {
+static void blis_order_rows(void* vctx, int64_t r0, int64_t r1) {
+  const mm_ctx* x = (const mm_ctx*)vctx;
+  const float* A = x->A; const float* B = x->B; float* C = x->C;
+  const int64_t N = x->N, K = x->K;
   const int64_t KC = 128, NB = 128;
-  (void)threads;
-#if defined(_OPENMP)
-#pragma omp parallel for schedule(static) num_threads(threads > 0 ? threads : 1)
-#endif
-  for (int64_t i = 0; i < M; ++i) {
+  for (int64_t i = r0; i < r1; ++i) {
     const float* a = A + i * K;
     float* c = C + i * N;
     for (int64_t j = 0; j < N; ++j) c[j] = 0.0f;
@@ -98,6 +133,11 @@ void oracle_matmul_blis_order(const float* A, const float* B, float* C, int64_t 
       }
     }
   }
+}
+void oracle_matmul_blis_order(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                              int threads) {
+  mm_ctx x = {A, B, C, M, N, K, NULL};
+  parallel_rows(blis_order_rows, &x, M, threads);
 }
 
 /* ---- dispatcher ---------------------------------------------------------------------------------
@@ -254,20 +294,21 @@ void oracle_epilogue(float* C, int64_t M, int64_t N, float alpha, float beta, co
 /* Selected rows of C = A.B in JIT order: row r of the output is row rows[r] of the full product.
  * Exact for a row-partitioned contraction; lets the tests check the large configurations on a
  * sample of rows in seconds. */
+static void jit_order_selected(void* vctx, int64_t r0, int64_t r1) {
+  const mm_ctx* x = (const mm_ctx*)vctx;
+  for (int64_t r = r0; r < r1; ++r) {
+    mm_ctx one = {x->A + x->rows[r] * x->K, x->B, x->C + r * x->N, 1, x->N, x->K, NULL};
+    jit_order_rows(&one, 0, 1);
+  }
+}
 void oracle_matmul_jit_order_rows(const float* A, const float* B, float* Crows, const int64_t* rows, int64_t nrows,
                                   int64_t N, int64_t K, int threads) {
-  (void)threads;
-#if defined(_OPENMP)
-#pragma omp parallel for schedule(dynamic, 1) num_threads(threads > 0 ? threads : 1)
-#endif
-  for (int64_t r = 0; r < nrows; ++r)
-    oracle_matmul_jit_order(A + rows[r] * K, B, Crows + r * N, 1, N, K, 1);
+  mm_ctx x = {A, B, Crows, nrows, N, K, rows};
+  parallel_rows(jit_order_selected, &x, nrows, threads);
 }
 
+/* Host cores available to this process. */
 int oracle_max_threads(void) {
-#if defined(_OPENMP)
-  return omp_get_max_threads();
-#else
-  return 1;
-#endif
+  long n = sysconf(_SC_NPROCESSORS_ONLN);
+  return n > 0 ? (int)n : 1;
 }

@@ -169,11 +169,11 @@ static int make_plan(const symplex_gemm_desc* d, const void* A, const void* B, P
   if (p->f32_in) {
     p->a_prep = p->b_prep = true;
     p->a_ldp = round_up(d->K, 4);
-    p->b_ldp = round_up(p->b_cols, 4);
+    p->b_ldp = round_up(d->K, 4);  // B planes are always written as [N][K]
     p->a_off = off;
     off = align256(off + (size_t)p->batch * 2 * d->M * p->a_ldp * 4);
     p->b_off = off;
-    off = align256(off + (size_t)p->batch * 2 * p->b_rows * p->b_ldp * 4);
+    off = align256(off + (size_t)p->batch * 2 * d->N * p->b_ldp * 4);
   } else {
     auto misaligned = [](const void* ptr, long long ld, long long bs) {
       return (ld % 8) != 0 || (bs % 8) != 0 || (reinterpret_cast<uintptr_t>(ptr) % 16) != 0;
@@ -205,6 +205,7 @@ static void debug_desc_override(TcGemmArgs* g) {
 static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, const void* B, void* C,
                     const float* bias, const void* residual, void* ws, DeviceState* st, cudaStream_t stream) {
   if (p.M == 0 || p.N == 0 || p.batch == 0) return SX_OK;  // nothing to write
+  if (p.K == 0) return fail(SX_ERR_INVALID, "K == 0 is not supported by the device entry points");
   uint8_t* w = static_cast<uint8_t*>(ws);
   TcGemmArgs g{};
   g.M = p.M; g.N = p.N; g.batch = p.batch;
@@ -215,40 +216,44 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
   g.alpha = d->alpha; g.beta = d->beta; g.act = d->activation;
   g.status = st->status;
   g.num_sms = st->num_sms;
-  // K == 0 is an empty sum: run one zero-padded k-block so the epilogue still writes act(beta R + bias).
   g.K = p.K;
   if (p.f32_in) {
+    // fp32: both operands are rewritten as {hi, lo} tf32 planes with K contiguous.
     float* Ap = reinterpret_cast<float*>(w + p.a_off);
     float* Bp = reinterpret_cast<float*>(w + p.b_off);
-    if (p.K > 0) {
-      int rc = launch_split_tf32(static_cast<const float*>(A), p.lda, p.a_bs, Ap, (int)p.M, (int)p.K, (int)p.a_ldp,
-                                 p.batch, stream);
-      if (rc != SX_OK) return fail(rc, "split_tf32(A) launch failed");
-      rc = launch_split_tf32(static_cast<const float*>(B), p.ldb, p.b_bs, Bp, (int)p.b_rows, (int)p.b_cols,
-                             (int)p.b_ldp, p.batch, stream);
-      if (rc != SX_OK) return fail(rc, "split_tf32(B) launch failed");
-      g_launches += 2;
-    }
-    g.kind = 1;
-    g.nseg = 3;
-    g.a_plane[0] = 0; g.b_plane[0] = 0;  // hi * hi
-    g.a_plane[1] = 0; g.b_plane[1] = 1;  // hi * lo
-    g.a_plane[2] = 1; g.b_plane[2] = 0;  // lo * hi
-    g.a_planes = 2; g.b_planes = 2;
-    g.za = 2 * p.batch; g.zb = 2 * p.batch;
+    int rc = launch_split_tf32(static_cast<const float*>(A), p.lda, p.a_bs, Ap, (int)p.M, (int)p.K, (int)p.a_ldp,
+                               p.batch, stream);
+    if (rc != SX_OK) return fail(rc, "split_tf32(A) launch failed");
+    if (p.b_col)
+      rc = launch_split_tf32(static_cast<const float*>(B), p.ldb, p.b_bs, Bp, (int)p.N, (int)p.K, (int)p.b_ldp,
+                             p.batch, stream);
+    else
+      rc = launch_split_tf32_transpose(static_cast<const float*>(B), p.ldb, p.b_bs, Bp, (int)p.K, (int)p.N,
+                                       (int)p.b_ldp, p.batch, stream);
+    if (rc != SX_OK) return fail(rc, "split_tf32(B) launch failed");
+    g_launches += 2;
     g.A = Ap; g.lda = p.a_ldp; g.a_plane_stride = p.M * p.a_ldp;
-    g.B = Bp; g.ldb = p.b_ldp; g.b_plane_stride = p.b_rows * p.b_ldp;
+    g.B = Bp; g.ldb = p.b_ldp; g.b_plane_stride = p.N * p.b_ldp;
+    int forced = d->tile_n;
+    if (const char* e = getenv("SYMPLEX_B200_TILE")) forced = atoi(e);
+    if (forced == 64 || forced == 128) g.bn = forced;
+    else g.bn = (p.N > 64 && ((p.M + 127) / 128) * ((p.N + 127) / 128) * p.batch >= st->num_sms) ? 128 : 64;
+    rc = launch_gemm_tf32x3(g, stream);
+    if (rc == SX_ERR_EXEC) return fail(rc, "GEMM kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    if (rc != SX_OK) return rc;
+    ++g_launches;
+    return SX_OK;
   } else {
     const void* Ause = A;
     const void* Buse = B;
     long long lda = p.lda, ldb = p.ldb, a_bs = p.a_bs, b_bs = p.b_bs;
-    if (p.a_prep && p.K > 0) {
+    if (p.a_prep) {
       int rc = launch_repack_16(A, p.lda, p.a_bs, w + p.a_off, p.a_ldp, (int)p.M, (int)p.K, p.batch, stream);
       if (rc != SX_OK) return fail(rc, "repack(A) launch failed");
       ++g_launches;
       Ause = w + p.a_off; lda = p.a_ldp; a_bs = p.M * p.a_ldp;
     }
-    if (p.b_prep && p.K > 0) {
+    if (p.b_prep) {
       int rc = launch_repack_16(B, p.ldb, p.b_bs, w + p.b_off, p.b_ldp, (int)p.b_rows, (int)p.b_cols, p.batch, stream);
       if (rc != SX_OK) return fail(rc, "repack(B) launch failed");
       ++g_launches;
@@ -265,9 +270,6 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
   if (const char* e = getenv("SYMPLEX_B200_TILE")) forced = atoi(e);
   g.bn = pick_bn(p.M, p.N, p.batch, st->num_sms, forced);
   debug_desc_override(&g);
-  if (p.K == 0) {
-    return fail(SX_ERR_INVALID, "K == 0 is not supported by the device entry points");
-  }
   int rc = launch_gemm_tc(g, stream);
   if (rc != SX_OK) {
     if (rc == SX_ERR_INVALID && strncmp(g_err, "cuTensorMap", 11) != 0)

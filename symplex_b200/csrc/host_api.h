@@ -49,6 +49,9 @@ struct TcGemmArgs {
 
 int launch_gemm_tc(const TcGemmArgs& a, cudaStream_t stream);
 int pick_bn(long long M, long long N, int batch, int num_sms, int forced);
+// 3xTF32 GEMM on pre-split operands: A planes [batch][2][M][lda], B planes [batch][2][N][ldb], both K contiguous;
+// a.bn is 128 or 64. Fields kind / b_mn / nseg / *_plane* of TcGemmArgs are ignored.
+int launch_gemm_tf32x3(const TcGemmArgs& a, cudaStream_t stream);
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
 int encode_tensor_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, const uint64_t dims[3],
@@ -59,6 +62,10 @@ int encode_tensor_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* b
 // plane 0 = tf32-rounded value, plane 1 = tf32-rounded remainder; columns >= cols are zero.
 int launch_split_tf32(const float* in, long long ld_in, long long batch_stride_in, float* out, int rows, int cols,
                       int cols_p, int batch, cudaStream_t stream);
+// Same split for a matrix that is stored transposed relative to what the GEMM wants:
+// fp32 [batch][rows][cols] -> planes [batch][2][cols][rows_p] (out[c][r] = in[r][c]); rows >= rows are zero.
+int launch_split_tf32_transpose(const float* in, long long ld_in, long long batch_stride_in, float* out, int rows,
+                                int cols, int rows_p, int batch, cudaStream_t stream);
 // Copy a 2-byte-element matrix into a buffer whose leading dimension is ld_out (zero padded).
 int launch_repack_16(const void* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
                      int rows, int cols, int batch, cudaStream_t stream);

@@ -52,6 +52,36 @@ split_tf32_kernel(const float* __restrict__ in, long long ld_in, long long batch
   }
 }
 
+// 32x32 tiles through shared memory: reads coalesced along the input's columns, writes coalesced
+// along the output's (= the input's rows).
+__global__ void __launch_bounds__(256)
+split_tf32_transpose_kernel(const float* __restrict__ in, long long ld_in, long long batch_stride_in,
+                            float* __restrict__ out, int rows, int cols, int rows_p) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const float* src = in + (long long)b * batch_stride_in;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + ty + i * 8, c = c0 + tx;
+    tile[ty + i * 8][tx] = (r < rows && c < cols) ? __ldg(src + (long long)r * ld_in + c) : 0.0f;
+  }
+  __syncthreads();
+  float* o_hi = out + ((long long)b * 2 + 0) * cols * rows_p;
+  float* o_lo = out + ((long long)b * 2 + 1) * cols * rows_p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = c0 + ty + i * 8, r = r0 + tx;  // output row = input column c, output column = input row r
+    if (c < cols && r < rows_p) {
+      const float x = tile[tx][ty + i * 8];
+      const float hi = tf32_round(x);
+      o_hi[(long long)c * rows_p + r] = hi;
+      o_lo[(long long)c * rows_p + r] = tf32_round(x - hi);
+    }
+  }
+}
+
 template <typename InT, bool kToBf16>
 __global__ void __launch_bounds__(256)
 repack_kernel(const InT* __restrict__ in, long long ld_in, long long batch_stride_in, uint16_t* __restrict__ out,
@@ -91,6 +121,15 @@ int launch_split_tf32(const float* in, long long ld_in, long long batch_stride_i
   if (cols_p % 4 != 0 || cols_p < cols) return SX_ERR_INVALID;
   const long long items = (long long)rows * (cols_p / 4) * batch;
   split_tf32_kernel<<<grid_for(items), 256, 0, stream>>>(in, ld_in, batch_stride_in, out, rows, cols, cols_p, batch);
+  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+}
+
+int launch_split_tf32_transpose(const float* in, long long ld_in, long long batch_stride_in, float* out, int rows,
+                                int cols, int rows_p, int batch, cudaStream_t stream) {
+  if (rows_p % 4 != 0 || rows_p < rows || batch > 65535) return SX_ERR_INVALID;
+  dim3 grid((cols + 31) / 32, (rows_p + 31) / 32, batch);
+  if (grid.y > 65535) return SX_ERR_INVALID;
+  split_tf32_transpose_kernel<<<grid, 256, 0, stream>>>(in, ld_in, batch_stride_in, out, rows, cols, rows_p);
   return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
 }
 

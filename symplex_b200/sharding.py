@@ -1,0 +1,189 @@
+"""Row-sharded GEMM across the GPUs of one box, and the ShardPlan vocabulary that describes it.
+
+Mirrors the planning types of the reference (``include/symplex/distributed/sharding.h:18-95``:
+``ShardingStrategy``, ``ShardingSpec``, ``ShardPlan``; ``nccl_bridge.h:19-26``: ``CollectiveOp``) and
+turns the plan into an executed computation: one process per GPU, ``torch.distributed`` (NCCL over
+NVLink) for the exchange, the tcgen05 GEMM library for the math.
+
+Partition (the reference parallelises the same way over CPU threads,
+``rust-engine/src/x86_emitter.rs:1857-1874``): rows of A and C are split evenly over the ranks, B is
+replicated, and C is all-gathered so every rank ends with the full product. To overlap the exchange
+with compute the local rows are processed in ``chunks`` pieces; the piece of every rank for chunk c
+forms one contiguous block of C, so each chunk is gathered in place by a single all-gather while the
+next chunk's GEMM runs. Rank g therefore owns, for each chunk c, rows
+``c*M/chunks + g*M/(chunks*world) + [0, M/(chunks*world))`` — with ``chunks == 1`` the usual
+contiguous split.
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence, Tuple
+
+
+class ShardingStrategy(enum.Enum):
+    """``sharding.h:18-24``."""
+    REPLICATE = 0
+    SHARD_DIM_0 = 1
+    SHARD_DIM_1 = 2
+    SHARD_2D = 3
+    PIPELINE = 4
+
+
+class CollectiveOp(enum.Enum):
+    """``nccl_bridge.h:19-26``."""
+    ALL_REDUCE = 0
+    ALL_GATHER = 1
+    REDUCE_SCATTER = 2
+    ALL_TO_ALL = 3
+    BROADCAST = 4
+    SEND_RECV = 5
+
+
+@dataclass
+class ShardingSpec:
+    """``sharding.h:27-62``."""
+    tensor_name: str
+    strategy: ShardingStrategy = ShardingStrategy.REPLICATE
+    shard_dims: List[int] = field(default_factory=list)
+    original_shape: List[int] = field(default_factory=list)
+    local_shape: List[int] = field(default_factory=list)
+
+    def to_string(self) -> str:
+        return (f"ShardingSpec{{name='{self.tensor_name}', strategy={self.strategy.name}, "
+                f"shard_dims=[{', '.join(map(str, self.shard_dims))}], "
+                f"original=[{'x'.join(map(str, self.original_shape))}], "
+                f"local=[{'x'.join(map(str, self.local_shape))}]}}")
+
+
+@dataclass
+class ShardPlan:
+    """``sharding.h:65-95`` plus ``all_gather_ops`` (the reference's plan only names all-reduce and
+    all-to-all; the row-sharded GEMM needs an all-gather)."""
+    tensor_shards: List[ShardingSpec] = field(default_factory=list)
+    all_reduce_ops: List[str] = field(default_factory=list)
+    all_to_all_ops: List[str] = field(default_factory=list)
+    all_gather_ops: List[str] = field(default_factory=list)
+    total_communication_bytes: int = 0
+    peak_memory_per_device: int = 0
+
+    def to_string(self) -> str:
+        return (f"ShardPlan{{tensors=[{', '.join(s.to_string() for s in self.tensor_shards)}], "
+                f"all_reduce_ops=[{', '.join(self.all_reduce_ops)}], "
+                f"all_to_all_ops=[{', '.join(self.all_to_all_ops)}], "
+                f"all_gather_ops=[{', '.join(self.all_gather_ops)}], "
+                f"comm_bytes={self.total_communication_bytes}, peak_mem={self.peak_memory_per_device}}}")
+
+
+def analyze_matmul(M: int, N: int, K: int, world_size: int, tensor_a: str = "A", tensor_b: str = "B",
+                   tensor_c: str = "C", bytes_per_element: int = 2) -> ShardPlan:
+    """Plan C = A.B over ``world_size`` devices: A ``SHARD_DIM_0``, B ``REPLICATE``, C computed
+    ``SHARD_DIM_0`` and all-gathered (``ShardingAnalyzer::analyze_matmul``, ``sharding.h:107-112``, with
+    the row split this path uses instead of the K split the reference's comment describes).
+
+    ``total_communication_bytes`` counts what every device receives: (world-1)/world of C.
+    """
+    if world_size < 1:
+        raise ValueError("world_size must be >= 1")
+    if M % world_size != 0:
+        raise ValueError(f"M={M} rows do not split evenly over {world_size} devices")
+    m_loc = M // world_size
+    bpe = bytes_per_element
+    plan = ShardPlan()
+    plan.tensor_shards = [
+        ShardingSpec(tensor_a, ShardingStrategy.SHARD_DIM_0, [0], [M, K], [m_loc, K]),
+        ShardingSpec(tensor_b, ShardingStrategy.REPLICATE, [], [K, N], [K, N]),
+        ShardingSpec(tensor_c, ShardingStrategy.SHARD_DIM_0, [0], [M, N], [m_loc, N]),
+    ]
+    if world_size > 1:
+        plan.all_gather_ops = [f"all_gather({tensor_c}, dim=0)"]
+        plan.total_communication_bytes = world_size * (world_size - 1) * m_loc * N * bpe
+    plan.peak_memory_per_device = (m_loc * K + K * N + M * N) * bpe
+    return plan
+
+
+def owned_row_blocks(M: int, world_size: int, rank: int, chunks: int) -> List[Tuple[int, int]]:
+    """``(first_row, row_count)`` of the block of C (and A) that ``rank`` owns in each chunk."""
+    if M % (world_size * chunks) != 0:
+        raise ValueError(f"M={M} must be a multiple of world_size*chunks={world_size * chunks}")
+    blk = M // (world_size * chunks)
+    return [(c * (M // chunks) + rank * blk, blk) for c in range(chunks)]
+
+
+def pick_chunks(M: int, world_size: int, requested: Optional[int] = None) -> int:
+    """Largest chunk count <= requested (default 4) that splits the rows evenly into blocks of whole
+    128-row tiles; 1 on a single device (nothing to overlap)."""
+    if world_size == 1:
+        return 1
+    want = requested if requested is not None else 4
+    for c in range(max(1, want), 0, -1):
+        if M % (world_size * c) == 0 and (M // (world_size * c)) % 128 == 0:
+            return c
+    return 1
+
+
+class RowShardedGemm:
+    """C = act(alpha * A.B + bias) with A row-sharded, B replicated, C all-gathered (bf16 or fp32).
+
+    One instance per process; ``__call__`` takes this rank's rows of A (``[M/world, K]``, ordered as
+    ``local_row_index()`` says), the full B, and returns the full C on every rank. The all-gather of
+    chunk c is issued asynchronously right after chunk c's GEMM and runs on NCCL's stream while chunk
+    c+1 computes; the call returns after all chunks have been gathered (stream-ordered, no host sync).
+    """
+
+    def __init__(self, M: int, N: int, K: int, *, group=None, chunks: Optional[int] = None, activation=None,
+                 b_layout: int = 0, local_gemm: Optional[Callable] = None):
+        import torch.distributed as dist
+        self.group = group
+        if dist.is_available() and dist.is_initialized():
+            self.world = dist.get_world_size(group)
+            self.rank = dist.get_rank(group)
+        else:
+            self.world, self.rank = 1, 0
+        if M % self.world != 0:
+            raise ValueError(f"M={M} rows do not split evenly over {self.world} ranks")
+        self.M, self.N, self.K = M, N, K
+        self.chunks = pick_chunks(M, self.world, chunks)
+        self.blocks = owned_row_blocks(M, self.world, self.rank, self.chunks)
+        self.activation = activation
+        self.b_layout = b_layout
+        self.plan = analyze_matmul(M, N, K, self.world)
+        # Host-logic tests (gloo, CPU tensors) inject the per-chunk product; the default is the CUDA library.
+        self._local_gemm = local_gemm
+
+    def local_row_index(self):
+        """Global row numbers of this rank's rows of A / C, in local storage order."""
+        import torch
+        return torch.cat([torch.arange(s, s + n) for s, n in self.blocks])
+
+    def _gemm_chunk(self, A_blk, B, bias, out_blk):
+        if self._local_gemm is not None:
+            self._local_gemm(A_blk, B, bias, out_blk)
+            return
+        from . import gemm
+        gemm(A_blk, B, bias=bias, activation=self.activation, out=out_blk, b_layout=self.b_layout)
+
+    def __call__(self, A_local, B, *, bias=None, out=None, out_dtype=None):
+        import torch
+        import torch.distributed as dist
+        m_loc = self.M // self.world
+        if tuple(A_local.shape) != (m_loc, self.K):
+            raise ValueError(f"A_local must be [{m_loc}, {self.K}], got {tuple(A_local.shape)}")
+        if out is None:
+            dt = out_dtype if out_dtype is not None else A_local.dtype
+            out = torch.empty((self.M, self.N), device=A_local.device, dtype=dt)
+        elif tuple(out.shape) != (self.M, self.N) or not out.is_contiguous():
+            raise ValueError(f"out must be a contiguous [{self.M}, {self.N}] tensor")
+        blk = m_loc // self.chunks
+        chunk_rows = self.M // self.chunks
+        works = []
+        for c, (row0, nrows) in enumerate(self.blocks):
+            mine = out[row0:row0 + nrows]
+            self._gemm_chunk(A_local[c * blk:(c + 1) * blk], B, bias, mine)
+            if self.world > 1:
+                whole = out[c * chunk_rows:(c + 1) * chunk_rows]
+                # in place: this rank's block already sits at its slot of the gathered chunk
+                works.append(dist.all_gather_into_tensor(whole, mine, group=self.group, async_op=True))
+        for w in works:
+            w.wait()  # makes the current stream wait for the collective; does not block the host on NCCL
+        return out

@@ -1,0 +1,355 @@
+"""Parity of the CUDA path against the CPU oracle, through the C ABI, on a B200.
+
+Tolerances are BASELINE's: relative Frobenius error <= 1e-5 for the fp32 (3xTF32) path against the
+reference's fp32 result, <= 1e-2 for bf16 inputs against the reference run on bf16-rounded inputs.
+Large configurations are checked on a sample of rows (exact for a row-partitioned contraction) plus a
+whole-output checksum identity.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import symplex_b200 as sx
+from oracle_loader import rel_frobenius
+from symplex_b200 import _capi, _symplex_core as core, engine
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-5
+TOL_BF16 = 1e-2
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _require_gpu(lib):
+    assert lib.symplex_cuda_available() == 1, "these tests need a B200 and the CUDA library (no fallback)"
+    before = lib.symplex_b200_launch_count()
+    yield
+    assert lib.symplex_b200_launch_count() > before, "no kernel of the library was launched"
+    assert lib.symplex_b200_sync_status(None) == 0
+
+
+def _bf16_t(x_np):
+    """numpy fp32 (already bf16-representable) -> torch bf16 on the GPU."""
+    return torch.from_numpy(x_np).to(DEV).to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------ fp32 path, host-pointer drop-ins
+
+def test_config1_fp32_512_cube(lib, oracle):
+    """BASELINE config 1: the shape the reference's own JIT-vs-NumPy bench runs."""
+    rng = np.random.default_rng(0)
+    A = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
+    B = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
+    ref = oracle.jit_parallel_matmul(A, B)
+    for fn in (core.jit_parallel_matmul, core.parallel_matmul, core.cuda_matmul):
+        C = np.full((512, 512), np.nan, np.float32)
+        assert fn(A.ctypes.data, B.ctypes.data, C.ctypes.data, 512, 512, 512) == 0
+        assert rel_frobenius(C, ref) <= TOL_F32
+    assert rel_frobenius(sx.matmul_jit(A, B), ref) <= TOL_F32
+    assert rel_frobenius(sx.matmul_tiled(A, B), ref) <= TOL_F32
+
+
+@pytest.mark.parametrize("shape", [
+    (1, 1, 1), (2, 2, 2), (4, 4, 4), (3, 5, 7), (65, 33, 17), (128, 128, 128), (129, 257, 63), (1, 1000, 33),
+    (1000, 1, 33), (300, 200, 1), (257, 129, 1025), (64, 64, 4096),
+])
+def test_fp32_shapes_against_oracle(lib, oracle, shape):
+    M, N, K = shape
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    C = np.full((M, N), np.nan, np.float32)
+    lib.symplex_matmul_f32(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K)
+    assert not np.isnan(C).any()
+    assert rel_frobenius(C, oracle.jit_parallel_matmul(A, B)) <= TOL_F32
+
+
+def test_reference_known_answers_on_gpu(lib):
+    A = np.array([[1, 2], [3, 4]], np.float32)
+    B = np.array([[5, 6], [7, 8]], np.float32)
+    np.testing.assert_array_equal(sx.matmul_jit(A, B), [[19, 22], [43, 50]])  # python/tests/test_jit.py:60-66
+    Bm = np.arange(1, 17, dtype=np.float32).reshape(4, 4)
+    np.testing.assert_allclose(sx.matmul_jit(np.eye(4, dtype=np.float32), Bm), Bm, atol=0.01)  # matmul_kernel.rs:1230
+    a = (((np.arange(128 * 128) * 7 + 13) % 97) / 10.0).astype(np.float32).reshape(128, 128)   # matmul_bench.rs:39
+    b = (((np.arange(128 * 128) * 11 + 17) % 89) / 10.0).astype(np.float32).reshape(128, 128)
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    assert np.max(np.abs(sx.matmul_jit(a, b) - exact)) <= 0.01
+    rng = np.random.default_rng(42)  # test_jit_native.py:60-78
+    x, y = rng.standard_normal((32, 32)).astype(np.float32), rng.standard_normal((32, 32)).astype(np.float32)
+    C = np.zeros((32, 32), np.float32)
+    assert engine.MatmulKernel().execute_raw(x.ctypes.data, y.ctypes.data, C.ctypes.data, 32, 32, 32) == 0
+    assert np.max(np.abs(C - x @ y)) < 1e-2
+
+
+def test_golden_vectors_from_the_reference(lib, golden):
+    for i in range(int(golden["mm_count"])):
+        A, B = golden[f"mm{i}_A"], golden[f"mm{i}_B"]
+        got = sx.matmul_jit(A, B)
+        for key in ("py_matmul_jit", "c_matmul_f32", "c_matmul_tiled_f32"):
+            assert rel_frobenius(got, golden[f"mm{i}_{key}"]) <= TOL_F32, (i, key)
+    X, W, b = golden["fused_X"], golden["fused_W"], golden["fused_b"]
+    assert rel_frobenius(sx.fused_matmul_bias_relu(X, W, b), golden["fused_relu"]) <= TOL_F32
+    d = sx.make_desc(X.shape[0], W.shape[1], X.shape[1], activation="gelu")
+    C = np.zeros((X.shape[0], W.shape[1]), np.float32)
+    sx.gemm_host(d, X.ctypes.data, W.ctypes.data, C.ctypes.data, b.ctypes.data)
+    assert rel_frobenius(C, golden["fused_gelu"]) <= TOL_F32
+
+
+def test_fused_matmul_bias_relu_kernel_abi(lib, oracle):
+    rng = np.random.default_rng(11)
+    M, N, K = 200, 136, 300
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    ref = oracle.fused_matmul_bias_relu(A, B, bias)
+    C = np.full((M, N), np.nan, np.float32)
+    k = engine.FusedMatMulBiasReLUKernel()
+    assert k.execute_raw(A.ctypes.data, B.ctypes.data, C.ctypes.data, bias.ctypes.data, M, N, K) == 0
+    assert rel_frobenius(C, ref) <= TOL_F32
+    assert np.all(C >= 0)
+    C2 = np.zeros_like(C)
+    assert lib.symplex_exec_fused_matmul_bias_relu(A.ctypes.data, B.ctypes.data, C2.ctypes.data, M, N, K,
+                                                   bias.ctypes.data) == 0
+    np.testing.assert_array_equal(C, C2)  # deterministic
+
+
+def test_thin_sgemm_abi_and_fixed_dims_kernel(lib, oracle):
+    rng = np.random.default_rng(12)
+    A = rng.uniform(-1, 1, (96, 80)).astype(np.float32)
+    B = rng.uniform(-1, 1, (80, 112)).astype(np.float32)
+    ref = oracle.jit_parallel_matmul(A, B)
+    for fn in (lib.blas_sgemm, lib.cache_tiled_sgemm_thin, lib.symplex_matmul_tiled_f32):
+        C = np.full((96, 112), np.nan, np.float32)
+        fn(A.ctypes.data, B.ctypes.data, C.ctypes.data, 96, 112, 80)
+        assert rel_frobenius(C, ref) <= TOL_F32
+    k = engine.AVX512MatmulKernel(96, 112, 80)
+    C = np.full((96, 112), np.nan, np.float32)
+    assert k.execute_raw(A.ctypes.data, B.ctypes.data, C.ctypes.data, 1, 1, 1) == 0  # runtime dims ignored
+    assert rel_frobenius(C, ref) <= TOL_F32
+
+
+def test_device_info_and_availability(lib):
+    info = core.cuda_device_info()
+    assert info["available"] is True and info["compute_capability_major"] == 10
+    assert info["num_sms"] >= 100 and info["warp_size"] == 32 and info["total_memory_bytes"] > 100e9
+    assert info["sm_arch"].startswith("sm_10") and "B200" in core.cuda_info()
+
+
+# ------------------------------------------------------------------ device-pointer API
+
+def _run(A_t, B_t, **kw):
+    out = sx.gemm(A_t, B_t, **kw)
+    sx.sync_status()
+    return out
+
+
+def test_config2_bf16_4096_colmajor_b(lib, oracle):
+    """BASELINE config 2 (bf16): row-major A, column-major B, fp32 output; oracle on 512 sampled rows."""
+    rng = np.random.default_rng(2)
+    n = 4096
+    A = oracle.bf16_round(rng.standard_normal((n, n)).astype(np.float32))
+    Bt = oracle.bf16_round(rng.standard_normal((n, n)).astype(np.float32))  # stored [N, K] = column-major B
+    C = _run(_bf16_t(A), _bf16_t(Bt), b_layout=sx.COL_MAJOR, out_dtype=torch.float32).cpu().numpy()
+    rows = np.sort(rng.choice(n, 512, replace=False))
+    ref = oracle.matmul_rows(A, np.ascontiguousarray(Bt.T), rows)
+    assert rel_frobenius(C[rows], ref) <= TOL_BF16
+    assert rel_frobenius(C[rows], ref) <= 1e-5  # bf16 products are exact in fp32; only summation order differs
+    _checksum_identity(C, A, Bt.T, 1e-5)
+
+
+def test_config2_fp32_4096_via_3xtf32(lib, oracle):
+    rng = np.random.default_rng(3)
+    n = 4096
+    A = rng.standard_normal((n, n)).astype(np.float32)
+    Bt = rng.standard_normal((n, n)).astype(np.float32)
+    C = _run(torch.from_numpy(A).to(DEV), torch.from_numpy(Bt).to(DEV), b_layout=sx.COL_MAJOR).cpu().numpy()
+    rows = np.sort(rng.choice(n, 256, replace=False))
+    ref = oracle.matmul_rows(A, np.ascontiguousarray(Bt.T), rows)
+    assert rel_frobenius(C[rows], ref) <= TOL_F32
+    _checksum_identity(C, A, Bt.T, 1e-5)
+
+
+def _checksum_identity(C, A, B, tol):
+    """Whole-output property: C.1 == A.(B.1) (evaluated in fp64)."""
+    lhs = C.astype(np.float64).sum(axis=1)
+    rhs = A.astype(np.float64) @ B.astype(np.float64).sum(axis=1)
+    scale = np.linalg.norm(np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64).sum(axis=1))
+    assert np.linalg.norm(lhs - rhs) / scale <= tol
+
+
+def test_config3_fused_gelu_mlp_layer(lib, oracle):
+    """BASELINE config 3: Y = GELU(X.W + b), bf16 in/out, one kernel; oracle on 96 sampled rows."""
+    rng = np.random.default_rng(4)
+    M, K, N = 8192, 4096, 16384
+    X = oracle.bf16_round(rng.normal(0, 0.02, (M, K)).astype(np.float32))
+    W = oracle.bf16_round(rng.normal(0, 0.02, (K, N)).astype(np.float32))
+    b = rng.normal(0, 0.02, N).astype(np.float32)
+    before = sx.launch_count()
+    Y = _run(_bf16_t(X), _bf16_t(W), bias=torch.from_numpy(b).to(DEV), activation="gelu")
+    assert sx.launch_count() - before == 1, "the fused layer must be a single kernel"
+    assert Y.dtype == torch.bfloat16
+    rows = np.sort(rng.choice(M, 96, replace=False))
+    ref = oracle.epilogue(oracle.matmul_rows(X, W, rows), bias=b, act=_capi.ACT_GELU)
+    ref = oracle.bf16_round(ref)
+    got = Y[torch.from_numpy(rows).to(DEV)].float().cpu().numpy()
+    assert rel_frobenius(got, ref) <= TOL_BF16
+
+
+def test_config4_batched_small_gemm(lib, oracle):
+    """BASELINE config 4: 2048 independent fp32 64x64x64 problems, strided-batched."""
+    rng = np.random.default_rng(5)
+    nb = 2048
+    A = rng.uniform(-1, 1, (nb, 64, 64)).astype(np.float32)
+    B = rng.uniform(-1, 1, (nb, 64, 64)).astype(np.float32)
+    C = _run(torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV)).cpu().numpy()
+    ref = np.stack([oracle.jit_parallel_matmul(A[i], B[i], threads=1) for i in range(nb)])
+    assert rel_frobenius(C, ref) <= TOL_F32
+    worst = max(rel_frobenius(C[i], ref[i]) for i in range(0, nb, 37))
+    assert worst <= TOL_F32
+
+
+def test_config5_row_sharded_shape_on_one_gpu(lib, oracle):
+    """BASELINE config 5 at one GPU: bf16 [65536, 8192] x [8192, 8192] -> bf16, no collective."""
+    from symplex_b200.sharding import RowShardedGemm
+    g = torch.Generator(device=DEV).manual_seed(6)
+    M, N, K = 65536, 8192, 8192
+    A = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    B = torch.randn(K, N, device=DEV, generator=g).to(torch.bfloat16)
+    op = RowShardedGemm(M, N, K)
+    assert op.world == 1 and op.chunks == 1
+    C = op(A, B)
+    sx.sync_status()
+    rows = np.sort(np.random.default_rng(6).choice(M, 48, replace=False))
+    rows_t = torch.from_numpy(rows).to(DEV)
+    ref = oracle.bf16_round(oracle.matmul_rows(A[rows_t].float().cpu().numpy(), B.float().cpu().numpy(),
+                                               np.arange(len(rows))))
+    assert rel_frobenius(C[rows_t].float().cpu().numpy(), ref) <= TOL_BF16
+    # whole-output checksum on the device in fp64: C.1 == A.(B.1), up to the bf16 rounding of C
+    lhs = C.double().sum(dim=1)
+    rhs = A.double() @ B.double().sum(dim=1)
+    scale = (A.double().abs() @ B.double().abs().sum(dim=1)).norm()
+    assert ((lhs - rhs).norm() / scale).item() <= 1e-3
+
+
+@pytest.mark.parametrize("tile", [64, 128, 256])
+@pytest.mark.parametrize("b_layout", [0, 1])
+def test_bf16_tiles_and_layouts(lib, oracle, tile, b_layout):
+    rng = np.random.default_rng(tile + b_layout)
+    M, N, K = 384, 640, 520
+    A = oracle.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    B = oracle.bf16_round(rng.standard_normal((K, N)).astype(np.float32))
+    Bs = np.ascontiguousarray(B.T) if b_layout == sx.COL_MAJOR else B
+    C = _run(_bf16_t(A), _bf16_t(Bs), b_layout=b_layout, out_dtype=torch.float32, tile_n=tile).cpu().numpy()
+    assert rel_frobenius(C, oracle.jit_parallel_matmul(A, B)) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(1, 8, 8), (5, 3, 9), (130, 70, 17), (128, 256, 64), (100, 260, 33), (257, 8, 1000)])
+@pytest.mark.parametrize("b_layout", [0, 1])
+def test_bf16_ragged_and_unaligned(lib, oracle, shape, b_layout):
+    """Shapes whose rows are not multiples of 16 bytes go through the padded-copy path."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    A = oracle.bf16_round(rng.standard_normal((M, K)).astype(np.float32))
+    B = oracle.bf16_round(rng.standard_normal((K, N)).astype(np.float32))
+    Bs = np.ascontiguousarray(B.T) if b_layout == sx.COL_MAJOR else B
+    C = _run(_bf16_t(A), _bf16_t(Bs), b_layout=b_layout).float().cpu().numpy()
+    ref = oracle.bf16_round(oracle.jit_parallel_matmul(A, B))
+    assert rel_frobenius(C, ref) <= TOL_BF16
+
+
+ACTS = [("none", 0), ("relu", 1), ("gelu", 2), ("sigmoid", 3), ("tanh", 4), ("silu", 5)]
+
+
+@pytest.mark.parametrize("name,code", ACTS)
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_epilogue_chain(lib, oracle, name, code, dtype):
+    """[MatMul, Mul, Add, act] with a residual: act(alpha * A.B + beta * R + bias)."""
+    rng = np.random.default_rng(code)
+    M, N, K = 200, 328, 136
+    A = rng.normal(0, 0.5, (M, K)).astype(np.float32)
+    B = rng.normal(0, 0.5, (K, N)).astype(np.float32)
+    R = rng.normal(0, 1, (M, N)).astype(np.float32)
+    bias = rng.normal(0, 1, N).astype(np.float32)
+    alpha, beta = 0.75, -0.5
+    if dtype == "bf16":
+        A, B, R = oracle.bf16_round(A), oracle.bf16_round(B), oracle.bf16_round(R)
+        mk = _bf16_t
+    else:
+        mk = lambda x: torch.from_numpy(x).to(DEV)
+    out = _run(mk(A), mk(B), bias=torch.from_numpy(bias).to(DEV), residual=mk(R), activation=name,
+               alpha=alpha, beta=beta).float().cpu().numpy()
+    ref = oracle.epilogue(oracle.jit_parallel_matmul(A, B), alpha=alpha, beta=beta, residual=R, bias=bias, act=code)
+    if dtype == "bf16":
+        assert rel_frobenius(out, oracle.bf16_round(ref)) <= TOL_BF16
+    else:
+        assert rel_frobenius(out, ref) <= TOL_F32
+
+
+def test_fp32_rowmajor_and_colmajor_b_agree(lib, oracle):
+    rng = np.random.default_rng(21)
+    M, N, K = 300, 200, 500
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    c_row = _run(torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV))
+    c_col = _run(torch.from_numpy(A).to(DEV), torch.from_numpy(np.ascontiguousarray(B.T)).to(DEV),
+                 b_layout=sx.COL_MAJOR)
+    assert torch.equal(c_row, c_col)  # same planes, same kernel: bit-identical
+    assert rel_frobenius(c_row.cpu().numpy(), oracle.jit_parallel_matmul(A, B)) <= TOL_F32
+
+
+def test_fp32_accuracy_does_not_drift_with_k(lib, oracle):
+    """Long reductions: the in-tensor-core accumulation is drained every 128 k, so error stays flat."""
+    rng = np.random.default_rng(22)
+    M, N, K = 128, 128, 16384
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    C = _run(torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV)).cpu().numpy()
+    exact = A.astype(np.float64) @ B.astype(np.float64)
+    assert rel_frobenius(C, exact) <= 2e-6
+    assert rel_frobenius(C, oracle.jit_parallel_matmul(A, B)) <= TOL_F32
+
+
+def test_linearity_property_full_size(lib):
+    """(A1 + A2).B == A1.B + A2.B within fp32 rounding, at 4096^3 (no oracle needed)."""
+    g = torch.Generator(device=DEV).manual_seed(23)
+    n = 4096
+    A1 = torch.randn(n, n, device=DEV, generator=g)
+    A2 = torch.randn(n, n, device=DEV, generator=g)
+    B = torch.randn(n, n, device=DEV, generator=g)
+    lhs = _run(A1 + A2, B)
+    rhs = _run(A1, B) + _run(A2, B)
+    assert ((lhs - rhs).double().norm() / lhs.double().norm()).item() <= 5e-6
+
+
+def test_caller_workspace_entry_point(lib, oracle):
+    rng = np.random.default_rng(24)
+    M, N, K = 256, 192, 320
+    A = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).to(DEV)
+    B = torch.from_numpy(rng.standard_normal((K, N)).astype(np.float32)).to(DEV)
+    d = sx.make_desc(M, N, K)
+    need = lib.symplex_b200_gemm_workspace_bytes(ctypes.byref(d))
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    C = torch.full((M, N), float("nan"), device=DEV)
+    s = torch.cuda.current_stream().cuda_stream
+    assert lib.symplex_b200_gemm_ws(ctypes.byref(d), A.data_ptr(), B.data_ptr(), C.data_ptr(), None, None,
+                                    ws.data_ptr(), need, s) == 0
+    assert lib.symplex_b200_gemm_ws(ctypes.byref(d), A.data_ptr(), B.data_ptr(), C.data_ptr(), None, None,
+                                    ws.data_ptr(), need - 1, s) == _capi.ERR_INVALID
+    sx.sync_status()
+    assert torch.equal(C, sx.gemm(A, B))
+
+
+def test_strided_host_output(lib, oracle):
+    """ldc > N on the host path keeps the bytes between rows."""
+    rng = np.random.default_rng(25)
+    M, N, K, ldc = 40, 24, 16, 32
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    Cbuf = np.full((M, ldc), 9.0, np.float32)
+    d = sx.make_desc(M, N, K, ldc=ldc)
+    sx.gemm_host(d, A.ctypes.data, B.ctypes.data, Cbuf.ctypes.data)
+    assert np.all(Cbuf[:, N:] == 9.0)
+    assert rel_frobenius(Cbuf[:, :N], oracle.jit_parallel_matmul(A, B)) <= TOL_F32

@@ -1,0 +1,122 @@
+"""Host logic of the row-sharded GEMM on CPU: the plan, the row ownership map, and the chunked in-place
+all-gather pipeline run as two gloo ranks. The per-chunk product is injected (torch on CPU) - these
+tests exercise the distribution logic, not the GPU kernels."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from symplex_b200 import sharding
+from symplex_b200.sharding import ShardingStrategy
+
+
+def test_plan_matches_row_sharded_config():
+    # BASELINE config 5: A [65536, 8192] split by rows, B replicated, bf16 C all-gathered
+    plan = sharding.analyze_matmul(65536, 8192, 8192, 8)
+    a, b, c = plan.tensor_shards
+    assert (a.strategy, a.local_shape) == (ShardingStrategy.SHARD_DIM_0, [8192, 8192])
+    assert (b.strategy, b.local_shape) == (ShardingStrategy.REPLICATE, [8192, 8192])
+    assert (c.strategy, c.original_shape, c.local_shape) == (ShardingStrategy.SHARD_DIM_0, [65536, 8192], [8192, 8192])
+    assert plan.all_gather_ops == ["all_gather(C, dim=0)"] and plan.all_reduce_ops == []
+    # every rank receives 7/8 of C in bf16
+    assert plan.total_communication_bytes == 8 * 7 * 8192 * 8192 * 2
+    assert "SHARD_DIM_0" in plan.to_string() and "comm_bytes=" in plan.to_string()
+
+
+def test_plan_like_reference_test():
+    # tests/test_distributed.cpp:27-33 of the reference: analyze_matmul(4096^3) gives a non-empty plan
+    # with communication; a single device needs none.
+    plan = sharding.analyze_matmul(4096, 4096, 4096, 4)
+    assert plan.tensor_shards and plan.total_communication_bytes > 0
+    solo = sharding.analyze_matmul(4096, 4096, 4096, 1)
+    assert solo.total_communication_bytes == 0 and solo.all_gather_ops == []
+    with pytest.raises(ValueError):
+        sharding.analyze_matmul(1000, 8, 8, 3)
+
+
+@pytest.mark.parametrize("M,world,chunks", [(1024, 2, 4), (65536, 8, 4), (512, 4, 1), (768, 3, 2)])
+def test_row_ownership_is_a_partition(M, world, chunks):
+    seen = np.zeros(M, np.int32)
+    for r in range(world):
+        blocks = sharding.owned_row_blocks(M, world, r, chunks)
+        assert len(blocks) == chunks
+        for c, (start, n) in enumerate(blocks):
+            assert n == M // (world * chunks)
+            # chunk c of every rank lies inside one contiguous block of C, in rank order
+            assert c * (M // chunks) <= start and start + n <= (c + 1) * (M // chunks)
+            assert start == c * (M // chunks) + r * n
+            seen[start:start + n] += 1
+    assert np.all(seen == 1)
+
+
+def test_pick_chunks():
+    assert sharding.pick_chunks(65536, 1) == 1
+    assert sharding.pick_chunks(65536, 8) == 4
+    assert sharding.pick_chunks(65536, 8, 16) == 16
+    assert sharding.pick_chunks(1024, 8) == 1      # 128 rows per rank: one tile, no split
+    assert sharding.pick_chunks(3 * 256, 2, 4) == 3
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _cpu_gemm(A_blk, B, bias, out_blk):
+    r = A_blk.float() @ B.float()
+    if bias is not None:
+        r = r + bias
+    out_blk.copy_(r.to(out_blk.dtype))
+
+
+def _worker(rank, world, port, M, N, K, chunks, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(1234)
+        A = torch.randn(M, K, generator=g)
+        B = torch.randn(K, N, generator=g)
+        bias = torch.randn(N, generator=g)
+        op = sharding.RowShardedGemm(M, N, K, chunks=chunks, local_gemm=_cpu_gemm)
+        idx = op.local_row_index()
+        C = op(A[idx].contiguous(), B, bias=bias, out_dtype=torch.float32)
+        ref = A @ B + bias
+        q.put((rank, op.chunks, bool(torch.equal(C, ref)), idx.tolist()[:3]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("chunks", [1, 2])
+def test_two_rank_gloo_pipeline(chunks):
+    world, M, N, K = 2, 512, 48, 40
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, M, N, K, chunks, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, used_chunks, ok, first_rows in sorted(results):
+        assert used_chunks == chunks
+        assert ok, f"rank {rank}: gathered C differs from the full product"
+    starts = {r: rows[0] for r, _, _, rows in results}
+    assert starts[0] == 0 and starts[1] == M // (world * chunks)
+
+
+def test_single_process_without_process_group():
+    op = sharding.RowShardedGemm(256, 32, 16, local_gemm=_cpu_gemm)
+    assert (op.world, op.rank, op.chunks) == (1, 0, 1)
+    A = torch.randn(256, 16)
+    B = torch.randn(16, 32)
+    torch.testing.assert_close(op(A, B, out_dtype=torch.float32), A @ B)
+    with pytest.raises(ValueError):
+        op(torch.randn(100, 16), B)
