@@ -270,7 +270,20 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
   if (const char* e = getenv("SYMPLEX_B200_TILE")) forced = atoi(e);
   g.bn = pick_bn(p.M, p.N, p.batch, st->num_sms, forced);
   debug_desc_override(&g);
-  int rc = launch_gemm_tc(g, stream);
+  if (const char* e = getenv("SYMPLEX_B200_GROUP_M")) g.group_m = atoi(e);
+  // Tile shape by how much work there is: 512x256 per CTA pair when that still fills the machine at least
+  // twice over (least L2 -> SM traffic per flop), 256x256 pairs for mid-size problems, single-CTA tiles
+  // (down to 128x64) when only those give every SM something to do.
+  int mode = 0;  // 0 single CTA, 1 pair 256x256, 2 pair 512x256
+  if (forced == 0 && g.bn == 256 && p.M > 128) {
+    const long long pairs = st->num_sms / 2;
+    const long long nt = (p.N + 255) / 256;
+    if (((p.M + 511) / 512) * nt * p.batch >= 2 * pairs) mode = 2;
+    else if (((p.M + 255) / 256) * nt * p.batch >= pairs) mode = 1;
+  }
+  if (const char* e = getenv("SYMPLEX_B200_PAIR")) mode = atoi(e);
+  if (mode == 2) g.bn = 512;
+  int rc = mode != 0 ? launch_gemm_pair(g, stream) : launch_gemm_tc(g, stream);
   if (rc != SX_OK) {
     if (rc == SX_ERR_INVALID && strncmp(g_err, "cuTensorMap", 11) != 0)
       return fail(rc, "operands are not TMA compatible (alignment) or tile %d invalid", g.bn);

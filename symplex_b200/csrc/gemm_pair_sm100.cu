@@ -1,0 +1,389 @@
+// bf16 GEMM on CTA pairs: tcgen05.mma.cta_group::2, one output tile per cluster of two CTAs.
+//
+// Why pairs: a CTA working alone on a 128x256 tile has to pull 48 KB of operands from L2 for every
+// 4.2 MFLOP, which is more than the L2 -> SM path sustains at full tensor rate (measured: tensor pipe 66 %
+// busy). In a pair each CTA stages only its own rows of A and HALF of the B tile; the paired MMA reads both
+// halves. Two shapes, selected by kMB (128-row blocks of A per CTA):
+//   kMB = 1   256 x 256 per pair, 32 KB / stage, 6 stages, TMEM = two alternating accumulators, so the
+//             epilogue of tile t overlaps the main loop of tile t+1. Used when there are few tiles.
+//   kMB = 2   512 x 256 per pair (256 x 256 per CTA), 48 KB / stage, 4 stages: 25 % less L2 -> SM traffic
+//             per flop. TMEM holds the tile's two row blocks, so tiles cannot be double buffered; instead
+//             the first and last two k-blocks of a tile are issued row-block-major, which lets the epilogue
+//             of block 0 start 8 MMAs early and the next tile start on block 0 while block 1 is still
+//             draining. Eight epilogue warps, all on block 0 first, then all on block 1.
+//
+// Roles per CTA: warp 0 = TMA producer for this CTA's tiles; warp 1 = TMEM allocation and, in the pair's
+// leader (cluster rank 0) only, MMA issue for both CTAs; warps 2.. = epilogue for this CTA's rows.
+// Barrier wiring: both producers' copies complete on the LEADER's full barrier; tcgen05.commit arrives on
+// the empty / accumulator-full barriers of BOTH CTAs; epilogue warps release an accumulator with a
+// (possibly remote) arrive on the leader's accumulator-empty barrier. No TMA multicast is used.
+//
+// All waits are bounded (sm100_ptx.cuh); on a timeout every role unwinds and the kernel reports
+// ST_WAIT_TIMEOUT through the status word.
+#include <cuda_bf16.h>
+
+#include "epilogue.cuh"
+#include "gemm_params.h"
+#include "host_api.h"
+#include "sm100_ptx.cuh"
+
+namespace sx {
+
+template <int kMB>
+struct PairCfg {
+  static constexpr int ROWS = 128 * kMB;   // rows of A / C per CTA
+  static constexpr int BM = 2 * ROWS;      // rows per pair
+  static constexpr int BN = 256;
+  static constexpr int BK = 64;            // 128 bytes of bf16
+  static constexpr int UMMA_K = 16;
+  static constexpr int A_BYTES = ROWS * 128;
+  static constexpr int B_BYTES = 128 * 128;  // this CTA's 128 of the 256 columns
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = kMB == 1 ? 6 : 4;
+  static constexpr int THREADS = 64 + 128 * kMB;
+  static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
+  static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;
+};
+
+struct PairTile {
+  int z, m0, n0;
+};
+
+template <int BM, int BN>
+__device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int t) {
+  const int per = p.m_tiles * p.n_tiles;
+  const int z = t / per;
+  const int r = t - z * per;
+  const int band = p.group_m * p.n_tiles;
+  const int g = r / band;
+  const int first_m = g * p.group_m;
+  const int gsz = min(p.m_tiles - first_m, p.group_m);
+  const int in_band = r - g * band;
+  PairTile c;
+  c.z = z;
+  c.m0 = (first_m + in_band % gsz) * BM;
+  c.n0 = (in_band / gsz) * BN;
+  return c;
+}
+
+template <typename OutT, bool kBmn, int kMB>
+__global__ void __launch_bounds__(PairCfg<kMB>::THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using Cfg = PairCfg<kMB>;
+  constexpr int BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES;
+
+  extern __shared__ uint8_t dyn_smem[];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();  // 0 = leader
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);   // leader: its producer's arrive.expect_tx (bytes of both CTAs)
+      mbar_init(&empty_bar[s], 1);  // one tcgen05.commit per use
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8 * kMB);  // every epilogue warp of both CTAs releases each accumulator
+    }
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(&tmem_base_slot, Cfg::TMEM_COLS);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before_sync();
+  __syncwarp();  // the cluster barrier is warp-aligned: reconverge after the single-thread setup above
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  const int total_tiles = p.batch * p.m_tiles * p.n_tiles;
+  const int nkb = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
+        const PairTile tc = pair_tile<Cfg::BM, BN>(p, t);
+        const int my_m0 = tc.m0 + int(cta_rank) * Cfg::ROWS;
+        const int my_n0 = tc.n0 + int(cta_rank) * 128;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) { ok = false; break; }
+          uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);
+          const uint32_t leader_full = mapa_u32(smem_u32(&full_bar[stage]), 0);
+          tma_load_3d_pair(sa, &tmA, leader_full, kb * BK, my_m0, tc.z);  // ROWS x 64 box
+          if constexpr (kBmn) {
+            tma_load_3d_pair(sb, &tmB, leader_full, my_n0, kb * BK, tc.z);
+            tma_load_3d_pair(sb + BK * 128, &tmB, leader_full, my_n0 + 64, kb * BK, tc.z);
+          } else {
+            tma_load_3d_pair(sb, &tmB, leader_full, kb * BK, my_n0, tc.z);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc(1, false, kBmn, 256, BN);
+      constexpr uint64_t a_hi = make_smem_desc_hi(16, 1024);
+      // B half tile held MN-major: two boxes of [64 k][64 n] (8192 B apart), 8-row k groups 1024 B apart.
+      constexpr uint64_t b_hi = kBmn ? make_smem_desc_hi(BK * 128, 1024) : make_smem_desc_hi(16, 1024);
+      constexpr uint32_t b_kstep = kBmn ? Cfg::UMMA_K * 128 : 32;
+      constexpr int KSTEPS = BK / Cfg::UMMA_K;
+      int stage = 0;
+      uint32_t phase = 0;
+      int slot = 0;            // kMB == 1: accumulator used by this tile
+      uint32_t acc_phase = 0;  // kMB == 1: flips every second tile; kMB == 2: every tile
+      bool ok = true;
+      auto advance = [&](int& s, uint32_t& ph) {
+        if (++s == STAGES) { s = 0; ph ^= 1; }
+      };
+      // four MMAs (one 64-wide k-block) into accumulator `mb` from stage `s`
+      auto issue_block = [&](int mb, int s, uint32_t accumulate) {
+        const uint32_t a_addr = smem_u32(tiles + s * Cfg::STAGE_BYTES) + mb * (128 * 128);
+        const uint32_t b_addr = smem_u32(tiles + s * Cfg::STAGE_BYTES) + Cfg::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < KSTEPS; ++k)
+          umma<2, 0>(tmem_base + mb * BN, smem_desc(a_hi, a_addr + k * 32), smem_desc(b_hi, b_addr + k * b_kstep),
+                     idesc, accumulate | (k != 0 ? 1u : 0u));
+      };
+      for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
+        if constexpr (kMB == 1) {
+          if (!mbar_wait<true>(&acc_empty[slot], acc_phase ^ 1, &abort_flag)) break;
+          tc_fence_after_sync();
+          for (int kb = 0; kb < nkb; ++kb) {
+            if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t a_addr = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
+            const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+            for (int k = 0; k < KSTEPS; ++k)
+              umma<2, 0>(tmem_base + slot * BN, smem_desc(a_hi, a_addr + k * 32),
+                         smem_desc(b_hi, b_addr + k * b_kstep), idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_commit_pair(&empty_bar[stage], 3);  // frees this stage in both CTAs
+            advance(stage, phase);
+          }
+          if (!ok) break;
+          umma_commit_pair(&acc_full[slot], 3);
+          if (++slot == 2) { slot = 0; acc_phase ^= 1; }
+        } else {
+          // The tile's two row blocks share every B stage. In the middle of a tile their MMAs interleave; the
+          // first and the last SKEW k-blocks are issued block-major, so block 0 completes 4*SKEW MMAs before
+          // block 1 and the next tile can start on block 0 while block 1 is still being drained.
+          constexpr int SKEW = 2;
+          const int head_end = min(SKEW, nkb);
+          const int tail_begin = max(head_end, nkb - SKEW);
+          auto group = [&](int g0, int g1) {  // k-blocks [g0, g1) block-major
+            for (int mb = 0; mb < 2 && ok; ++mb) {
+              if (g0 == 0) {
+                if (!mbar_wait<true>(&acc_empty[mb], acc_phase ^ 1, &abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+              }
+              int s = stage;
+              uint32_t ph = phase;
+              for (int kb = g0; kb < g1; ++kb) {
+                if (mb == 0) {
+                  if (!mbar_wait(&full_bar[s], ph, &abort_flag)) { ok = false; break; }
+                  tc_fence_after_sync();
+                }
+                issue_block(mb, s, kb != 0 ? 1u : 0u);
+                if (mb == 1) umma_commit_pair(&empty_bar[s], 3);
+                advance(s, ph);
+              }
+              if (ok && g1 == nkb) umma_commit_pair(&acc_full[mb], 3);
+            }
+            for (int kb = g0; kb < g1; ++kb) advance(stage, phase);
+          };
+          group(0, head_end);
+          for (int kb = head_end; ok && kb < tail_begin; ++kb) {
+            if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t a_addr = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
+            const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+            for (int k = 0; k < KSTEPS; ++k) {
+#pragma unroll
+              for (int mb = 0; mb < 2; ++mb)
+                umma<2, 0>(tmem_base + mb * BN, smem_desc(a_hi, a_addr + mb * (128 * 128) + k * 32),
+                           smem_desc(b_hi, b_addr + k * b_kstep), idesc, 1u);
+            }
+            umma_commit_pair(&empty_bar[stage], 3);
+            advance(stage, phase);
+          }
+          if (ok && tail_begin < nkb) group(tail_begin, nkb);
+          if (!ok) break;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // kMB == 1: four warps, each drains all 256 columns of the tile's accumulator.
+    // kMB == 2: eight warps drain block 0 and then block 1, each taking one half of the columns, so block 0 is
+    //           free again after half the epilogue time.
+    const int half = kMB == 1 ? 0 : (warp - 2) >> 2;
+    constexpr int STRIPS = (BN / 32) / kMB;  // 32-column strips per warp and accumulator
+    const EpilogueCtx<OutT> ep(p);
+    int slot = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
+      const PairTile tc = pair_tile<Cfg::BM, BN>(p, t);
+#pragma unroll 1
+      for (int blk = 0; blk < kMB; ++blk) {
+        if constexpr (kMB == 2) slot = blk;
+        if (!mbar_wait(&acc_full[slot], acc_phase, &abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const int row = tc.m0 + int(cta_rank) * Cfg::ROWS + blk * 128 + q * 32 + lane;
+        const bool row_ok = row < p.M;
+        const long long row_off = (long long)tc.z * p.c_batch_stride + (long long)row * p.ldc;
+#pragma unroll 1
+        for (int c = half * STRIPS; c < (half + 1) * STRIPS; c += 2) {
+          // two 32-column strips per wait: the second load's latency hides behind the first strip's math
+          uint32_t r0[32], r1[32];
+          const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + slot * BN + c * 32;
+          tmem_ld_32x32(taddr, r0);
+          tmem_ld_32x32(taddr + 32, r1);
+          tmem_ld_wait();
+          const int col0 = tc.n0 + c * 32;
+          if (col0 >= p.N) continue;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
+          ep.template strip<true>(v, row_ok, row_off, col0);
+          if (col0 + 32 >= p.N) continue;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
+          ep.template strip<true>(v, row_ok, row_off, col0 + 32);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[slot]), 0));  // leader's barrier
+      }
+      if constexpr (kMB == 1) {
+        if (++slot == 2) { slot = 0; acc_phase ^= 1; }
+      } else {
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // Both CTAs stay resident until every remote barrier signal and paired MMA has landed.
+  tc_fence_before_sync();
+  __syncwarp();  // reconverge the role branches before the warp-aligned cluster barrier
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<2>(tmem_base, Cfg::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && abort_flag != 0 && p.status != nullptr) atomicExch(p.status, int(ST_WAIT_TIMEOUT));
+}
+
+// ------------------------------------------------------------------ host side
+namespace {
+
+template <typename OutT, bool kBmn, int kMB>
+int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int pairs, cudaStream_t stream) {
+  using Cfg = PairCfg<kMB>;
+  auto kern = gemm_pair_kernel<OutT, kBmn, kMB>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::DYN_SMEM) != cudaSuccess)
+    return SX_ERR_DRIVER;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::DYN_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+}
+
+template <typename OutT, bool kBmn>
+int launch_pair_mb(int mb, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int pairs,
+                   cudaStream_t stream) {
+  return mb == 2 ? launch_pair<OutT, kBmn, 2>(tmA, tmB, p, pairs, stream)
+                 : launch_pair<OutT, kBmn, 1>(tmA, tmB, p, pairs, stream);
+}
+
+}  // namespace
+
+// bf16 operands only (a.kind == 0); operand conventions of launch_gemm_tc. a.bn selects the pair tile:
+// 512 -> 512 x 256 (256 rows per CTA), anything else -> 256 x 256.
+int launch_gemm_pair(const TcGemmArgs& a, cudaStream_t stream) {
+  if (a.kind != 0 || a.nseg != 1) return SX_ERR_INVALID;
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return SX_ERR_INVALID;
+  if ((a.lda * 2) % 16 || (a.ldb * 2) % 16 || (a.a_plane_stride * 2) % 16 || (a.b_plane_stride * 2) % 16)
+    return SX_ERR_INVALID;
+  if (reinterpret_cast<uintptr_t>(a.A) % 16 || reinterpret_cast<uintptr_t>(a.B) % 16) return SX_ERR_INVALID;
+  const int mb = a.bn == 512 ? 2 : 1;
+  const int bm = 256 * mb;
+
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[3] = {(uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.za};
+    uint64_t strides[2] = {(uint64_t)a.lda * 2, (uint64_t)a.a_plane_stride * 2};
+    uint32_t box[3] = {64u, (uint32_t)(128 * mb), 1u};
+    int rc = encode_tensor_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.A, dims, strides, box);
+    if (rc != SX_OK) return rc;
+  }
+  if (a.b_mn) {
+    uint64_t dims[3] = {(uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.zb};
+    uint64_t strides[2] = {(uint64_t)a.ldb * 2, (uint64_t)a.b_plane_stride * 2};
+    uint32_t box[3] = {64u, 64u, 1u};
+    int rc = encode_tensor_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.B, dims, strides, box);
+    if (rc != SX_OK) return rc;
+  } else {
+    uint64_t dims[3] = {(uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.zb};
+    uint64_t strides[2] = {(uint64_t)a.ldb * 2, (uint64_t)a.b_plane_stride * 2};
+    uint32_t box[3] = {64u, 128u, 1u};
+    int rc = encode_tensor_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.B, dims, strides, box);
+    if (rc != SX_OK) return rc;
+  }
+
+  GemmParams p{};
+  p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
+  p.batch = a.batch;
+  p.nseg = 1;
+  p.a_planes = 1; p.b_planes = 1;
+  p.C = a.C; p.ldc = a.ldc; p.c_batch_stride = a.c_batch_stride;
+  p.bias = a.bias; p.residual = a.residual;
+  p.alpha = a.alpha; p.beta = a.beta; p.act = a.act;
+  p.status = a.status;
+  p.m_tiles = (int)((a.M + bm - 1) / bm);
+  p.n_tiles = (int)((a.N + 255) / 256);
+  p.group_m = a.group_m > 0 ? a.group_m : (mb == 2 ? 4 : 8);
+  const long long total = (long long)p.batch * p.m_tiles * p.n_tiles;
+  const int max_pairs = a.num_sms / 2;
+  const int pairs = (int)(total < max_pairs ? total : max_pairs);
+  if (a.out_bf16)
+    return a.b_mn ? launch_pair_mb<__nv_bfloat16, true>(mb, tmA, tmB, p, pairs, stream)
+                  : launch_pair_mb<__nv_bfloat16, false>(mb, tmA, tmB, p, pairs, stream);
+  return a.b_mn ? launch_pair_mb<float, true>(mb, tmA, tmB, p, pairs, stream)
+                : launch_pair_mb<float, false>(mb, tmA, tmB, p, pairs, stream);
+}
+
+}  // namespace sx

@@ -13,6 +13,7 @@
 // (rust-engine/src/cuda_backend.rs:300-504, gen_matmul) and its host wrapper (:1344-1385).
 #include <cuda_bf16.h>
 
+#include "epilogue.cuh"
 #include "gemm_params.h"
 #include "host_api.h"
 #include "sm100_ptx.cuh"
@@ -37,51 +38,6 @@ struct TileCfg {
   static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns: power of two <= 512");
 };
-
-__device__ __forceinline__ float tanh_fast(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// Activation over a register strip. The switch sits outside the element loop so that each case is
-// straight-line code the compiler can interleave across the 32 independent elements. All of the
-// smooth activations reduce to one MUFU tanh (rel. error ~2^-11, far inside the bf16-input
-// tolerance): sigmoid(x) = 0.5 + 0.5 tanh(x/2), silu(x) = x sigmoid(x),
-// gelu(x) = 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))).
-__device__ __forceinline__ void apply_activation32(float (&v)[32], int act) {
-  switch (act) {
-    case ACT_RELU:
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
-      break;
-    case ACT_GELU:
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float x = v[j];
-        const float u = x * fmaf(0.0356774081f, x * x, 0.7978845608f);  // sqrt(2/pi) (x + 0.044715 x^3)
-        const float h = 0.5f * x;
-        v[j] = fmaf(h, tanh_fast(u), h);
-      }
-      break;
-    case ACT_SIGMOID:
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = fmaf(0.5f, tanh_fast(0.5f * v[j]), 0.5f);
-      break;
-    case ACT_TANH:
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = tanh_fast(v[j]);
-      break;
-    case ACT_SILU:
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float h = 0.5f * v[j];
-        v[j] = fmaf(h, tanh_fast(h), h);
-      }
-      break;
-    default: break;
-  }
-}
 
 struct TileCoord {
   int z, m0, n0;
@@ -225,11 +181,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    OutT* __restrict__ Cbase = reinterpret_cast<OutT*>(p.C);
-    const OutT* __restrict__ Rbase = reinterpret_cast<const OutT*>(p.residual);
-    constexpr int VEC = 16 / int(sizeof(OutT));
-    const bool vec_ok = (p.ldc % VEC == 0) && (p.c_batch_stride % VEC == 0) &&
-                        (reinterpret_cast<uintptr_t>(p.C) % 16 == 0);
+    const EpilogueCtx<OutT> ep(p);
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
@@ -248,45 +200,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (col0 >= p.N) continue;  // uniform across the warp
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        if (Rbase != nullptr && row_ok) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] += p.beta * float(Rbase[row_off + col0 + j]);
-        }
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] += (col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
-        }
-        apply_activation32(v, p.act);
-        if (row_ok) {
-          OutT* dst = Cbase + row_off + col0;
-          if (vec_ok && col0 + 32 <= p.N) {
-            if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                uint4 pk;
-                pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                *reinterpret_cast<uint4*>(dst + j) = pk;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) dst[j] = OutT(v[j]);
-          }
-        }
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        ep.template strip<true>(v, row_ok, row_off, col0);
       }
       tc_fence_before_sync();
       __syncwarp();

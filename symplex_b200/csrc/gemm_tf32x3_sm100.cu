@@ -19,6 +19,7 @@
 // cuda_matmul, the fused matmul+bias+ReLU kernel (rust-engine/src/x86_emitter.rs:437-770).
 #include <cuda_bf16.h>
 
+#include "epilogue.cuh"
 #include "gemm_params.h"
 #include "host_api.h"
 #include "sm100_ptx.cuh"
@@ -40,38 +41,6 @@ struct X3Cfg {
   static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;
   static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
 };
-
-// Activations of the fp32 path use the accurate libm-style device functions: this path is held to
-// 1e-5 against the CPU reference. The switch is outside the element loop (straight-line cases).
-__device__ __forceinline__ void x3_activation32(float (&v)[32], int act) {
-  switch (act) {
-    case ACT_RELU:
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
-      break;
-    case ACT_GELU:
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float x = v[j];
-        const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-        v[j] = 0.5f * x * (1.0f + tanhf(u));
-      }
-      break;
-    case ACT_SIGMOID:
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = 1.0f / (1.0f + expf(-v[j]));
-      break;
-    case ACT_TANH:
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = tanhf(v[j]);
-      break;
-    case ACT_SILU:
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = v[j] / (1.0f + expf(-v[j]));
-      break;
-    default: break;
-  }
-}
 
 template <typename OutT, int kBN>
 __global__ void __launch_bounds__(192, 1)
@@ -199,11 +168,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   } else {
     // ------------------------------------------------------------ accumulate + epilogue (warps 2..5)
     const int q = warp & 3;
-    OutT* __restrict__ Cbase = reinterpret_cast<OutT*>(p.C);
-    const OutT* __restrict__ Rbase = reinterpret_cast<const OutT*>(p.residual);
-    constexpr int VEC = 16 / int(sizeof(OutT));
-    const bool vec_ok = (p.ldc % VEC == 0) && (p.c_batch_stride % VEC == 0) &&
-                        (reinterpret_cast<uintptr_t>(p.C) % 16 == 0);
+    const EpilogueCtx<OutT> ep(p);
     const uint32_t lane_base = uint32_t(q * 32) << 16;
     int macc = 0, cacc = 0;
     uint32_t mphase = 0, cphase = 0;
@@ -247,52 +212,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (++cacc == 2) { cacc = 0; cphase ^= 1; }
 
       const int row = m0 + q * 32 + lane;
-      if (row < p.M) {
-        const long long row_off = (long long)z * p.c_batch_stride + (long long)row * p.ldc;
+      const bool row_ok = row < p.M;
+      const long long row_off = (long long)z * p.c_batch_stride + (long long)row * p.ldc;
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col0 = n0 + c * 32;
-          if (col0 >= p.N) break;
-          float v[32];
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = sum[c * 32 + j] * p.alpha;
-          if (Rbase != nullptr) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] += p.beta * float(Rbase[row_off + col0 + j]);
-          }
-          if (p.bias != nullptr) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += (col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
-          }
-          x3_activation32(v, p.act);
-          OutT* dst = Cbase + row_off + col0;
-          if (vec_ok && col0 + 32 <= p.N) {
-            if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                uint4 pk;
-                pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                *reinterpret_cast<uint4*>(dst + j) = pk;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) dst[j] = OutT(v[j]);
-          }
-        }
+        for (int j = 0; j < 32; ++j) v[j] = sum[c * 32 + j];
+        ep.template strip<false>(v, row_ok, row_off, col0);
       }
     }
   }

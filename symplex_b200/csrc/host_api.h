@@ -49,6 +49,8 @@ struct TcGemmArgs {
 
 int launch_gemm_tc(const TcGemmArgs& a, cudaStream_t stream);
 int pick_bn(long long M, long long N, int batch, int num_sms, int forced);
+// bf16 GEMM on CTA pairs (256x256 tiles, tcgen05 cta_group::2); operand conventions of launch_gemm_tc, a.bn ignored.
+int launch_gemm_pair(const TcGemmArgs& a, cudaStream_t stream);
 // 3xTF32 GEMM on pre-split operands: A planes [batch][2][M][lda], B planes [batch][2][N][ldb], both K contiguous;
 // a.bn is 128 or 64. Fields kind / b_mn / nseg / *_plane* of TcGemmArgs are ignored.
 int launch_gemm_tf32x3(const TcGemmArgs& a, cudaStream_t stream);
