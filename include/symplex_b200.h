@@ -90,6 +90,21 @@ int symplex_b200_gemm(const symplex_gemm_desc* d, const void* A, const void* B, 
 int symplex_b200_gemm_ws(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
                          const void* residual, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Allocation-free fp32 GEMM, C = A.B (row-major, device pointers, asynchronous on `stream`). No counterpart
+ * in the reference: it exists for callers that cannot allocate GPU memory at the time of the call - processes
+ * whose own allocator already owns all device memory, serving loops with a no-allocation-after-start-up rule,
+ * callers that cannot tolerate the device-wide synchronisation of cudaMalloc/cudaFree. The operand planes of
+ * the 3xTF32 scheme live in a fixed SYMPLEX_B200_NOALLOC_SCRATCH_BYTES array inside the library (resident on
+ * every GPU that loads it, until exit); this function calls no allocating routine.
+ * Limit: 8*(M+N)*round_up(K,4) + 512 <= SYMPLEX_B200_NOALLOC_SCRATCH_BYTES (e.g. 1024^3 is too big by 512 B,
+ * 1024 x 1024 x 1020 fits), else SYMPLEX_ERR_INVALID.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that call
+ * before starting any stream capture. All calls share the one array: calls whose GPU work may overlap race
+ * on it and must be serialised by the caller. Nothing needs clearing between calls. */
+#define SYMPLEX_B200_NOALLOC_SCRATCH_BYTES (16 * 1024 * 1024)
+int symplex_b200_sgemm_noalloc(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                               void* stream);
+
 /* Synchronise `stream` and return the device-side status of the launches since the last call:
  * 0, SYMPLEX_ERR_TIMEOUT or SYMPLEX_ERR_EXEC. */
 int symplex_b200_sync_status(void* stream);

@@ -55,6 +55,7 @@ SIGNATURES = {
     "symplex_b200_gemm": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "symplex_b200_gemm_ws": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_size_t, c_void_p]),
+    "symplex_b200_sgemm_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "symplex_b200_sync_status": (c_int, [c_void_p]),
     "symplex_b200_last_error": (c_char_p, []),
     "symplex_b200_gemm_host": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -25,6 +25,9 @@ static int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+// For the other translation units of the library: record a message for symplex_b200_last_error().
+int set_last_error(int code, const char* msg) { return fail(code, "%s", msg); }
+
 static int cuda_fail(cudaError_t e, const char* what) {
   const int code = (e == cudaErrorMemoryAllocation) ? SX_ERR_OOM
                    : (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver || e == cudaErrorInitializationError)

@@ -55,6 +55,9 @@ int launch_gemm_pair(const TcGemmArgs& a, cudaStream_t stream);
 // a.bn is 128 or 64. Fields kind / b_mn / nseg / *_plane* of TcGemmArgs are ignored.
 int launch_gemm_tf32x3(const TcGemmArgs& a, cudaStream_t stream);
 
+// Records `msg` as the calling thread's last error and returns `code`.
+int set_last_error(int code, const char* msg);
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
 int encode_tensor_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, const uint64_t dims[3],
                          const uint64_t strides_bytes[2], const uint32_t box[3]);

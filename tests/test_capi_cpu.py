@@ -16,6 +16,7 @@ HEADER = os.path.join(ROOT, "include", "symplex_b200.h")
 def _declared_functions():
     text = open(HEADER).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = "\n".join(line for line in text.splitlines() if not line.lstrip().startswith("#"))
     names = re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{}]*\)\s*;", text)
     return sorted(set(n for n in names if n.startswith(("symplex_", "blas_", "cache_tiled_"))))
 
