@@ -48,8 +48,16 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "cfg5_row_sharded_bf16_65536x8192x8192"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
-# summarised under profiles/ (None where no capture of that workload exists).
-NCU_TRAFFIC_BYTES = {}
+# summarised under profiles/ (absent where no capture of that workload exists).
+#   bf16 pair kernel, 8192 x 8192 x 8192: 881.65 MB read + 120.29 MB written (profiles/gemm_pair_kernel_bf16_8192_cube_bias_gelu.md).
+#   Its traffic is proportional to the rows of A per launch (B is re-streamed once per band of 2048 rows, A and C
+#   are touched once), so the row-sharded workload scales that capture by rows / 8192.
+#   fp32 3xTF32 kernel, 4096^3: 1103.19 MB + 62.13 MB (profiles/gemm_tf32x3_kernel_fp32_4096_cube.md).
+NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192 = 881.65e6 + 120.29e6
+NCU_TRAFFIC_BYTES = {
+    "headline_bf16_8192_cube_bias_gelu": NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192,
+    "cfg2_fp32_4096_cube_colmajor_b": 1103.19e6 + 62.13e6,
+}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -181,7 +189,7 @@ def cpu_rows_for(w, seconds=3.0, gflops_guess=5.0):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="symplex_b200", choices=["symplex_b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
@@ -317,15 +325,18 @@ def main():
             sx.gemm(Ak, Bm, bias=bias, activation=w["act"], out=Ck, b_layout=b_layout)
     else:
         kernel_only = step
-    kernel_only()
-    torch.cuda.synchronize()
-    kreps = max(3, min(args.steps, 10))
-    k0.record()
-    for _ in range(kreps):
+    if sharded and op.world == 1:
+        kernel_ms = elapsed_ms / args.steps  # one step is exactly one launch of the GEMM kernel
+    else:
         kernel_only()
-    k1.record()
-    torch.cuda.synchronize()
-    kernel_ms = k0.elapsed_time(k1) / kreps
+        torch.cuda.synchronize()
+        kreps = max(3, min(args.steps, 10))
+        k0.record()
+        for _ in range(kreps):
+            kernel_only()
+        k1.record()
+        torch.cuda.synchronize()
+        kernel_ms = k0.elapsed_time(k1) / kreps
     clocks = sampler.stop() if sampler else None
 
     t = torch.tensor([elapsed_ms, float(launches)], device=dev, dtype=torch.float64)
@@ -352,6 +363,9 @@ def main():
         return 0
 
     achieved = launches_per_step_flops / (kernel_ms * 1e-3) / 1e12
+    traffic = NCU_TRAFFIC_BYTES.get(args.workload)
+    if sharded:  # rows of A per launch, scaled from the 8192-row capture of the same kernel
+        traffic = NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192 * (M / args.gpus / config["chunks"]) / 8192.0
     tensor_bound = w["dt"] == "bf16" or w["K"] >= 1024
     if w["dt"] == "bf16":
         peak = float(peaks["bf16_tflops"])
@@ -360,13 +374,13 @@ def main():
         peak = float(peaks["bf16_tflops"]) / 6.0
         peak_desc = f"derived 3xTF32 ceiling = bf16 burst / 2 / 3, {peak_note}"
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "kernel_ms": kernel_ms, "peak_kind": peak_desc,
+                "traffic": traffic, "kernel_ms": kernel_ms, "peak_kind": peak_desc,
                 "flops_per_launch": launches_per_step_flops}
     if not tensor_bound:
         algo_bytes = ((M * K + K * N) * 4 + M * N * 4) * batch
         ach = algo_bytes / (kernel_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "achieved": ach, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
-                    "frac": ach / float(peaks["hbm_gbs"]), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                    "frac": ach / float(peaks["hbm_gbs"]), "traffic": traffic,
                     "kernel_ms": kernel_ms, "peak_kind": f"HBM copy, {peak_note}", "bytes_per_launch": algo_bytes,
                     "note": "kernel_ms covers the split pre-pass and the GEMM of one step"}
 

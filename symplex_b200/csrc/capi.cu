@@ -137,6 +137,7 @@ struct Plan {
   bool a_prep, b_prep;
   long long a_ldp, b_ldp;  // leading dimension of the prepared copies
   size_t a_off, b_off, total;
+  bool b_ready = false;  // the prepared copy of B is already in the scratch (row-chunked host path)
 };
 
 static int make_plan(const symplex_gemm_desc* d, const void* A, const void* B, Plan* p) {
@@ -227,14 +228,17 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
     int rc = launch_split_tf32(static_cast<const float*>(A), p.lda, p.a_bs, Ap, (int)p.M, (int)p.K, (int)p.a_ldp,
                                p.batch, stream);
     if (rc != SX_OK) return fail(rc, "split_tf32(A) launch failed");
-    if (p.b_col)
-      rc = launch_split_tf32(static_cast<const float*>(B), p.ldb, p.b_bs, Bp, (int)p.N, (int)p.K, (int)p.b_ldp,
-                             p.batch, stream);
-    else
-      rc = launch_split_tf32_transpose(static_cast<const float*>(B), p.ldb, p.b_bs, Bp, (int)p.K, (int)p.N,
-                                       (int)p.b_ldp, p.batch, stream);
-    if (rc != SX_OK) return fail(rc, "split_tf32(B) launch failed");
-    g_launches += 2;
+    ++g_launches;
+    if (!p.b_ready) {
+      if (p.b_col)
+        rc = launch_split_tf32(static_cast<const float*>(B), p.ldb, p.b_bs, Bp, (int)p.N, (int)p.K, (int)p.b_ldp,
+                               p.batch, stream);
+      else
+        rc = launch_split_tf32_transpose(static_cast<const float*>(B), p.ldb, p.b_bs, Bp, (int)p.K, (int)p.N,
+                                         (int)p.b_ldp, p.batch, stream);
+      if (rc != SX_OK) return fail(rc, "split_tf32(B) launch failed");
+      ++g_launches;
+    }
     g.A = Ap; g.lda = p.a_ldp; g.a_plane_stride = p.M * p.a_ldp;
     g.B = Bp; g.ldb = p.b_ldp; g.b_plane_stride = p.N * p.b_ldp;
     int forced = d->tile_n;
@@ -257,9 +261,12 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
       Ause = w + p.a_off; lda = p.a_ldp; a_bs = p.M * p.a_ldp;
     }
     if (p.b_prep) {
-      int rc = launch_repack_16(B, p.ldb, p.b_bs, w + p.b_off, p.b_ldp, (int)p.b_rows, (int)p.b_cols, p.batch, stream);
-      if (rc != SX_OK) return fail(rc, "repack(B) launch failed");
-      ++g_launches;
+      if (!p.b_ready) {
+        int rc = launch_repack_16(B, p.ldb, p.b_bs, w + p.b_off, p.b_ldp, (int)p.b_rows, (int)p.b_cols, p.batch,
+                                  stream);
+        if (rc != SX_OK) return fail(rc, "repack(B) launch failed");
+        ++g_launches;
+      }
       Buse = w + p.b_off; ldb = p.b_ldp; b_bs = p.b_rows * p.b_ldp;
     }
     g.kind = 0;
@@ -299,7 +306,10 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
 
 // ------------------------------------------------------------------ host-pointer path
 struct HostCtx {
-  cudaStream_t stream = nullptr;
+  cudaStream_t stream = nullptr;                  // compute (and, for small problems, everything)
+  cudaStream_t h2d = nullptr, d2h = nullptr;      // copy streams of the row-chunked pipeline
+  cudaEvent_t ev_in[64] = {}, ev_out[64] = {};    // chunk c: inputs landed / result ready
+  bool pipeline_ready = false;
   void* buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // A, B, C, bias, residual
   size_t cap[5] = {0, 0, 0, 0, 0};
   int dev = -1;
@@ -353,6 +363,75 @@ static int gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, v
   if ((rc = host_buf(0, a_bytes, &dA)) != SX_OK) return rc;
   if ((rc = host_buf(1, b_bytes, &dB)) != SX_OK) return rc;
   if ((rc = host_buf(2, c_bytes, &dC)) != SX_OK) return rc;
+  // Large single problems: split the rows of A / C into chunks and run a three-stream pipeline, so the
+  // host -> device copy of chunk c+1, the GEMM of chunk c and the device -> host copy of chunk c-1 overlap.
+  // Rows of C are independent, so the result is the one the single-shot path produces.
+  {
+    const size_t row_bytes = (size_t)p.K * in_elt + (size_t)p.N * out_elt;
+    size_t chunk_mb = 96;  // bytes of A + C moved per chunk: ~2 ms of PCIe time, several waves of GEMM tiles
+    if (const char* e = getenv("SYMPLEX_B200_PIPELINE_MB")) chunk_mb = (size_t)atoi(e) > 0 ? (size_t)atoi(e) : 1;
+    long long chunk_rows = (long long)((chunk_mb << 20) / row_bytes) / 512 * 512;
+    if (chunk_rows < 2048) chunk_rows = 2048;
+    if (chunk_rows * 64 < p.M) chunk_rows = ((p.M + 63) / 64 + 511) / 512 * 512;  // at most 64 chunks
+    const long long nchunks = (p.M + chunk_rows - 1) / chunk_rows;
+    const bool dense = p.lda == p.K && p.ldc == p.N;
+    if (p.batch == 1 && dense && !residual && nchunks >= 3 && nchunks <= 64 && getenv("SYMPLEX_B200_NO_PIPELINE") == nullptr) {
+      if (!h.pipeline_ready) {
+        SX_CUDA(cudaStreamCreateWithFlags(&h.h2d, cudaStreamNonBlocking));
+        SX_CUDA(cudaStreamCreateWithFlags(&h.d2h, cudaStreamNonBlocking));
+        for (int i = 0; i < 64; ++i) {
+          SX_CUDA(cudaEventCreateWithFlags(&h.ev_in[i], cudaEventDisableTiming));
+          SX_CUDA(cudaEventCreateWithFlags(&h.ev_out[i], cudaEventDisableTiming));
+        }
+        h.pipeline_ready = true;
+      }
+      void* ws = nullptr;
+      if (p.total && (rc = pool_scratch(st, p.total, &ws)) != SX_OK) return rc;
+      SX_CUDA(cudaMemcpyAsync(dB, B, b_bytes, cudaMemcpyHostToDevice, h.h2d));
+      if (bias) {
+        if ((rc = host_buf(3, (size_t)p.N * 4, &dbias)) != SX_OK) return rc;
+        SX_CUDA(cudaMemcpyAsync(dbias, bias, (size_t)p.N * 4, cudaMemcpyHostToDevice, h.h2d));
+      }
+      for (long long c = 0; c < nchunks; ++c) {
+        const long long r0 = c * chunk_rows;
+        const long long rows = (p.M - r0) < chunk_rows ? (p.M - r0) : chunk_rows;
+        const uint8_t* hA = static_cast<const uint8_t*>(A) + (size_t)r0 * p.K * in_elt;
+        uint8_t* dAc = static_cast<uint8_t*>(dA) + (size_t)r0 * p.K * in_elt;
+        uint8_t* dCc = static_cast<uint8_t*>(dC) + (size_t)r0 * p.N * out_elt;
+        SX_CUDA(cudaMemcpyAsync(dAc, hA, (size_t)rows * p.K * in_elt, cudaMemcpyHostToDevice, h.h2d));
+        SX_CUDA(cudaEventRecord(h.ev_in[c], h.h2d));
+        SX_CUDA(cudaStreamWaitEvent(h.stream, h.ev_in[c], 0));
+        Plan pc = p;
+        pc.M = rows;
+        pc.a_bs = rows * p.lda;
+        pc.c_bs = rows * p.ldc;
+        pc.b_ready = c > 0;
+        // this chunk's slice of the A scratch region (fp32 planes: 2 x rows x a_ldp floats; padded bf16: rows x a_ldp)
+        pc.a_off = p.a_off + (size_t)r0 * p.a_ldp * (p.f32_in ? 8 : 2);
+        rc = run_gemm(d, pc, dAc, dB, dCc, static_cast<const float*>(dbias), nullptr, ws, st, h.stream);
+        if (rc != SX_OK) {
+          cudaStreamSynchronize(h.h2d);
+          cudaStreamSynchronize(h.stream);
+          cudaStreamSynchronize(h.d2h);
+          return rc;
+        }
+        SX_CUDA(cudaEventRecord(h.ev_out[c], h.stream));
+        SX_CUDA(cudaStreamWaitEvent(h.d2h, h.ev_out[c], 0));
+        SX_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(C) + (size_t)r0 * p.N * out_elt, dCc, (size_t)rows * p.N * out_elt,
+                                cudaMemcpyDeviceToHost, h.d2h));
+      }
+      int status = 0;
+      SX_CUDA(cudaMemcpyAsync(&status, st->status, sizeof(int), cudaMemcpyDeviceToHost, h.d2h));
+      SX_CUDA(cudaStreamSynchronize(h.d2h));
+      SX_CUDA(cudaStreamSynchronize(h.stream));
+      if (status != 0) {
+        cudaMemsetAsync(st->status, 0, sizeof(int), h.stream);
+        cudaStreamSynchronize(h.stream);
+        return fail(SX_ERR_TIMEOUT, "device-side wait timed out (status %d); the output is not valid", status);
+      }
+      return SX_OK;
+    }
+  }
   SX_CUDA(cudaMemcpyAsync(dA, A, a_bytes, cudaMemcpyHostToDevice, h.stream));
   SX_CUDA(cudaMemcpyAsync(dB, B, b_bytes, cudaMemcpyHostToDevice, h.stream));
   if (bias) {

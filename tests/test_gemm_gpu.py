@@ -353,3 +353,42 @@ def test_strided_host_output(lib, oracle):
     sx.gemm_host(d, A.ctypes.data, B.ctypes.data, Cbuf.ctypes.data)
     assert np.all(Cbuf[:, N:] == 9.0)
     assert rel_frobenius(Cbuf[:, :N], oracle.jit_parallel_matmul(A, B)) <= TOL_F32
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_host_path_row_chunked_pipeline(lib, oracle, dtype, monkeypatch):
+    """Large host-buffer problems are copied and computed in row chunks on three streams; the result must be the
+    one the single-shot path gives (rows are independent)."""
+    rng = np.random.default_rng(31)
+    M, N, K = 8192 + 100, 384, 512
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    if dtype == "bf16":
+        A_h = torch.from_numpy(A).to(torch.bfloat16)
+        B_h = torch.from_numpy(B).to(torch.bfloat16)
+        C_h = torch.empty(M, N, dtype=torch.bfloat16)
+        d = sx.make_desc(M, N, K, sx.DT_BF16, sx.DT_BF16, activation="relu")
+    else:
+        A_h, B_h = torch.from_numpy(A), torch.from_numpy(B)
+        C_h = torch.empty(M, N, dtype=torch.float32)
+        d = sx.make_desc(M, N, K, activation="relu")
+    results = []
+    for env in ({"SYMPLEX_B200_PIPELINE_MB": "1"}, {"SYMPLEX_B200_NO_PIPELINE": "1"}):
+        for k, v in env.items():
+            monkeypatch.setenv(k, v)
+        C_h.fill_(float("nan"))
+        before = sx.launch_count()
+        sx.gemm_host(d, A_h.data_ptr(), B_h.data_ptr(), C_h.data_ptr(), bias.ctypes.data)
+        results.append((C_h.float().numpy().copy(), sx.launch_count() - before))
+        for k in env:
+            monkeypatch.delenv(k)
+    (chunked, n_chunked), (single, n_single) = results
+    assert n_chunked >= 4 * n_single - 4, "the chunked path should have launched one GEMM per row chunk"
+    np.testing.assert_array_equal(chunked, single)
+    rows = np.sort(rng.choice(M, 300, replace=False))
+    Ar = oracle.bf16_round(A) if dtype == "bf16" else A
+    Br = oracle.bf16_round(B) if dtype == "bf16" else B
+    ref = oracle.epilogue(oracle.matmul_rows(Ar, Br, rows), bias=bias, act=_capi.ACT_RELU)
+    tol = TOL_BF16 if dtype == "bf16" else TOL_F32
+    assert rel_frobenius(chunked[rows], oracle.bf16_round(ref) if dtype == "bf16" else ref) <= tol
