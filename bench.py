@@ -193,7 +193,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="symplex_b200", choices=["symplex_b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
-    ap.add_argument("--chunks", type=int, default=None, help="row chunks per rank for the all-gather pipeline")
+    ap.add_argument("--chunks", type=int, default=None, help="row chunks per rank for the NCCL all-gather pipeline")
+    ap.add_argument("--exchange", default=None, choices=["peer_store", "nccl"],
+                    help="how C is all-gathered at N > 1 (default: fused peer stores from the GEMM epilogue)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -256,12 +258,16 @@ def main():
 
     sharded = w["sharded"]
     if sharded:
-        op = RowShardedGemm(M, N, K, chunks=args.chunks, activation=w["act"], b_layout=b_layout)
+        op = RowShardedGemm(M, N, K, chunks=args.chunks, activation=w["act"], b_layout=b_layout,
+                            exchange=args.exchange)
         m_loc = M // op.world
         ga = torch.Generator(device=dev).manual_seed(100 + rank)
         A = (torch.randn(m_loc, K, device=dev, generator=ga) * scale).to(tdt)
-        C = torch.empty(M, N, device=dev, dtype=odt)
+        peer_store = op.exchange == "peer_store" and op.world > 1
+        C = op.output_buffer(odt, dev) if peer_store else torch.empty(M, N, device=dev, dtype=odt)
         config["chunks"] = op.chunks
+        config["exchange"] = ("fused into the GEMM epilogue: TMA stores to every peer's C over NVLink" if peer_store
+                              else ("NCCL all_gather_into_tensor per chunk" if op.world > 1 else "none (1 GPU)"))
 
         def step():
             op(A, Bm, bias=bias, out=C)
@@ -427,8 +433,7 @@ def run_e2e(args, w, sx, lib, torch, dist, dev, rank, world, Bm, bias, b_layout,
     else:
         dA = torch.empty(hA.shape, device=dev, dtype=tdt)
         dB = torch.empty(hB.shape, device=dev, dtype=tdt)
-        dC = torch.empty(M, N, device=dev, dtype=odt)
-        idx = op.local_row_index().to(dev)
+        dC = op.output_buffer(odt, dev) if op.exchange == "peer_store" else torch.empty(M, N, device=dev, dtype=odt)
 
         def host_step():
             dA.copy_(hA, non_blocking=True)

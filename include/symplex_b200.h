@@ -85,6 +85,16 @@ size_t symplex_b200_gemm_workspace_bytes(const symplex_gemm_desc* d);
 int symplex_b200_gemm(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
                       const void* residual, void* stream);
 
+/* symplex_b200_gemm that additionally writes every tile of C, from inside the GEMM kernel, to the same offset of
+ * `n_peers` (<= 7) other buffers: the C of other GPUs of the box, mapped into this process (CUDA IPC / symmetric
+ * memory), written over NVLink by TMA stores issued from the epilogue. This is the all-gather of a row-sharded
+ * product fused into the GEMM - no separate collective. bf16 inputs; C and every peer buffer need 16-byte
+ * aligned rows. The caller orders the GPUs (all ranks done before C is read, and before the next call overwrites
+ * it). The reference only has a planner that emits collective calls as text
+ * (include/symplex/distributed/nccl_bridge.h:91-98); this is the executed counterpart. */
+int symplex_b200_gemm_peers(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
+                            const void* residual, const void* const* peer_C, int32_t n_peers, void* stream);
+
 /* Same, with caller-provided scratch of at least symplex_b200_gemm_workspace_bytes(d) bytes
  * (256-byte aligned device memory); never allocates. */
 int symplex_b200_gemm_ws(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,

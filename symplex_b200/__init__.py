@@ -127,12 +127,16 @@ def gemm_host(desc: GemmDesc, A_ptr: int, B_ptr: int, C_ptr: int, bias_ptr: int 
 
 
 def gemm(A, B, *, bias=None, residual=None, activation=None, alpha=1.0, beta=0.0, out=None, out_dtype=None,
-         b_layout=ROW_MAJOR, tile_n=0, stream=None):
+         b_layout=ROW_MAJOR, tile_n=0, stream=None, peer_outputs=None):
     """Fused GEMM on CUDA tensors: ``act(alpha * A @ B + beta * residual + bias)``.
 
     ``A`` is ``[M,K]`` or ``[batch,M,K]``; ``B`` is ``[K,N]`` (``ROW_MAJOR``) or stored as ``[N,K]``
     (``COL_MAJOR``), with the same optional batch dimension. Inputs are both ``torch.float32`` (3xTF32
     path) or both ``torch.bfloat16``. Asynchronous on ``stream`` (default: torch's current stream).
+
+    ``peer_outputs``: device addresses (ints) of up to 7 more buffers with the layout of ``out`` - typically
+    the same region of other GPUs' C, mapped into this process - that receive every output tile as well,
+    written from inside the kernel (``symplex_b200_gemm_peers``). bf16 inputs only.
     """
     import torch
 
@@ -180,9 +184,16 @@ def gemm(A, B, *, bias=None, residual=None, activation=None, alpha=1.0, beta=0.0
         raise ValueError("K == 0 is not supported")
     s = stream if stream is not None else torch.cuda.current_stream(A.device).cuda_stream
     with torch.cuda.device(A.device):
-        rc = _capi.load().symplex_b200_gemm(ctypes.byref(d), A.data_ptr(), B.data_ptr(), out.data_ptr(),
-                                            bias.data_ptr() if bias is not None else None,
-                                            residual.data_ptr() if residual is not None else None, s)
+        if peer_outputs:
+            arr = (ctypes.c_void_p * len(peer_outputs))(*[int(x) for x in peer_outputs])
+            rc = _capi.load().symplex_b200_gemm_peers(ctypes.byref(d), A.data_ptr(), B.data_ptr(), out.data_ptr(),
+                                                      bias.data_ptr() if bias is not None else None,
+                                                      residual.data_ptr() if residual is not None else None,
+                                                      arr, len(peer_outputs), s)
+        else:
+            rc = _capi.load().symplex_b200_gemm(ctypes.byref(d), A.data_ptr(), B.data_ptr(), out.data_ptr(),
+                                                bias.data_ptr() if bias is not None else None,
+                                                residual.data_ptr() if residual is not None else None, s)
     _capi.check(rc)
     return out
 

@@ -53,6 +53,8 @@ SIGNATURES = {
     "symplex_b200_gemm_desc_init": (None, [ctypes.POINTER(GemmDesc), c_int64, c_int64, c_int64, c_int32, c_int32]),
     "symplex_b200_gemm_workspace_bytes": (c_size_t, [ctypes.POINTER(GemmDesc)]),
     "symplex_b200_gemm": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "symplex_b200_gemm_peers": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        ctypes.POINTER(c_void_p), c_int32, c_void_p]),
     "symplex_b200_gemm_ws": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_size_t, c_void_p]),
     "symplex_b200_sgemm_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),

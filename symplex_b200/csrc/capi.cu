@@ -207,7 +207,8 @@ static void debug_desc_override(TcGemmArgs* g) {
 }
 
 static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, const void* B, void* C,
-                    const float* bias, const void* residual, void* ws, DeviceState* st, cudaStream_t stream) {
+                    const float* bias, const void* residual, void* ws, DeviceState* st, cudaStream_t stream,
+                    const void* const* peer_C = nullptr, int n_peers = 0) {
   if (p.M == 0 || p.N == 0 || p.batch == 0) return SX_OK;  // nothing to write
   if (p.K == 0) return fail(SX_ERR_INVALID, "K == 0 is not supported by the device entry points");
   uint8_t* w = static_cast<uint8_t*>(ws);
@@ -221,6 +222,8 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
   g.status = st->status;
   g.num_sms = st->num_sms;
   g.K = p.K;
+  if (n_peers > 0 && p.f32_in)
+    return fail(SX_ERR_INVALID, "peer destinations are supported for bf16 inputs only");
   if (p.f32_in) {
     // fp32: both operands are rewritten as {hi, lo} tf32 planes with K contiguous.
     float* Ap = reinterpret_cast<float*>(w + p.a_off);
@@ -292,11 +295,20 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
     else if (((p.M + 255) / 256) * nt * p.batch >= pairs) mode = 1;
   }
   if (const char* e = getenv("SYMPLEX_B200_PAIR")) mode = atoi(e);
+  g.tma_store = 1;
+  if (const char* e = getenv("SYMPLEX_B200_TMA_STORE")) g.tma_store = atoi(e);
+  if (n_peers > 0) {
+    if (n_peers > 7) return fail(SX_ERR_INVALID, "at most 7 peer destinations");
+    if (mode == 0) mode = 1;  // only the pair kernels carry the peer-store epilogue
+    g.n_peers = n_peers;
+    for (int i = 0; i < n_peers; ++i) g.peer_C[i] = peer_C[i];
+  }
   if (mode == 2) g.bn = 512;
   int rc = mode != 0 ? launch_gemm_pair(g, stream) : launch_gemm_tc(g, stream);
   if (rc != SX_OK) {
     if (rc == SX_ERR_INVALID && strncmp(g_err, "cuTensorMap", 11) != 0)
-      return fail(rc, "operands are not TMA compatible (alignment) or tile %d invalid", g.bn);
+      return fail(rc, "operands%s are not TMA compatible (16-byte alignment) or tile %d invalid",
+                  n_peers > 0 ? " or peer buffers" : "", g.bn);
     if (rc == SX_ERR_EXEC) return fail(rc, "GEMM kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     return rc;
   }
@@ -512,6 +524,21 @@ int symplex_b200_gemm(const symplex_gemm_desc* d, const void* A, const void* B, 
   void* ws = nullptr;
   if (p.total && (rc = pool_scratch(st, p.total, &ws)) != SX_OK) return rc;
   return run_gemm(d, p, A, B, C, bias, residual, ws, st, static_cast<cudaStream_t>(stream));
+}
+
+int symplex_b200_gemm_peers(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
+                            const void* residual, const void* const* peer_C, int32_t n_peers, void* stream) {
+  Plan p;
+  int rc = make_plan(d, A, B, &p);
+  if (rc != SX_OK) return rc;
+  if (n_peers < 0 || (n_peers > 0 && peer_C == nullptr)) return fail(SX_ERR_INVALID, "bad peer list");
+  if (p.M == 0 || p.N == 0 || p.batch == 0) return SX_OK;
+  if (!A || !B || !C) return fail(SX_ERR_INVALID, "null matrix pointer");
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != SX_OK) return rc;
+  void* ws = nullptr;
+  if (p.total && (rc = pool_scratch(st, p.total, &ws)) != SX_OK) return rc;
+  return run_gemm(d, p, A, B, C, bias, residual, ws, st, static_cast<cudaStream_t>(stream), peer_C, n_peers);
 }
 
 int symplex_b200_gemm_ws(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,

@@ -90,10 +90,11 @@ struct EpilogueCtx {
     bias_vec = reinterpret_cast<uintptr_t>(p.bias) % 16 == 0;  // tile columns start at multiples of 32
   }
 
-  // v: raw accumulators of columns [col0, col0 + 32) of one row; row_off: element offset of that row in C.
-  // col0 < N is required; all lanes of a warp must agree on col0.
+  // v: raw accumulators of columns [col0, col0 + 32) of one row, replaced by the final values
+  // act(alpha v + beta R + bias). row_off: element offset of that row in C. col0 < N is required and all
+  // lanes of a warp must agree on col0.
   template <bool kFast>
-  __device__ __forceinline__ void strip(float (&v)[32], bool row_ok, long long row_off, int col0) const {
+  __device__ __forceinline__ void math(float (&v)[32], bool row_ok, long long row_off, int col0) const {
     if (alpha != 1.0f) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] *= alpha;
@@ -118,6 +119,24 @@ struct EpilogueCtx {
       }
     }
     activation32<kFast>(v, act);
+  }
+
+  // 8 consecutive values -> one 16-byte chunk of the output type (fp32: two chunks via pack4).
+  static __device__ __forceinline__ uint4 pack8_bf16(const float* v) {
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]);
+    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]);
+    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[6], v[7]);
+    uint4 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+    pk.z = *reinterpret_cast<uint32_t*>(&h2);
+    pk.w = *reinterpret_cast<uint32_t*>(&h3);
+    return pk;
+  }
+
+  // Final values of one strip straight to global memory.
+  __device__ __forceinline__ void store(const float (&v)[32], bool row_ok, long long row_off, int col0) const {
     if (!row_ok) return;
     OutT* dst = C + row_off + col0;
     if (vec_ok && col0 + 32 <= N) {
@@ -127,23 +146,36 @@ struct EpilogueCtx {
           *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-          __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-          __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-          __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-          uint4 pk;
-          pk.x = *reinterpret_cast<uint32_t*>(&h0);
-          pk.y = *reinterpret_cast<uint32_t*>(&h1);
-          pk.z = *reinterpret_cast<uint32_t*>(&h2);
-          pk.w = *reinterpret_cast<uint32_t*>(&h3);
-          *reinterpret_cast<uint4*>(dst + j) = pk;
-        }
+        for (int j = 0; j < 32; j += 8) *reinterpret_cast<uint4*>(dst + j) = pack8_bf16(v + j);
       }
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
         if (col0 + j < N) dst[j] = OutT(v[j]);
+    }
+  }
+
+  template <bool kFast>
+  __device__ __forceinline__ void strip(float (&v)[32], bool row_ok, long long row_off, int col0) const {
+    math<kFast>(v, row_ok, row_off, col0);
+    store(v, row_ok, row_off, col0);
+  }
+
+  // Final values of one strip into a 128-byte-swizzled staging tile of 32 rows x 128 bytes (the layout a
+  // SWIZZLE_128B tensor map expects): this lane's row, 16-byte chunk c stored at chunk position c ^ (row & 7).
+  // `first_chunk` is where this strip starts inside the 128-byte row (bf16: 0 or 4; fp32: 0).
+  __device__ __forceinline__ void stage(const float (&v)[32], uint8_t* tile, int lane, int first_chunk) const {
+    uint8_t* row = tile + lane * 128;
+    const int sw = lane & 7;
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<float4*>(row + (((first_chunk + c) ^ sw) << 4)) =
+            make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4*>(row + (((first_chunk + c) ^ sw) << 4)) = pack8_bf16(v + 8 * c);
     }
   }
 };

@@ -42,7 +42,13 @@ struct PairCfg {
   static constexpr int STAGES = kMB == 1 ? 6 : 4;
   static constexpr int THREADS = 64 + 128 * kMB;
   static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
-  static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;
+  static constexpr int EPI_WARPS = 4 * kMB;
+  static constexpr int STAGING_BYTES = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes, 128B-swizzled
+  static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + EPI_WARPS * STAGING_BYTES + 1024;
+};
+
+struct DstMaps {
+  CUtensorMap m[MAX_DST];
 };
 
 struct PairTile {
@@ -69,7 +75,7 @@ __device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int t) {
 template <typename OutT, bool kBmn, int kMB>
 __global__ void __launch_bounds__(PairCfg<kMB>::THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmParams p) {
+                 const __grid_constant__ DstMaps dst, const GemmParams p) {
   using Cfg = PairCfg<kMB>;
   constexpr int BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES;
 
@@ -243,6 +249,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int half = kMB == 1 ? 0 : (warp - 2) >> 2;
     constexpr int STRIPS = (BN / 32) / kMB;  // 32-column strips per warp and accumulator
     const EpilogueCtx<OutT> ep(p);
+    uint8_t* staging = tiles + STAGES * Cfg::STAGE_BYTES + (warp - 2) * Cfg::STAGING_BYTES;
     int slot = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -253,7 +260,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if constexpr (kMB == 2) slot = blk;
         if (!mbar_wait(&acc_full[slot], acc_phase, &abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const int row = tc.m0 + int(cta_rank) * Cfg::ROWS + blk * 128 + q * 32 + lane;
+        const int row0 = tc.m0 + int(cta_rank) * Cfg::ROWS + blk * 128 + q * 32;  // this warp's first row
+        const int row = row0 + lane;
         const bool row_ok = row < p.M;
         const long long row_off = (long long)tc.z * p.c_batch_stride + (long long)row * p.ldc;
 #pragma unroll 1
@@ -266,14 +274,53 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_wait();
           const int col0 = tc.n0 + c * 32;
           if (col0 >= p.N) continue;
+          const bool second = col0 + 32 < p.N;
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
-          ep.template strip<true>(v, row_ok, row_off, col0);
-          if (col0 + 32 >= p.N) continue;
+          ep.template math<true>(v, row_ok, row_off, col0);
+          if (p.n_dst == 0) {
+            ep.store(v, row_ok, row_off, col0);
+            if (!second) continue;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
-          ep.template strip<true>(v, row_ok, row_off, col0 + 32);
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
+            ep.template strip<true>(v, row_ok, row_off, col0 + 32);
+          } else {
+            // Staged path: the warp's 32 x 128-byte block goes to shared memory and one lane hands it to the
+            // TMA unit once per destination (local C, then each peer GPU's C). bf16: both strips form one
+            // block; fp32: one block per strip.
+            if (lane == 0) bulk_wait_group_read<0>();  // the previous block has left the staging tile
+            __syncwarp();
+            ep.stage(v, staging, lane, 0);
+            if constexpr (sizeof(OutT) == 4) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                for (int d = 0; d < p.n_dst; ++d) tma_store_3d(&dst.m[d], staging, col0, row0, tc.z);
+                bulk_commit_group();
+              }
+              if (!second) continue;
+            }
+            if (second) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
+              ep.template math<true>(v, row_ok, row_off, col0 + 32);
+              if constexpr (sizeof(OutT) == 4) {
+                if (lane == 0) bulk_wait_group_read<0>();
+                __syncwarp();
+                ep.stage(v, staging, lane, 0);
+              } else {
+                ep.stage(v, staging, lane, 4);
+              }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const int cstore = sizeof(OutT) == 4 ? col0 + 32 : col0;
+              for (int d = 0; d < p.n_dst; ++d) tma_store_3d(&dst.m[d], staging, cstore, row0, tc.z);
+              bulk_commit_group();
+            }
+          }
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -285,6 +332,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         acc_phase ^= 1;
       }
     }
+    if (p.n_dst != 0 && lane == 0) bulk_wait_group<0>();  // every store of this warp has been performed
   }
 
   // Both CTAs stay resident until every remote barrier signal and paired MMA has landed.
@@ -302,7 +350,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 namespace {
 
 template <typename OutT, bool kBmn, int kMB>
-int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int pairs, cudaStream_t stream) {
+int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const DstMaps& dst, const GemmParams& p, int pairs,
+                cudaStream_t stream) {
   using Cfg = PairCfg<kMB>;
   auto kern = gemm_pair_kernel<OutT, kBmn, kMB>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::DYN_SMEM) != cudaSuccess)
@@ -319,14 +368,14 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, dst, p) == cudaSuccess ? SX_OK : SX_ERR_EXEC;
 }
 
 template <typename OutT, bool kBmn>
-int launch_pair_mb(int mb, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int pairs,
-                   cudaStream_t stream) {
-  return mb == 2 ? launch_pair<OutT, kBmn, 2>(tmA, tmB, p, pairs, stream)
-                 : launch_pair<OutT, kBmn, 1>(tmA, tmB, p, pairs, stream);
+int launch_pair_mb(int mb, const CUtensorMap& tmA, const CUtensorMap& tmB, const DstMaps& dst, const GemmParams& p,
+                   int pairs, cudaStream_t stream) {
+  return mb == 2 ? launch_pair<OutT, kBmn, 2>(tmA, tmB, dst, p, pairs, stream)
+                 : launch_pair<OutT, kBmn, 1>(tmA, tmB, dst, p, pairs, stream);
 }
 
 }  // namespace
@@ -376,14 +425,38 @@ int launch_gemm_pair(const TcGemmArgs& a, cudaStream_t stream) {
   p.m_tiles = (int)((a.M + bm - 1) / bm);
   p.n_tiles = (int)((a.N + 255) / 256);
   p.group_m = a.group_m > 0 ? a.group_m : (mb == 2 ? 4 : 8);
+
+  // Output path. Staged TMA stores need 16-byte aligned rows; they are what carries C to peer GPUs, and they
+  // also replace 32 scattered 16-byte stores per warp instruction by one bulk store per 32 x 128-byte block.
+  static DstMaps dst;  // zero-initialised maps are never dereferenced when n_dst == 0
+  DstMaps dmaps = dst;
+  const int out_elt = a.out_bf16 ? 2 : 4;
+  const bool c_tma_ok = (a.ldc * out_elt) % 16 == 0 && (a.c_batch_stride * out_elt) % 16 == 0 &&
+                        reinterpret_cast<uintptr_t>(a.C) % 16 == 0;
+  p.n_dst = 0;
+  if (a.n_peers > 0 && !c_tma_ok) return SX_ERR_INVALID;
+  if (a.n_peers < 0 || a.n_peers > MAX_DST - 1) return SX_ERR_INVALID;
+  if (c_tma_ok && (a.tma_store || a.n_peers > 0)) {
+    const CUtensorMapDataType odt = a.out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    uint64_t dims[3] = {(uint64_t)a.N, (uint64_t)a.M, (uint64_t)a.batch};
+    uint64_t strides[2] = {(uint64_t)a.ldc * out_elt, (uint64_t)a.c_batch_stride * out_elt};
+    uint32_t box[3] = {(uint32_t)(128 / out_elt), 32u, 1u};
+    for (int i = 0; i <= a.n_peers; ++i) {
+      const void* base = i == 0 ? a.C : a.peer_C[i - 1];
+      if (base == nullptr || reinterpret_cast<uintptr_t>(base) % 16) return SX_ERR_INVALID;
+      int rc = encode_tensor_map_3d(&dmaps.m[i], odt, base, dims, strides, box);
+      if (rc != SX_OK) return rc;
+    }
+    p.n_dst = 1 + a.n_peers;
+  }
   const long long total = (long long)p.batch * p.m_tiles * p.n_tiles;
   const int max_pairs = a.num_sms / 2;
   const int pairs = (int)(total < max_pairs ? total : max_pairs);
   if (a.out_bf16)
-    return a.b_mn ? launch_pair_mb<__nv_bfloat16, true>(mb, tmA, tmB, p, pairs, stream)
-                  : launch_pair_mb<__nv_bfloat16, false>(mb, tmA, tmB, p, pairs, stream);
-  return a.b_mn ? launch_pair_mb<float, true>(mb, tmA, tmB, p, pairs, stream)
-                : launch_pair_mb<float, false>(mb, tmA, tmB, p, pairs, stream);
+    return a.b_mn ? launch_pair_mb<__nv_bfloat16, true>(mb, tmA, tmB, dmaps, p, pairs, stream)
+                  : launch_pair_mb<__nv_bfloat16, false>(mb, tmA, tmB, dmaps, p, pairs, stream);
+  return a.b_mn ? launch_pair_mb<float, true>(mb, tmA, tmB, dmaps, p, pairs, stream)
+                : launch_pair_mb<float, false>(mb, tmA, tmB, dmaps, p, pairs, stream);
 }
 
 }  // namespace sx

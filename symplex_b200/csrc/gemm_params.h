@@ -37,8 +37,13 @@ struct GemmParams {
   int act;
   int* status;  // device word, receives KernelStatus on failure
   int m_tiles, n_tiles, group_m;
+  int n_dst;  // 0: epilogue stores straight from registers; >= 1: staged in shared memory and written by TMA
+              // to n_dst destinations (the local C first, then the same tile of every peer GPU's C)
   // shared-memory descriptor fields for a B tile held MN-major (row-major B[K,N])
   uint32_t b_lbo, b_sbo, b_kstep;
 };
+
+// Tensor maps of the output destinations of the TMA-store epilogue (local C, then peers' C).
+constexpr int MAX_DST = 8;
 
 }  // namespace sx

@@ -44,6 +44,9 @@ struct TcGemmArgs {
   int* status;
   int num_sms;
   int group_m;
+  int tma_store;               // pair kernels: stage the output in shared memory and write it with TMA
+  int n_peers;                 // pair kernels: also write every tile to the same offset of these buffers
+  const void* peer_C[7];       //   (other GPUs' copies of C, mapped into this process)
   uint32_t dbg_lbo, dbg_sbo, dbg_kstep;  // 0 = use the library's values
 };
 

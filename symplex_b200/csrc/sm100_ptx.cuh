@@ -150,6 +150,25 @@ __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorM
       : "memory");
 }
 
+// 3-D tiled store shared::cta -> global (this GPU's memory or a peer's mapped memory), bulk-group completion.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tm)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// All but the newest kN groups of this thread have finished READING their shared-memory source.
+template <int kN>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kN) : "memory");
+}
+// ... have completed entirely (writes performed).
+template <int kN>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(kN) : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05
 template <int kCtaGroup>
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {

@@ -2,8 +2,20 @@
 
 Mirrors the planning types of the reference (``include/symplex/distributed/sharding.h:18-95``:
 ``ShardingStrategy``, ``ShardingSpec``, ``ShardPlan``; ``nccl_bridge.h:19-26``: ``CollectiveOp``) and
-turns the plan into an executed computation: one process per GPU, ``torch.distributed`` (NCCL over
-NVLink) for the exchange, the tcgen05 GEMM library for the math.
+turns the plan into an executed computation: one process per GPU, the tcgen05 GEMM library for the math,
+``torch.distributed`` for the plumbing (process group, symmetric-memory rendezvous, barriers).
+
+Two ways to exchange C:
+
+``exchange="peer_store"`` (default on GPUs)
+    C lives in symmetric memory (every rank can address every rank's copy). The GEMM kernel's epilogue
+    writes each finished tile to the local C and, by TMA stores over NVLink, to the same place in every
+    peer's C (``symplex_b200_gemm_peers``): the all-gather is fused into the GEMM and overlaps it tile by
+    tile; there is no separate collective kernel competing for SMs. A barrier before (peers are done
+    reading the previous result) and after (everybody's tiles have landed) orders the ranks.
+``exchange="nccl"``
+    The local rows are computed in ``chunks`` pieces and each piece is gathered in place by an asynchronous
+    ``all_gather_into_tensor`` while the next piece computes (also the path the CPU/gloo tests drive).
 
 Partition (the reference parallelises the same way over CPU threads,
 ``rust-engine/src/x86_emitter.rs:1857-1874``): rows of A and C are split evenly over the ranks, B is
@@ -132,7 +144,7 @@ class RowShardedGemm:
     """
 
     def __init__(self, M: int, N: int, K: int, *, group=None, chunks: Optional[int] = None, activation=None,
-                 b_layout: int = 0, local_gemm: Optional[Callable] = None):
+                 b_layout: int = 0, local_gemm: Optional[Callable] = None, exchange: Optional[str] = None):
         import torch.distributed as dist
         self.group = group
         if dist.is_available() and dist.is_initialized():
@@ -143,6 +155,16 @@ class RowShardedGemm:
         if M % self.world != 0:
             raise ValueError(f"M={M} rows do not split evenly over {self.world} ranks")
         self.M, self.N, self.K = M, N, K
+        if exchange is None:
+            exchange = "nccl" if (local_gemm is not None or self.world == 1) else "peer_store"
+        if exchange not in ("peer_store", "nccl"):
+            raise ValueError("exchange must be 'peer_store' or 'nccl'")
+        self.exchange = exchange
+        if exchange == "peer_store":
+            chunks = 1  # one GEMM launch over all local rows; the exchange rides on its epilogue
+        self._symm_out = None
+        self._peer_ptrs = None
+        self._flag = None
         self.chunks = pick_chunks(M, self.world, chunks)
         self.blocks = owned_row_blocks(M, self.world, self.rank, self.chunks)
         self.activation = activation
@@ -155,6 +177,45 @@ class RowShardedGemm:
         """Global row numbers of this rank's rows of A / C, in local storage order."""
         import torch
         return torch.cat([torch.arange(s, s + n) for s, n in self.blocks])
+
+    def output_buffer(self, dtype, device):
+        """The [M, N] result buffer of the peer-store exchange: symmetric memory, allocated and exchanged
+        among the ranks on first use (a collective call), then reused by every ``__call__``."""
+        import os
+
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        if self._symm_out is not None and self._symm_out.dtype == dtype:
+            return self._symm_out
+        # plain peer mappings are all this exchange needs; keep NVLink multicast objects out of it
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        buf = symm_mem.empty((self.M, self.N), dtype=dtype, device=device)
+        grp = self.group if self.group is not None else dist.group.WORLD
+        hdl = symm_mem.rendezvous(buf, grp)
+        self._symm_out = buf
+        self._peer_ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self._hdl = hdl
+        self._flag = torch.zeros(1, device=device, dtype=torch.int32)
+        return buf
+
+    def _barrier(self):
+        """Stream-ordered barrier over the group (a one-element all-reduce)."""
+        import torch.distributed as dist
+        dist.all_reduce(self._flag, group=self.group)
+
+    def _call_peer_store(self, A_local, B, bias, out_dtype):
+        from . import gemm
+        out = self.output_buffer(out_dtype, A_local.device)
+        row0, nrows = self.blocks[0]
+        elt = out.element_size()
+        mine = out[row0:row0 + nrows]
+        peers = [p + row0 * self.N * elt for r, p in enumerate(self._peer_ptrs) if r != self.rank]
+        self._barrier()  # every rank has finished with the previous contents of C
+        gemm(A_local, B, bias=bias, activation=self.activation, out=mine, b_layout=self.b_layout,
+             peer_outputs=peers)
+        self._barrier()  # every rank's tiles have been written everywhere
+        return out
 
     def _gemm_chunk(self, A_blk, B, bias, out_blk):
         if self._local_gemm is not None:
@@ -169,6 +230,12 @@ class RowShardedGemm:
         m_loc = self.M // self.world
         if tuple(A_local.shape) != (m_loc, self.K):
             raise ValueError(f"A_local must be [{m_loc}, {self.K}], got {tuple(A_local.shape)}")
+        if self.exchange == "peer_store" and self.world > 1:
+            dt = out.dtype if out is not None else (out_dtype if out_dtype is not None else A_local.dtype)
+            if out is not None and (self._symm_out is None or out.data_ptr() != self._symm_out.data_ptr()):
+                raise ValueError("with exchange='peer_store' the result lives in output_buffer(); pass out=None "
+                                 "or that buffer")
+            return self._call_peer_store(A_local, B, bias, dt)
         if out is None:
             dt = out_dtype if out_dtype is not None else A_local.dtype
             out = torch.empty((self.M, self.N), device=A_local.device, dtype=dt)

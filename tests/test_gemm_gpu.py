@@ -392,3 +392,30 @@ def test_host_path_row_chunked_pipeline(lib, oracle, dtype, monkeypatch):
     ref = oracle.epilogue(oracle.matmul_rows(Ar, Br, rows), bias=bias, act=_capi.ACT_RELU)
     tol = TOL_BF16 if dtype == "bf16" else TOL_F32
     assert rel_frobenius(chunked[rows], oracle.bf16_round(ref) if dtype == "bf16" else ref) <= tol
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(1024, 768, 320), (600, 520, 136), (4096, 2048, 512)])
+def test_peer_outputs_receive_every_tile(lib, shape, out_dtype):
+    """The multi-destination epilogue on one GPU: two extra buffers stand in for other GPUs' C."""
+    M, N, K = shape
+    g = torch.Generator(device=DEV).manual_seed(41)
+    A = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    B = torch.randn(K, N, device=DEV, generator=g).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV, generator=g)
+    want = _run(A, B, bias=bias, activation="silu", out_dtype=out_dtype)
+    peers = [torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype) for _ in range(2)]
+    got = _run(A, B, bias=bias, activation="silu", out_dtype=out_dtype, peer_outputs=[p.data_ptr() for p in peers])
+    assert torch.equal(got, want)
+    for p in peers:
+        assert torch.equal(p, want)
+
+
+def test_tma_store_and_direct_store_epilogues_agree(lib, monkeypatch):
+    g = torch.Generator(device=DEV).manual_seed(42)
+    A = torch.randn(2048, 512, device=DEV, generator=g).to(torch.bfloat16)
+    B = torch.randn(512, 1000, device=DEV, generator=g).to(torch.bfloat16)  # ragged N: TMA clips the last block
+    staged = _run(A, B, activation="gelu")
+    monkeypatch.setenv("SYMPLEX_B200_TMA_STORE", "0")
+    direct = _run(A, B, activation="gelu")
+    assert torch.equal(staged, direct)
