@@ -81,6 +81,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   extern __shared__ uint8_t dyn_smem[];
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint64_t fwd_bar[Cfg::EPI_WARPS];  // per epilogue warp: a finished block is back in its staging tile
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -100,6 +101,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 8 * kMB);  // every epilogue warp of both CTAs releases each accumulator
     }
+    for (int w = 0; w < Cfg::EPI_WARPS; ++w) mbar_init(&fwd_bar[w], 1);
     abort_flag = 0;
     fence_mbar_init();
   }
@@ -251,7 +253,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const EpilogueCtx<OutT> ep(p);
     uint8_t* staging = tiles + STAGES * Cfg::STAGE_BYTES + (warp - 2) * Cfg::STAGING_BYTES;
     int slot = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, fwd_phase = 0;
     bool ok = true;
     for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
       const PairTile tc = pair_tile<Cfg::BM, BN>(p, t);
@@ -287,8 +289,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             ep.template strip<true>(v, row_ok, row_off, col0 + 32);
           } else {
             // Staged path: the warp's 32 x 128-byte block goes to shared memory and one lane hands it to the
-            // TMA unit once per destination (local C, then each peer GPU's C). bf16: both strips form one
-            // block; fp32: one block per strip.
+            // TMA unit, which writes it to the local C. bf16: both strips form one block; fp32: one block
+            // per strip. (Peers are served after TMEM has been released, see below.)
             if (lane == 0) bulk_wait_group_read<0>();  // the previous block has left the staging tile
             __syncwarp();
             ep.stage(v, staging, lane, 0);
@@ -296,7 +298,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0) {
-                for (int d = 0; d < p.n_dst; ++d) tma_store_3d(&dst.m[d], staging, col0, row0, tc.z);
+                tma_store_3d(&dst.m[0], staging, col0, row0, tc.z);
                 bulk_commit_group();
               }
               if (!second) continue;
@@ -317,7 +319,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             __syncwarp();
             if (lane == 0) {
               const int cstore = sizeof(OutT) == 4 ? col0 + 32 : col0;
-              for (int d = 0; d < p.n_dst; ++d) tma_store_3d(&dst.m[d], staging, cstore, row0, tc.z);
+              tma_store_3d(&dst.m[0], staging, cstore, row0, tc.z);
               bulk_commit_group();
             }
           }
@@ -330,6 +332,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (++slot == 2) { slot = 0; acc_phase ^= 1; }
       } else {
         acc_phase ^= 1;
+      }
+      // Forwarding to the peer GPUs. TMEM is free again, so the MMAs of the next tile are already running;
+      // NVLink back-pressure now only delays this warp, not the tensor pipe. Each block this warp wrote to
+      // the local C is read back (an L2 hit) into the staging tile by TMA and stored to every peer's C.
+      if (ok && p.n_dst > 1) {
+        if (lane == 0) {
+          bulk_wait_group<0>();  // this tile's local stores have been performed
+          constexpr int STEP = sizeof(OutT) == 4 ? 1 : 2;  // strips per 128-byte block
+          for (int blk = 0; ok && blk < kMB; ++blk) {
+            const int row0 = tc.m0 + int(cta_rank) * Cfg::ROWS + blk * 128 + q * 32;
+            if (row0 >= p.M) continue;
+            for (int c = half * STRIPS; c < (half + 1) * STRIPS; c += STEP) {
+              const int col0 = tc.n0 + c * 32;
+              if (col0 >= p.N) break;
+              bulk_wait_group_read<0>();  // the previous block has left the staging tile
+              mbar_arrive_expect_tx(&fwd_bar[warp - 2], Cfg::STAGING_BYTES);
+              tma_load_3d(staging, &dst.m[0], &fwd_bar[warp - 2], col0, row0, tc.z);
+              if (!mbar_wait(&fwd_bar[warp - 2], fwd_phase, &abort_flag)) { ok = false; break; }
+              fwd_phase ^= 1;
+              for (int d = 1; d < p.n_dst; ++d) tma_store_3d(&dst.m[d], staging, col0, row0, tc.z);
+              bulk_commit_group();
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       }
     }
     if (p.n_dst != 0 && lane == 0) bulk_wait_group<0>();  // every store of this warp has been performed
