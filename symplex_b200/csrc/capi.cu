@@ -60,7 +60,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 int encode_tensor_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, const uint64_t dims[3],
-                         const uint64_t strides_bytes[2], const uint32_t box[3]) {
+                         const uint64_t strides_bytes[2], const uint32_t box[3], bool swizzle128) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(SX_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t d[3] = {dims[0], dims[1], dims[2]};
@@ -68,7 +68,7 @@ int encode_tensor_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* b
   cuuint32_t b[3] = {box[0], box[1], box[2]};
   cuuint32_t es[3] = {1, 1, 1};
   CUresult r = fn(out, dt, 3, const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(SX_ERR_INVALID, "cuTensorMapEncodeTiled failed (%d): dims %llu,%llu,%llu strides %llu,%llu box %u,%u,%u",
                 (int)r, (unsigned long long)d[0], (unsigned long long)d[1], (unsigned long long)d[2],
@@ -225,7 +225,23 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
   if (n_peers > 0 && p.f32_in)
     return fail(SX_ERR_INVALID, "peer destinations are supported for bf16 inputs only");
   if (p.f32_in) {
-    // fp32: both operands are rewritten as {hi, lo} tf32 planes with K contiguous.
+    // Small and batched problems (each operand element feeds only a few tiles): split inside the GEMM kernel.
+    {
+      TcGemmArgs f = g;
+      f.b_mn = !p.b_col;
+      f.A = A; f.lda = p.lda; f.a_plane_stride = p.a_bs;
+      f.B = B; f.ldb = p.ldb; f.b_plane_stride = p.b_bs;
+      bool fused = (p.M + 127) / 128 <= 8 && (p.N + 63) / 64 <= 16 && f32_fused_operands_ok(f);
+      if (const char* e = getenv("SYMPLEX_B200_F32_FUSED")) fused = atoi(e) != 0 && f32_fused_operands_ok(f);
+      if (fused) {
+        int rc = launch_gemm_f32_fused(f, stream);
+        if (rc == SX_ERR_EXEC) return fail(rc, "GEMM kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        if (rc != SX_OK) return rc;
+        ++g_launches;
+        return SX_OK;
+      }
+    }
+    // Otherwise both operands are rewritten as {hi, lo} tf32 planes with K contiguous.
     float* Ap = reinterpret_cast<float*>(w + p.a_off);
     float* Bp = reinterpret_cast<float*>(w + p.b_off);
     int rc = launch_split_tf32(static_cast<const float*>(A), p.lda, p.a_bs, Ap, (int)p.M, (int)p.K, (int)p.a_ldp,

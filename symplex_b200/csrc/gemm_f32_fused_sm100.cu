@@ -1,0 +1,350 @@
+// fp32 GEMM (3xTF32, round-to-nearest chunk accumulation) with the hi/lo operand split done INSIDE the kernel.
+//
+// gemm_tf32x3_kernel reads operands that a pre-pass has already split into {hi, lo} tf32 planes. That is the
+// right trade for large products, where every plane is re-read by many tiles. For small and batched problems
+// (512^3; 2048 x 64^3) each operand element is used by few tiles, the pre-pass triples the HBM traffic and adds
+// two kernel launches. Here the TMA producer streams the RAW fp32 tiles; four converter warps turn each staged
+// tile into the planes the tensor core consumes, in shared memory:
+//   A tile  [128 rows][32 k], loaded 128B-swizzled: hi = tf32(x) overwrites x in place, lo = tf32(x - hi) goes
+//           to a second buffer at the same (swizzled) position - the split is element-wise, so the swizzle
+//           pattern carries over untouched.
+//   B tile, column-major B ([N,K], K contiguous): same as A.
+//   B tile, row-major B ([K,N]): loaded unswizzled as [32 k][64 n]; the converters transpose while splitting and
+//           write K-major 128B-swizzled hi / lo tiles (kind::tf32 wants K-major operands here).
+// Everything downstream (three MMAs per k step, main accumulator drained every 4 k-blocks into fp32 registers,
+// correction accumulator added once per tile, fused epilogue) is the scheme of gemm_tf32x3_kernel.
+//
+//   warp 0      TMA producer (raw tiles)            warp 1      MMA issuer
+//   warps 2..5  accumulate + epilogue               warps 6..9  converters
+#include <cuda_bf16.h>
+
+#include "epilogue.cuh"
+#include "gemm_params.h"
+#include "host_api.h"
+#include "sm100_ptx.cuh"
+
+namespace sx {
+
+struct FusedCfg {
+  static constexpr int BM = 128, BN = 64, BK = 32, UMMA_K = 8, CHUNK_KB = 4;
+  static constexpr int A_OFF = 0;             // raw A, becomes A hi          16 KB
+  static constexpr int ALO_OFF = 16 * 1024;   // A lo                          16 KB
+  static constexpr int BRAW_OFF = 32 * 1024;  // raw B (K-major: becomes hi)    8 KB
+  static constexpr int BHI_OFF = 40 * 1024;   // B hi when B had to be transposed 8 KB
+  static constexpr int BLO_OFF = 48 * 1024;   // B lo                           8 KB
+  static constexpr int STAGE_BYTES = 56 * 1024;
+  static constexpr int RAW_BYTES = 16 * 1024 + 8 * 1024;  // bytes the TMA delivers per stage
+  static constexpr int STAGES = 4;
+  static constexpr int TMEM_COLS = 4 * BN;  // main[2] + corr[2]
+  static constexpr int THREADS = 320;
+  static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;
+};
+
+__device__ __forceinline__ float tf32_rna(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+__device__ __forceinline__ void split4(const float4& x, float4& hi, float4& lo) {
+  hi.x = tf32_rna(x.x); hi.y = tf32_rna(x.y); hi.z = tf32_rna(x.z); hi.w = tf32_rna(x.w);
+  lo.x = tf32_rna(x.x - hi.x); lo.y = tf32_rna(x.y - hi.y); lo.z = tf32_rna(x.z - hi.z); lo.w = tf32_rna(x.w - hi.w);
+}
+
+template <typename OutT, bool kBmn>
+__global__ void __launch_bounds__(FusedCfg::THREADS, 1)
+gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const GemmParams p) {
+  using Cfg = FusedCfg;
+  constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES, CH = Cfg::CHUNK_KB;
+
+  extern __shared__ uint8_t dyn_smem[];
+  __shared__ uint64_t raw_full[STAGES], conv_done[STAGES], empty_bar[STAGES];
+  __shared__ uint64_t main_full[2], main_empty[2], corr_full[2], corr_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&conv_done[s], 4);  // one arrival per converter warp
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&main_full[a], 1);
+      mbar_init(&main_empty[a], 4);
+      mbar_init(&corr_full[a], 1);
+      mbar_init(&corr_empty[a], 4);
+    }
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(&tmem_base_slot, Cfg::TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  const int per = p.m_tiles * p.n_tiles;
+  const int total_tiles = p.batch * per;
+  const int nkb = (p.K + BK - 1) / BK;
+  const int nchunks = (nkb + CH - 1) / CH;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer: raw fp32 tiles
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        const int z = t / per, r = t - z * per;
+        const int m0 = (r % p.m_tiles) * BM, n0 = (r / p.m_tiles) * BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) { ok = false; break; }
+          uint8_t* base = tiles + stage * Cfg::STAGE_BYTES;
+          mbar_arrive_expect_tx(&raw_full[stage], Cfg::RAW_BYTES);
+          tma_load_3d(base + Cfg::A_OFF, &tmA, &raw_full[stage], kb * BK, m0, z);
+          if constexpr (kBmn) tma_load_3d(base + Cfg::BRAW_OFF, &tmB, &raw_full[stage], n0, kb * BK, z);
+          else tma_load_3d(base + Cfg::BRAW_OFF, &tmB, &raw_full[stage], kb * BK, n0, z);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(2, false, false, BM, BN);
+      constexpr uint64_t dhi = make_smem_desc_hi(16, 1024);
+      int stage = 0;
+      uint32_t phase = 0;
+      int macc = 0, cacc = 0;
+      uint32_t mphase = 0, cphase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        if (!mbar_wait(&corr_empty[cacc], cphase ^ 1, &abort_flag)) break;
+        const uint32_t d_corr = tmem_base + 2 * BN + cacc * BN;
+        int kb = 0;
+        for (int ch = 0; ok && ch < nchunks; ++ch) {
+          if (!mbar_wait(&main_empty[macc], mphase ^ 1, &abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t d_main = tmem_base + macc * BN;
+          const int kb_end = min(kb + CH, nkb);
+          for (int kc = 0; kb < kb_end; ++kb, ++kc) {
+            if (!mbar_wait(&conv_done[stage], phase, &abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t base = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
+            const uint32_t a_hi = base + Cfg::A_OFF, a_lo = base + Cfg::ALO_OFF;
+            const uint32_t b_hi = base + (kBmn ? Cfg::BHI_OFF : Cfg::BRAW_OFF), b_lo = base + Cfg::BLO_OFF;
+#pragma unroll
+            for (int k = 0; k < BK / Cfg::UMMA_K; ++k) {
+              const uint32_t o = k * 32;
+              umma<1, 1>(d_main, smem_desc(dhi, a_hi + o), smem_desc(dhi, b_hi + o), idesc, (kc | k) != 0 ? 1u : 0u);
+              umma<1, 1>(d_corr, smem_desc(dhi, a_hi + o), smem_desc(dhi, b_lo + o), idesc, (kb | k) != 0 ? 1u : 0u);
+              umma<1, 1>(d_corr, smem_desc(dhi, a_lo + o), smem_desc(dhi, b_hi + o), idesc, 1u);
+            }
+            umma_commit(&empty_bar[stage]);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          umma_commit(&main_full[macc]);
+          if (++macc == 2) { macc = 0; mphase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&corr_full[cacc]);
+        if (++cacc == 2) { cacc = 0; cphase ^= 1; }
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ converters (128 threads)
+    const int tid = threadIdx.x - 192;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!mbar_wait(&raw_full[stage], phase, &abort_flag)) { ok = false; break; }
+        uint8_t* base = tiles + stage * Cfg::STAGE_BYTES;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {  // A: 1024 16-byte chunks, position-wise
+          const int off = (i * 128 + tid) * 16;
+          float4 hi, lo;
+          split4(*reinterpret_cast<const float4*>(base + Cfg::A_OFF + off), hi, lo);
+          *reinterpret_cast<float4*>(base + Cfg::A_OFF + off) = hi;
+          *reinterpret_cast<float4*>(base + Cfg::ALO_OFF + off) = lo;
+        }
+        if constexpr (!kBmn) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {  // B [64 n][32 k], position-wise
+            const int off = (i * 128 + tid) * 16;
+            float4 hi, lo;
+            split4(*reinterpret_cast<const float4*>(base + Cfg::BRAW_OFF + off), hi, lo);
+            *reinterpret_cast<float4*>(base + Cfg::BRAW_OFF + off) = hi;
+            *reinterpret_cast<float4*>(base + Cfg::BLO_OFF + off) = lo;
+          }
+        } else {
+          const float* raw = reinterpret_cast<const float*>(base + Cfg::BRAW_OFF);  // [32 k][64 n]
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {  // transpose: 4 consecutive k of one column n -> one 16-byte chunk
+            const int item = i * 128 + tid;
+            const int n = item & 63, kc = item >> 6;
+            float4 x;
+            x.x = raw[(kc * 4 + 0) * 64 + n];
+            x.y = raw[(kc * 4 + 1) * 64 + n];
+            x.z = raw[(kc * 4 + 2) * 64 + n];
+            x.w = raw[(kc * 4 + 3) * 64 + n];
+            float4 hi, lo;
+            split4(x, hi, lo);
+            const int off = n * 128 + ((kc ^ (n & 7)) << 4);
+            *reinterpret_cast<float4*>(base + Cfg::BHI_OFF + off) = hi;
+            *reinterpret_cast<float4*>(base + Cfg::BLO_OFF + off) = lo;
+          }
+        }
+        fence_proxy_async_smem();  // the tensor core reads these tiles through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&conv_done[stage]);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ accumulate + epilogue (warps 2..5)
+    const int q = warp & 3;
+    const EpilogueCtx<OutT> ep(p);
+    const uint32_t lane_base = uint32_t(q * 32) << 16;
+    int macc = 0, cacc = 0;
+    uint32_t mphase = 0, cphase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      const int z = t / per, r = t - z * per;
+      const int m0 = (r % p.m_tiles) * BM, n0 = (r / p.m_tiles) * BN;
+      float sum[BN];
+#pragma unroll
+      for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
+      for (int ch = 0; ch < nchunks; ++ch) {
+        if (!mbar_wait(&main_full[macc], mphase, &abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t rr[32];
+          tmem_ld_32x32(tmem_base + lane_base + macc * BN + c * 32, rr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[c * 32 + j] += __uint_as_float(rr[j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&main_empty[macc]);
+        if (++macc == 2) { macc = 0; mphase ^= 1; }
+      }
+      if (!ok) break;
+      if (!mbar_wait(&corr_full[cacc], cphase, &abort_flag)) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t rr[32];
+        tmem_ld_32x32(tmem_base + lane_base + 2 * BN + cacc * BN + c * 32, rr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum[c * 32 + j] += __uint_as_float(rr[j]);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&corr_empty[cacc]);
+      if (++cacc == 2) { cacc = 0; cphase ^= 1; }
+
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const long long row_off = (long long)z * p.c_batch_stride + (long long)row * p.ldc;
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = sum[c * 32 + j];
+        ep.template strip<false>(v, row_ok, row_off, col0);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc<1>(tmem_base, Cfg::TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && abort_flag != 0 && p.status != nullptr) atomicExch(p.status, int(ST_WAIT_TIMEOUT));
+}
+
+// ------------------------------------------------------------------ host side
+namespace {
+
+template <typename OutT, bool kBmn>
+int launch_fused(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t stream) {
+  auto kern = gemm_f32_fused_kernel<OutT, kBmn>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedCfg::DYN_SMEM) != cudaSuccess)
+    return SX_ERR_DRIVER;
+  kern<<<grid, FusedCfg::THREADS, FusedCfg::DYN_SMEM, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+}
+
+}  // namespace
+
+bool f32_fused_operands_ok(const TcGemmArgs& a) {
+  return a.lda % 4 == 0 && a.ldb % 4 == 0 && a.a_plane_stride % 4 == 0 && a.b_plane_stride % 4 == 0 &&
+         reinterpret_cast<uintptr_t>(a.A) % 16 == 0 && reinterpret_cast<uintptr_t>(a.B) % 16 == 0;
+}
+
+// Raw fp32 operands: A [batch][M][lda]; B [batch][K][ldb] (a.b_mn = 1, row-major) or [batch][N][ldb] (a.b_mn = 0).
+// a_plane_stride / b_plane_stride are the batch strides. Needs 16-byte aligned rows (f32_fused_operands_ok).
+int launch_gemm_f32_fused(const TcGemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return SX_ERR_INVALID;
+  if (!f32_fused_operands_ok(a)) return SX_ERR_INVALID;
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[3] = {(uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.batch};
+    uint64_t strides[2] = {(uint64_t)a.lda * 4, (uint64_t)a.a_plane_stride * 4};
+    uint32_t box[3] = {32u, 128u, 1u};
+    int rc = encode_tensor_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.A, dims, strides, box);
+    if (rc != SX_OK) return rc;
+  }
+  if (a.b_mn) {
+    uint64_t dims[3] = {(uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.batch};
+    uint64_t strides[2] = {(uint64_t)a.ldb * 4, (uint64_t)a.b_plane_stride * 4};
+    uint32_t box[3] = {64u, 32u, 1u};
+    int rc = encode_tensor_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.B, dims, strides, box, /*swizzle128=*/false);
+    if (rc != SX_OK) return rc;
+  } else {
+    uint64_t dims[3] = {(uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.batch};
+    uint64_t strides[2] = {(uint64_t)a.ldb * 4, (uint64_t)a.b_plane_stride * 4};
+    uint32_t box[3] = {32u, 64u, 1u};
+    int rc = encode_tensor_map_3d(&tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.B, dims, strides, box);
+    if (rc != SX_OK) return rc;
+  }
+  GemmParams p{};
+  p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
+  p.batch = a.batch;
+  p.C = a.C; p.ldc = a.ldc; p.c_batch_stride = a.c_batch_stride;
+  p.bias = a.bias; p.residual = a.residual;
+  p.alpha = a.alpha; p.beta = a.beta; p.act = a.act;
+  p.status = a.status;
+  p.m_tiles = (int)((a.M + 127) / 128);
+  p.n_tiles = (int)((a.N + 63) / 64);
+  const long long total = (long long)p.batch * p.m_tiles * p.n_tiles;
+  const int grid = (int)(total < a.num_sms ? total : a.num_sms);
+  if (a.out_bf16)
+    return a.b_mn ? launch_fused<__nv_bfloat16, true>(tmA, tmB, p, grid, stream)
+                  : launch_fused<__nv_bfloat16, false>(tmA, tmB, p, grid, stream);
+  return a.b_mn ? launch_fused<float, true>(tmA, tmB, p, grid, stream)
+                : launch_fused<float, false>(tmA, tmB, p, grid, stream);
+}
+
+}  // namespace sx

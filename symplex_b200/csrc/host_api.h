@@ -61,9 +61,14 @@ int launch_gemm_tf32x3(const TcGemmArgs& a, cudaStream_t stream);
 // Records `msg` as the calling thread's last error and returns `code`.
 int set_last_error(int code, const char* msg);
 
+// fp32 GEMM with the tf32 hi/lo split done in shared memory (no pre-pass, no scratch): raw fp32 operands,
+// 128 x 64 tiles. For small and batched problems; operands must satisfy f32_fused_operands_ok.
+int launch_gemm_f32_fused(const TcGemmArgs& a, cudaStream_t stream);
+bool f32_fused_operands_ok(const TcGemmArgs& a);
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
 int encode_tensor_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, const uint64_t dims[3],
-                         const uint64_t strides_bytes[2], const uint32_t box[3]);
+                         const uint64_t strides_bytes[2], const uint32_t box[3], bool swizzle128 = true);
 
 // Operand preparation kernels (prep_kernels.cu).
 // fp32 [batch][rows][cols] (leading dimension ld_in) -> planes [batch][2][rows][cols_p]:
