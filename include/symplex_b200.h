@@ -157,6 +157,14 @@ void symplex_matmul_tiled_f32(const float* A, const float* B, float* C, int64_t 
 void blas_sgemm(const float* a, const float* b, float* c, size_t m, size_t n, size_t k);
 void cache_tiled_sgemm_thin(const float* a, const float* b, float* c, size_t m, size_t n, size_t k);
 
+/* Execute one serialized Instr::TensorMatMul record (rust-engine/src/types.rs:407-417,646-657,884-904: opcode
+ * 0xA2, dst/lhs/rhs slot u16, m/n/k u64, element_ty, lhs_layout, rhs_layout; 34 bytes little endian) against an
+ * array of host pointers indexed by slot - what the reference's JIT lowers to a blas_sgemm call
+ * (rust-engine/src/phase3_jit.rs:13024-13118). Unlike the reference, which parses the layout bytes and then
+ * ignores them, rhs_layout is honoured (RowMajor: [K,N]; ColMajor: stored [N,K]); F32 and BF16 element types;
+ * lhs must be RowMajor. Returns 0 or a negative SYMPLEX_ERR_* code. */
+int64_t symplex_b200_exec_tensor_matmul(const uint8_t* record, size_t record_len, void* const* slots, size_t nslots);
+
 /* ---- device queries -------------------------------------------------------------------------- */
 
 /* CudaRuntime::is_available / _symplex_core.cuda_available (rust-engine/src/cuda_backend.rs:1078-1100,

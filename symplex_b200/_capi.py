@@ -70,6 +70,7 @@ SIGNATURES = {
     "symplex_matmul_tiled_f32": (None, [_F32P, _F32P, _F32P, c_int64, c_int64, c_int64]),
     "blas_sgemm": (None, [_F32P, _F32P, _F32P, c_size_t, c_size_t, c_size_t]),
     "cache_tiled_sgemm_thin": (None, [_F32P, _F32P, _F32P, c_size_t, c_size_t, c_size_t]),
+    "symplex_b200_exec_tensor_matmul": (c_int64, [c_char_p, c_size_t, ctypes.POINTER(c_void_p), c_size_t]),
     "symplex_cuda_available": (c_int, []),
     "symplex_cuda_device_info": (c_int, [ctypes.POINTER(DeviceInfo)]),
     "symplex_b200_launch_count": (c_uint64, []),

@@ -634,6 +634,35 @@ void cache_tiled_sgemm_thin(const float* a, const float* b, float* c, size_t m, 
   symplex_matmul_f32(a, b, c, (int64_t)m, (int64_t)n, (int64_t)k);
 }
 
+int64_t symplex_b200_exec_tensor_matmul(const uint8_t* rec, size_t len, void* const* slots, size_t nslots) {
+  // Wire format of Instr::TensorMatMul (rust-engine/src/types.rs:884-904): 0xA2, dst u16, lhs u16, rhs u16,
+  // m u64, n u64, k u64, element_ty u8, lhs_layout u8, rhs_layout u8 - little endian, 34 bytes.
+  if (rec == nullptr || len < 34) return fail(SX_ERR_INVALID, "TensorMatMul record needs 34 bytes, got %zu", len);
+  if (rec[0] != 0xA2) return fail(SX_ERR_INVALID, "opcode 0x%02X is not TensorMatMul (0xA2)", rec[0]);
+  auto u16 = [&](size_t o) { return (uint32_t)rec[o] | ((uint32_t)rec[o + 1] << 8); };
+  auto u64 = [&](size_t o) {
+    uint64_t v = 0;
+    for (int i = 7; i >= 0; --i) v = (v << 8) | rec[o + i];
+    return v;
+  };
+  const uint32_t dst = u16(1), lhs = u16(3), rhs = u16(5);
+  const uint64_t m = u64(7), n = u64(15), k = u64(23);
+  const int ety = rec[31], lhs_layout = rec[32], rhs_layout = rec[33];
+  if (dst >= nslots || lhs >= nslots || rhs >= nslots || slots == nullptr)
+    return fail(SX_ERR_INVALID, "slot index out of range (%u, %u, %u of %zu)", dst, lhs, rhs, nslots);
+  if (ety != SYMPLEX_DT_F32 && ety != SYMPLEX_DT_BF16)
+    return fail(SX_ERR_INVALID, "element type %d not supported on this path (F32 = 9, BF16 = 11)", ety);
+  if (lhs_layout != SYMPLEX_ROW_MAJOR) return fail(SX_ERR_INVALID, "lhs must be row-major");
+  if (rhs_layout != SYMPLEX_ROW_MAJOR && rhs_layout != SYMPLEX_COL_MAJOR)
+    return fail(SX_ERR_INVALID, "rhs layout byte %d is not a MatrixLayout", rhs_layout);
+  if (m > 0x7fffffffULL || n > 0x7fffffffULL || k > 0x7fffffffULL) return fail(SX_ERR_INVALID, "dimension too large");
+  if (m == 0 || n == 0 || k == 0) return 0;
+  symplex_gemm_desc d;
+  symplex_b200_gemm_desc_init(&d, (int64_t)m, (int64_t)n, (int64_t)k, ety, ety);
+  d.b_layout = rhs_layout;
+  return gemm_host(&d, slots[lhs], slots[rhs], slots[dst], nullptr, nullptr);
+}
+
 int symplex_cuda_available(void) {
   int n = 0;
   if (cudaGetDeviceCount(&n) != cudaSuccess || n < 1) {

@@ -419,3 +419,31 @@ def test_tma_store_and_direct_store_epilogues_agree(lib, monkeypatch):
     monkeypatch.setenv("SYMPLEX_B200_TMA_STORE", "0")
     direct = _run(A, B, activation="gelu")
     assert torch.equal(staged, direct)
+
+
+@pytest.mark.parametrize("ety,rhs_layout", [(9, 0), (9, 1), (11, 0), (11, 1)])
+def test_tensor_matmul_wire_record(lib, oracle, ety, rhs_layout):
+    """A serialized Instr::TensorMatMul (34-byte 0xA2 record) executed against a slot array of host pointers;
+    the rhs layout byte is honoured."""
+    import struct
+    rng = np.random.default_rng(51 + ety + rhs_layout)
+    M, N, K = 96, 136, 200
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = rng.standard_normal((K, N)).astype(np.float32)
+    if ety == 11:
+        A, B = oracle.bf16_round(A), oracle.bf16_round(B)
+        to_dev = lambda x: oracle.f32_to_bf16_bits(x)
+        C = np.zeros((M, N), np.uint16)
+    else:
+        to_dev = lambda x: x
+        C = np.full((M, N), np.nan, np.float32)
+    a_buf = np.ascontiguousarray(to_dev(A))
+    b_buf = np.ascontiguousarray(to_dev(B.T if rhs_layout == 1 else B))
+    rec = struct.pack("<BHHHQQQBBB", 0xA2, 3, 1, 2, M, N, K, ety, 0, rhs_layout)
+    slots = (ctypes.c_void_p * 4)(None, a_buf.ctypes.data, b_buf.ctypes.data, C.ctypes.data)
+    assert lib.symplex_b200_exec_tensor_matmul(rec, len(rec), slots, 4) == 0, _capi.last_error()
+    ref = oracle.jit_parallel_matmul(A, B)
+    if ety == 11:
+        assert rel_frobenius(oracle.bf16_bits_to_f32(C), oracle.bf16_round(ref)) <= TOL_BF16
+    else:
+        assert rel_frobenius(C, ref) <= TOL_F32
