@@ -388,7 +388,7 @@ def main():
         roofline = {"bound": "hbm", "achieved": ach, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
                     "frac": ach / float(peaks["hbm_gbs"]), "traffic": traffic,
                     "kernel_ms": kernel_ms, "peak_kind": f"HBM copy, {peak_note}", "bytes_per_launch": algo_bytes,
-                    "note": "kernel_ms covers the split pre-pass and the GEMM of one step"}
+                    "note": "one step = one launch of the fused-split fp32 GEMM kernel (no pre-pass)"}
 
     cpu_baseline = None
     if not args.no_cpu_baseline and world == 1:
