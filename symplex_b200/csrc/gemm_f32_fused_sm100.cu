@@ -40,10 +40,11 @@ struct FusedCfg {
   static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;
 };
 
+// Round to tf32 (10 mantissa bits), nearest with ties away from zero - the result of cvt.rna.tf32.f32, written
+// with two full-rate integer instructions (add half an ulp to the magnitude, clear the 13 dropped bits) because
+// the conversion instruction issues at a fraction of that rate and the converter warps are on the critical path.
 __device__ __forceinline__ float tf32_rna(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
 }
 
 __device__ __forceinline__ void split4(const float4& x, float4& hi, float4& lo) {
@@ -290,8 +291,7 @@ namespace {
 template <typename OutT, bool kBmn>
 int launch_fused(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t stream) {
   auto kern = gemm_f32_fused_kernel<OutT, kBmn>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedCfg::DYN_SMEM) != cudaSuccess)
-    return SX_ERR_DRIVER;
+  SX_ENSURE_DYN_SMEM(kern, FusedCfg::DYN_SMEM);
   kern<<<grid, FusedCfg::THREADS, FusedCfg::DYN_SMEM, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
 }

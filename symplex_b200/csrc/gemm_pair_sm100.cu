@@ -381,8 +381,7 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const DstMaps& d
                 cudaStream_t stream) {
   using Cfg = PairCfg<kMB>;
   auto kern = gemm_pair_kernel<OutT, kBmn, kMB>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::DYN_SMEM) != cudaSuccess)
-    return SX_ERR_DRIVER;
+  SX_ENSURE_DYN_SMEM(kern, Cfg::DYN_SMEM);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   cfg.blockDim = dim3(Cfg::THREADS, 1, 1);

@@ -227,16 +227,7 @@ template <typename OutT, int kBN, bool kBmn, int kKind>
 int launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t stream) {
   using Cfg = TileCfg<kBN, kKind>;
   auto kern = gemm_tc_kernel<OutT, kBN, kBmn, kKind>;
-  static thread_local int configured_dev[16] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 16 && !configured_dev[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::DYN_SMEM) != cudaSuccess)
-      return SX_ERR_DRIVER;
-    configured_dev[dev] = 1;
-  } else if (dev >= 16) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::DYN_SMEM);
-  }
+  SX_ENSURE_DYN_SMEM(kern, Cfg::DYN_SMEM);
   kern<<<grid, 192, Cfg::DYN_SMEM, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
 }

@@ -242,8 +242,7 @@ template <typename OutT, int kBN>
 int launch_x3(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t stream) {
   using Cfg = X3Cfg<kBN>;
   auto kern = gemm_tf32x3_kernel<OutT, kBN>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::DYN_SMEM) != cudaSuccess)
-    return SX_ERR_DRIVER;
+  SX_ENSURE_DYN_SMEM(kern, Cfg::DYN_SMEM);
   kern<<<grid, 192, Cfg::DYN_SMEM, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
 }

@@ -5,6 +5,22 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
+
+// Raise a kernel's dynamic shared-memory limit once per device. The static lives at the expansion site, i.e.
+// once per template instantiation of the launcher that uses it.
+#define SX_ENSURE_DYN_SMEM(kern, bytes)                                                                        \
+  do {                                                                                                         \
+    static std::atomic<uint32_t> done__{0};                                                                    \
+    int dev__ = 0;                                                                                             \
+    cudaGetDevice(&dev__);                                                                                     \
+    if (dev__ < 0 || dev__ >= 32 || !((done__.load(std::memory_order_relaxed) >> dev__) & 1u)) {                \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)       \
+        return SX_ERR_DRIVER;                                                                                  \
+      if (dev__ >= 0 && dev__ < 32) done__.fetch_or(1u << dev__);                                              \
+    }                                                                                                          \
+  } while (0)
+
 namespace sx {
 
 // Status codes returned through the C ABI. They mirror the failure classes of the reference's
