@@ -49,14 +49,16 @@ DEFAULT_WORKLOAD = "cfg5_row_sharded_bf16_65536x8192x8192"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (absent where no capture of that workload exists).
-#   bf16 pair kernel, 8192 x 8192 x 8192: 881.65 MB read + 120.29 MB written (profiles/gemm_pair_kernel_bf16_8192_cube_bias_gelu.md).
+#   bf16 pair kernel, 8192 x 8192 x 8192: 882.17 MB read + 119.91 MB written (profiles/gemm_pair_kernel_bf16_8192_cube_bias_gelu.md).
 #   Its traffic is proportional to the rows of A per launch (B is re-streamed once per band of 2048 rows, A and C
 #   are touched once), so the row-sharded workload scales that capture by rows / 8192.
 #   fp32 3xTF32 kernel, 4096^3: 1103.19 MB + 62.13 MB (profiles/gemm_tf32x3_kernel_fp32_4096_cube.md).
-NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192 = 881.65e6 + 120.29e6
+NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192 = 882.17e6 + 119.91e6
 NCU_TRAFFIC_BYTES = {
     "headline_bf16_8192_cube_bias_gelu": NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192,
     "cfg2_fp32_4096_cube_colmajor_b": 1103.19e6 + 62.13e6,
+    # fused fp32 kernel, 2048 x 64^3: 67.19 MB read + 5.14 MB written (C stays in L2 during the launch)
+    "cfg4_batched_fp32_2048x64_cube": 67.19e6 + 5.14e6,
 }
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
