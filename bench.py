@@ -61,6 +61,16 @@ NCU_TRAFFIC_BYTES = {
     "cfg4_batched_fp32_2048x64_cube": 67.19e6 + 5.14e6,
 }
 
+# Fused elementwise chains (single HBM pass; not GEMMs): (op, lhs_src, lhs_idx, rhs_src, rhs_idx) programs of the
+# reference's FusedOpDesc form. "axpb_sum" is the chain the reference's own comment uses as its example
+# (x * 2.0 + 1.0 -> sum over an 800 MB array).
+ELEMENTWISE_WORKLOADS = {
+    "f3_fused_axpb_sum_200M": dict(n=200_000_000, n_inputs=1, ops=[(2, 0, 0, 1, 0), (0, 2, 0, 1, 1)],
+                                   consts=[2.0, 1.0], reduce_op=0, desc="sum(x * 2.0 + 1.0)"),
+    "f3_fused_mul_add_relu_64M": dict(n=64 << 20, n_inputs=3, ops=[(2, 0, 0, 0, 1), (0, 2, 0, 0, 2), (15, 2, 1, 0, 0)],
+                                      consts=[], reduce_op=255, desc="dst = relu(a * b + c)"),
+}
+
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -188,13 +198,182 @@ def cpu_rows_for(w, seconds=3.0, gflops_guess=5.0):
 
 
 # ----------------------------------------------------------------------------- main
+# ----------------------------------------------------------------------------- fused elementwise workloads
+def _elementwise_cpu(w, n_sample, steps, warmup):
+    """GB/s of the CPU restatement of the reference's interpreter (oracle port, 1 thread) on n_sample elements."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from oracle_loader import load_oracle
+    orc = load_oracle()
+    rng = np.random.default_rng(0)
+    arrays = [rng.uniform(-1, 1, n_sample).astype(np.float32) for _ in range(w["n_inputs"])]
+    for _ in range(max(1, warmup)):
+        orc.fused_elementwise(w["ops"], arrays, w["consts"], reduce_op=w["reduce_op"])
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        orc.fused_elementwise(w["ops"], arrays, w["consts"], reduce_op=w["reduce_op"])
+    dt = (time.perf_counter() - t0) / steps
+    streams = w["n_inputs"] + (0 if w["reduce_op"] != 255 else 1)
+    sample = (f"{n_sample} of {w['n']} elements, C restatement of the reference's fused_elem_f32_avx2_core "
+              "(scalar code, 1 thread; the reference runs the same chain 8 lanes wide on 1 thread)")
+    return 4.0 * streams * n_sample / dt / 1e9, dt, sample
+
+
+def main_elementwise(args):
+    w = ELEMENTWISE_WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    n, reduce = w["n"], w["reduce_op"] != 255
+    streams = w["n_inputs"] + (0 if reduce else 1)
+    algo_bytes = 4.0 * streams * n
+    config = {"workload": args.workload, "chain": w["desc"], "elements": n, "inputs": w["n_inputs"],
+              "output": "scalar (f64)" if reduce else "f32 array", "partition": "replicas only",
+              "l2": f"arrays of {4 * n / 1e6:.0f} MB each, larger than L2"}
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        gbs, dt, sample = _elementwise_cpu(w, 16 << 20, args.steps, args.warmup)
+        line = {"impl": "reference", "metric": "fused_elementwise_gbps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample},
+                "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line), flush=True)
+        return 0
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import symplex_b200 as sx
+    from symplex_b200 import _capi, _symplex_core
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks, peak_note = load_peaks()
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    arrays = [torch.rand(n, device=dev, generator=g) * 2 - 1 for _ in range(w["n_inputs"])]
+    out = None if reduce else torch.empty(n, device=dev)
+
+    # Arguments of the C-ABI call are packed once: a step is then one library call = one kernel launch, with
+    # a few microseconds of host work (the kernels run 0.1-0.2 ms, so per-step Python work would show).
+    lib = _capi.load()
+    c_ops = _capi.pack_fused_ops(w["ops"])
+    c_ptrs = (ctypes.c_void_p * len(arrays))(*[a.data_ptr() for a in arrays])
+    c_consts = (ctypes.c_float * max(len(w["consts"]), 1))(*w["consts"])
+    res = torch.zeros((), device=dev, dtype=torch.float64) if reduce else out
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def step():
+        rc = lib.symplex_b200_fused_elementwise_f32(c_ops, len(w["ops"]), c_ptrs, len(arrays), c_consts, len(w["consts"]),
+                                                    n, w["reduce_op"], None if reduce else out.data_ptr(),
+                                                    res.data_ptr() if reduce else None, stream)
+        if rc != 0:
+            raise SystemExit(f"fused elementwise failed: {_capi.last_error()}")
+        return res
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0 = sx.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sx.sync_status()
+    elapsed_ms = e0.elapsed_time(e1)
+    launches = sx.launch_count() - launches0
+    if sampler and elapsed_ms < 1500:  # keep the kernel running long enough for nvidia-smi to sample it under load
+        t_end = time.perf_counter() + 1.5
+        while time.perf_counter() < t_end:
+            step()
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    t = torch.tensor([elapsed_ms, float(launches)], device=dev, dtype=torch.float64)
+    if world > 1:
+        tmax, tsum = t.clone(), t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        elapsed_ms, launches = tmax[0].item(), int(tsum[1].item())
+    ms_per_step = elapsed_ms / args.steps
+    value = algo_bytes * world / (ms_per_step * 1e-3) / 1e9
+
+    # End to end through the reference-shaped host entry point: pinned host arrays in, host array / scalar out.
+    e2e = None
+    if not args.no_e2e:
+        host = [torch.empty(n, dtype=torch.float32).pin_memory() for _ in range(w["n_inputs"])]
+        for h, a in zip(host, arrays):
+            h.copy_(a)
+        hout = None if reduce else torch.empty(n, dtype=torch.float32).pin_memory()
+        ptrs = [h.data_ptr() for h in host]
+
+        def host_step():
+            return _symplex_core.simd_fused_elementwise_f32(w["ops"], ptrs, w["consts"], n, w["reduce_op"],
+                                                            0 if reduce else hout.data_ptr())
+        host_step()
+        reps = max(2, min(args.steps, 5))
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            hv = host_step()
+        dt = (time.perf_counter() - t0) / reps
+        tt = torch.tensor([dt], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = tt.item()
+        e2e = {"value": algo_bytes * world / dt / 1e9, "unit": "GB/s", "ms_per_step": dt * 1e3,
+               "h2d_bytes_per_step": 4 * n * w["n_inputs"], "d2h_bytes_per_step": 8 if reduce else 4 * n,
+               "api": "symplex_simd_fused_elementwise_f32 (pinned host arrays, chunked copy/compute/copy pipeline)"}
+        if reduce:
+            e2e["result"] = hv
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+    ach = algo_bytes / (ms_per_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": ach, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
+                "frac": ach / float(peaks["hbm_gbs"]), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                "kernel_ms": ms_per_step, "peak_kind": f"HBM copy, {peak_note}", "bytes_per_launch": algo_bytes,
+                "note": "one step = one launch of fused_elementwise_ring_kernel"}
+    cpu_baseline = None
+    if not args.no_cpu_baseline and world == 1:
+        gbs, dt, sample = _elementwise_cpu(w, 16 << 20, steps=3, warmup=1)
+        cpu_baseline = {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample}
+    line = {"metric": "fused_elementwise_gbps", "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "roofline": roofline,
+            "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks}
+    if reduce:
+        line["result"] = float(res.item())
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="symplex_b200", choices=["symplex_b200", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(ELEMENTWISE_WORKLOADS))
     ap.add_argument("--chunks", type=int, default=None, help="row chunks per rank for the NCCL all-gather pipeline")
     ap.add_argument("--exchange", default=None, choices=["peer_store", "nccl"],
                     help="how C is all-gathered at N > 1 (default: fused peer stores from the GEMM epilogue)")
@@ -203,6 +382,8 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3 and args.impl != "reference":
         args.warmup = 3  # timing rule: at least 3 warm-up steps
+    if args.workload in ELEMENTWISE_WORKLOADS:
+        return main_elementwise(args)
 
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))

@@ -188,6 +188,60 @@ int symplex_cuda_device_info(symplex_device_info* out);
 /* Kernels launched by this library on the calling process since load (all threads). */
 uint64_t symplex_b200_launch_count(void);
 
+/* ---- fused elementwise programs (optional reduction) ------------------------------------------ */
+
+/* FusedOpDesc of the reference, #[repr(C)], 8 bytes (rust-engine/src/x86_emitter.rs:1937-1953).
+ * op: 0 add, 1 sub, 2 mul, 3 div, 4 min, 5 max, 6 neg, 7 abs, 8 sqrt, 9 exp, 10 log, 11 sin, 12 cos, 13 tanh,
+ * 14 sigmoid, 15 relu (6..15 unary: rhs ignored; other codes pass lhs through).
+ * lhs_src / rhs_src: 0 input array, 1 constant, 2 result of an earlier op; *_idx indexes that source.
+ * As in the reference, an input or constant index out of range reads as 0; so does a reference to an op
+ * that has not run yet. */
+typedef struct symplex_fused_op {
+  uint8_t op;
+  uint8_t lhs_src;
+  uint16_t lhs_idx;
+  uint8_t rhs_src;
+  uint8_t reserved;
+  uint16_t rhs_idx;
+} symplex_fused_op;
+
+#define SYMPLEX_REDUCE_SUM 0
+#define SYMPLEX_REDUCE_MAX 1
+#define SYMPLEX_REDUCE_MIN 2
+#define SYMPLEX_REDUCE_NONE 255
+
+/* x86_emitter::simd_fused_elementwise_f32 / _symplex_core.simd_fused_elementwise_f32
+ * (rust-engine/src/x86_emitter.rs:2442-2470, python/src/lib.rs:1686-1695): evaluate the op chain over n
+ * elements of HOST arrays in one pass. reduce_op 255: the last op's values are written to dst_ptr and 0.0 is
+ * returned; 0 / 1 / 2: their sum / max / min is returned and dst_ptr is not touched. n == 0 or an empty chain
+ * returns 0.0. There is no error channel in the reference; on failure this returns NaN and
+ * symplex_b200_last_error() says why. Limits: 1024 ops, 16 distinct input arrays, 16 values alive at once.
+ * Difference from the reference, on purpose: for max / min with n not a multiple of 8 the reference ADDS the
+ * maximum of the vector part and the maximum of the scalar tail (x86_emitter.rs:2347); this returns the
+ * true maximum / minimum. */
+double symplex_simd_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_ops, const float* const* input_ptrs,
+                                          size_t n_inputs, const float* constants, size_t n_constants, size_t n,
+                                          uint8_t reduce_op, float* dst_ptr);
+
+/* Same computation on DEVICE arrays, asynchronous on `stream`. `result` (device double, 8-byte aligned)
+ * receives the reduced value when reduce_op != 255; `dst` receives the values otherwise and may alias an
+ * input. Arrays that are all 16-byte aligned take the bulk-copy kernel, others a plain-load kernel.
+ * No counterpart in the reference (its GPU path copies host arrays per call, cuda_backend.rs:1420-1455). */
+int symplex_b200_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_ops, const float* const* inputs,
+                                       size_t n_inputs, const float* constants, size_t n_constants, int64_t n,
+                                       int reduce_op, float* dst, double* result, void* stream);
+
+/* cuda_backend::cuda_elementwise / symplex_engine.cuda_elementwise_raw (rust-engine/src/cuda_backend.rs:1420-1455,
+ * rust-engine/src/lib.rs:1597-1626): dst[i] = a[i] <op> b[i] on host arrays, op 0 add, 1 sub, 2 mul, 3 div,
+ * 4 min, 5 max. Returns 0, -1 on a CUDA error, -2 for an unknown op. */
+int64_t symplex_cuda_elementwise(const float* a, const float* b, float* dst, int64_t n, int op);
+
+/* Host-only: compile a chain and report how many slots of the per-thread slot file it needs and how many
+ * distinct input arrays it reads. Returns SYMPLEX_ERR_INVALID for chains outside the limits above.
+ * Needs no GPU. */
+int symplex_b200_fused_program_info(const symplex_fused_op* ops, size_t n_ops, size_t n_inputs, int* n_slots,
+                                    int* n_inputs_used);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

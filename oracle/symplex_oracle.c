@@ -14,7 +14,8 @@
  * Pinning: checked by tests/test_oracle.py against every known-answer vector the reference's own
  * tests hold for this path (2x2 product, I4.B = B, the (7i+13)%97 / (11i+17)%89 pattern against a
  * scalar triple loop, gelu(0)=0) and against the reference's own kernels/matmul.c compiled unchanged
- * into oracle/_ref/. bf16-input, GELU-fused and batched results have no vector in the reference:
+ * into oracle/_ref/. The fused elementwise chain (last section) has no vector in the reference's tests
+ * either: parity unpinned, restated from the Rust source. bf16-input, GELU-fused and batched results have no vector in the reference:
  * parity for those is unpinned by the reference and rests on this restatement alone.
  */
 #include <math.h>
@@ -308,6 +309,131 @@ void oracle_matmul_jit_order_rows(const float* A, const float* B, float* Crows, 
 }
 
 /* Host cores available to this process. */
+/* ---- fused elementwise chain with optional reduction --------------------------------------------
+ * Restates fused_elem_f32_avx2_core (rust-engine/src/x86_emitter.rs:2027-2351): the op chain is evaluated
+ * per element with separately rounded fp32 operations (ops 0-5 are vaddps/vsubps/vmulps/vdivps/vminps/
+ * vmaxps, ops 6-15 go lane by lane through apply_unop_f32, :1981-1996, i.e. libm). The reduction keeps the
+ * reference's accumulator structure: four 8-lane fp32 accumulators over blocks of 32 elements (:2044-2166),
+ * accumulator 0 for the remaining blocks of 8 (:2169-2233), an f64 scalar for the last n mod 8 elements
+ * (:2236-2295), then acc0+acc1, +acc2, +acc3 and the three shuffle steps (:2298-2344), and finally
+ * "result as f64 + scalar_acc" (:2347) - which for max / min with a tail ADDS the two partial extrema; the
+ * restatement keeps that so it is the reference's answer, and `exact` = 1 asks for the true extremum instead.
+ * Operand rules: input / constant index out of range reads 0.0; a reference to op j >= the current op
+ * reads 0.0 here (the scalar tail's rule, :2239; the vector body would read a stale value). */
+typedef struct {
+  uint8_t op, lhs_src;
+  uint16_t lhs_idx;
+  uint8_t rhs_src, pad_;
+  uint16_t rhs_idx;
+} oracle_fused_op;
+
+static float fe_unop(uint8_t op, float v) {
+  switch (op) {
+    case 6: return -v;
+    case 7: return fabsf(v);
+    case 8: return sqrtf(v);
+    case 9: return expf(v);
+    case 10: return logf(v);
+    case 11: return sinf(v);
+    case 12: return cosf(v);
+    case 13: return tanhf(v);
+    case 14: { float e = expf(-v); float d = 1.0f + e; return 1.0f / d; }
+    case 15: return v > 0.0f ? v : 0.0f; /* f32::max(0.0): NaN -> 0 */
+    default: return v;
+  }
+}
+
+static float fe_element(const oracle_fused_op* ops, int64_t n_ops, const float* const* in, int64_t n_in,
+                        const float* consts, int64_t n_consts, int64_t i, float* tmp) {
+  for (int64_t o = 0; o < n_ops; ++o) {
+    float v[2];
+    for (int side = 0; side < 2; ++side) {
+      const uint8_t src = side ? ops[o].rhs_src : ops[o].lhs_src;
+      const uint16_t idx = side ? ops[o].rhs_idx : ops[o].lhs_idx;
+      float x = 0.0f;
+      if (src == 0) x = idx < n_in ? in[idx][i] : 0.0f;
+      else if (src == 1) x = idx < n_consts ? consts[idx] : 0.0f;
+      else if (src == 2) x = idx < o ? tmp[idx] : 0.0f;
+      v[side] = x;
+    }
+    float r;
+    if (ops[o].op >= 6) r = fe_unop(ops[o].op, v[0]);
+    else switch (ops[o].op) {
+      case 0: r = v[0] + v[1]; break;
+      case 1: r = v[0] - v[1]; break;
+      case 2: r = v[0] * v[1]; break;
+      case 3: r = v[0] / v[1]; break;
+      case 4: r = v[0] < v[1] ? v[0] : v[1]; break; /* vminps: second operand unless first is smaller */
+      default: r = v[0] > v[1] ? v[0] : v[1]; break;
+    }
+    tmp[o] = r;
+  }
+  return tmp[n_ops - 1];
+}
+
+static float fe_red(int reduce_op, float a, float b) {
+  if (reduce_op == 0) return a + b;
+  if (reduce_op == 1) return a > b ? a : b; /* vmaxps(acc, v) */
+  return a < b ? a : b;
+}
+
+double oracle_fused_elementwise_f32(const oracle_fused_op* ops, int64_t n_ops, const float* const* in, int64_t n_in,
+                                    const float* consts, int64_t n_consts, int64_t n, int reduce_op, float* dst,
+                                    int exact) {
+  if (n <= 0 || n_ops <= 0) return 0.0;
+  float* tmp = (float*)malloc(sizeof(float) * (size_t)n_ops);
+  const int has_reduce = reduce_op != 255;
+  const float init = reduce_op == 1 ? -INFINITY : reduce_op == 2 ? INFINITY : 0.0f;
+  float acc[4][8];
+  for (int a = 0; a < 4; ++a) for (int l = 0; l < 8; ++l) acc[a][l] = init;
+  int64_t i = 0;
+  const int64_t n32 = n & ~(int64_t)31, n8 = n & ~(int64_t)7;
+  for (; i < n32; i += 32)
+    for (int u = 0; u < 4; ++u)
+      for (int l = 0; l < 8; ++l) {
+        const int64_t e = i + u * 8 + l;
+        const float v = fe_element(ops, n_ops, in, n_in, consts, n_consts, e, tmp);
+        if (has_reduce) acc[u][l] = fe_red(reduce_op, acc[u][l], v);
+        else dst[e] = v;
+      }
+  for (; i < n8; i += 8)
+    for (int l = 0; l < 8; ++l) {
+      const float v = fe_element(ops, n_ops, in, n_in, consts, n_consts, i + l, tmp);
+      if (has_reduce) acc[0][l] = fe_red(reduce_op, acc[0][l], v);
+      else dst[i + l] = v;
+    }
+  double scalar_acc = 0.0;
+  int first = 1;
+  for (; i < n; ++i) {
+    const float v = fe_element(ops, n_ops, in, n_in, consts, n_consts, i, tmp);
+    if (!has_reduce) { dst[i] = v; continue; }
+    if (reduce_op == 0) scalar_acc += (double)v;
+    else if (first) scalar_acc = (double)v;
+    else if (reduce_op == 1) scalar_acc = scalar_acc > (double)v ? scalar_acc : (double)v;
+    else scalar_acc = scalar_acc < (double)v ? scalar_acc : (double)v;
+    first = 0;
+  }
+  free(tmp);
+  if (!has_reduce) return 0.0;
+  float a0[8];
+  for (int l = 0; l < 8; ++l) {
+    float t = fe_red(reduce_op, acc[0][l], acc[1][l]);
+    t = fe_red(reduce_op, t, acc[2][l]);
+    a0[l] = fe_red(reduce_op, t, acc[3][l]);
+  }
+  float s1[4], s2[2];
+  for (int l = 0; l < 4; ++l) s1[l] = fe_red(reduce_op, a0[l], a0[l + 4]); /* swap 128-bit halves */
+  for (int l = 0; l < 2; ++l) s2[l] = fe_red(reduce_op, s1[l], s1[l + 2]); /* shuffle 0x4E */
+  const float r = fe_red(reduce_op, s2[0], s2[1]);                         /* shuffle 0xB1 */
+  if (exact && reduce_op != 0) {
+    if (first) return (double)r;      /* no tail */
+    if (n8 == 0) return scalar_acc;   /* tail only */
+    return reduce_op == 1 ? ((double)r > scalar_acc ? (double)r : scalar_acc)
+                          : ((double)r < scalar_acc ? (double)r : scalar_acc);
+  }
+  return (double)r + scalar_acc;
+}
+
 int oracle_max_threads(void) {
   long n = sysconf(_SC_NPROCESSORS_ONLN);
   return n > 0 ? (int)n : 1;

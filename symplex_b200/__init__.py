@@ -25,7 +25,7 @@ from ._capi import (ACT_GELU, ACT_NONE, ACT_RELU, ACT_SIGMOID, ACT_SILU, ACT_TAN
 
 __all__ = [
     "matmul_jit", "matmul_tiled", "matmul", "fused_matmul_bias_relu", "gemm", "gemm_host", "make_desc",
-    "cuda_available", "launch_count", "SymplexB200Error",
+    "cuda_available", "launch_count", "SymplexB200Error", "fused_elementwise",
 ]
 
 
@@ -203,3 +203,41 @@ def sync_status(stream=None) -> None:
     import torch
     s = stream if stream is not None else torch.cuda.current_stream().cuda_stream
     _capi.check(_capi.load().symplex_b200_sync_status(s))
+
+
+def fused_elementwise(ops, inputs, constants=(), *, reduce_op=_capi.REDUCE_NONE, out=None, stream=None):
+    """Run a fused op chain (the reference's ``FusedOpDesc`` program, ``rust-engine/src/x86_emitter.rs:1937-1953``)
+    over CUDA ``float32`` tensors of equal size in one kernel.
+
+    ``ops``: ``[(op, lhs_src, lhs_idx, rhs_src, rhs_idx), ...]``. With ``reduce_op`` 255 returns the result
+    tensor (``out`` or a new one, shaped like ``inputs[0]``); with 0 / 1 / 2 returns a 0-d ``float64`` CUDA
+    tensor holding the sum / max / min. Asynchronous on ``stream`` (default: torch's current stream).
+    """
+    import torch
+
+    if not inputs:
+        raise ValueError("fused_elementwise() needs at least one input tensor")
+    n = inputs[0].numel()
+    for t in inputs:
+        if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n:
+            raise ValueError("inputs must be contiguous CUDA float32 tensors of equal size")
+    dev = inputs[0].device
+    arr = _capi.pack_fused_ops(ops)
+    ptrs = (ctypes.c_void_p * len(inputs))(*[t.data_ptr() for t in inputs])
+    consts = (ctypes.c_float * max(len(constants), 1))(*[float(c) for c in constants])
+    reduce = reduce_op != _capi.REDUCE_NONE
+    if reduce:
+        res = torch.zeros((), device=dev, dtype=torch.float64)
+        dst_ptr, res_ptr = None, res.data_ptr()
+    else:
+        if out is None:
+            out = torch.empty_like(inputs[0])
+        elif not out.is_cuda or out.dtype != torch.float32 or not out.is_contiguous() or out.numel() != n:
+            raise ValueError("out must be a contiguous CUDA float32 tensor of the inputs' size")
+        dst_ptr, res_ptr = out.data_ptr(), None
+    s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
+    with torch.cuda.device(dev):
+        rc = _capi.load().symplex_b200_fused_elementwise_f32(arr, len(ops), ptrs, len(inputs), consts, len(constants), n,
+                                                             int(reduce_op), dst_ptr, res_ptr, s)
+    _capi.check(rc)
+    return res if reduce else out

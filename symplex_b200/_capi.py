@@ -7,7 +7,8 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
+from ctypes import (c_char, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_size_t, c_uint8, c_uint16, c_uint64,
+                    c_void_p)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libsymplex_b200.so")
@@ -46,6 +47,14 @@ class DeviceInfo(ctypes.Structure):
     ]
 
 
+class FusedOp(ctypes.Structure):
+    """``symplex_fused_op`` (the reference's ``FusedOpDesc``, 8 bytes)."""
+    _fields_ = [("op", c_uint8), ("lhs_src", c_uint8), ("lhs_idx", c_uint16), ("rhs_src", c_uint8),
+                ("reserved", c_uint8), ("rhs_idx", c_uint16)]
+
+
+REDUCE_SUM, REDUCE_MAX, REDUCE_MIN, REDUCE_NONE = 0, 1, 2, 255
+
 _F32P = c_void_p  # raw addresses; callers pass ints (numpy ``.ctypes.data`` / torch ``.data_ptr()``)
 
 # name -> (restype, argtypes): every symbol include/symplex_b200.h declares.
@@ -74,7 +83,23 @@ SIGNATURES = {
     "symplex_cuda_available": (c_int, []),
     "symplex_cuda_device_info": (c_int, [ctypes.POINTER(DeviceInfo)]),
     "symplex_b200_launch_count": (c_uint64, []),
+    "symplex_simd_fused_elementwise_f32": (c_double, [ctypes.POINTER(FusedOp), c_size_t, ctypes.POINTER(c_void_p), c_size_t,
+                                                      ctypes.POINTER(c_float), c_size_t, c_size_t, c_uint8, _F32P]),
+    "symplex_b200_fused_elementwise_f32": (c_int, [ctypes.POINTER(FusedOp), c_size_t, ctypes.POINTER(c_void_p), c_size_t,
+                                                   ctypes.POINTER(c_float), c_size_t, c_int64, c_int, _F32P, c_void_p,
+                                                   c_void_p]),
+    "symplex_cuda_elementwise": (c_int64, [_F32P, _F32P, _F32P, c_int64, c_int]),
+    "symplex_b200_fused_program_info": (c_int, [ctypes.POINTER(FusedOp), c_size_t, c_size_t, ctypes.POINTER(c_int),
+                                                ctypes.POINTER(c_int)]),
 }
+
+
+def pack_fused_ops(ops):
+    """``[(op, lhs_src, lhs_idx, rhs_src, rhs_idx), ...]`` -> a ctypes array of ``FusedOp``."""
+    arr = (FusedOp * max(len(ops), 1))()
+    for i, (op, ls, li, rs, ri) in enumerate(ops):
+        arr[i] = FusedOp(int(op), int(ls), int(li), int(rs), 0, int(ri))
+    return arr
 
 _lib = None
 

@@ -63,3 +63,23 @@ def cuda_info() -> str:
         return f"CUDA not available: {d['error']}"
     return (f"{d['name']} ({d['sm_arch']}, {d['num_sms']} SMs, {d['total_memory_gb']:.1f} GB): "
             "symplex_b200 tcgen05 GEMM library")
+
+
+def simd_fused_elementwise_f32(ops, input_ptrs, constants, n: int, reduce_op: int, dst_ptr: int) -> float:
+    """``python/src/lib.rs:1686-1695``: run a fused op chain over ``n`` elements of host ``float32`` arrays.
+
+    ``ops`` is a list of ``(op, lhs_src, lhs_idx, rhs_src, rhs_idx)``; ``input_ptrs`` are host addresses as
+    ints; ``reduce_op`` 0 / 1 / 2 returns the sum / max / min, 255 writes to ``dst_ptr`` and returns 0.0.
+    One GPU pass per chunk of the arrays (single kernel: loads, the whole chain, store or reduction).
+    """
+    import ctypes
+    import math
+    lib = _capi.load()
+    arr = _capi.pack_fused_ops(ops)
+    ptrs = (ctypes.c_void_p * max(len(input_ptrs), 1))(*[int(p) for p in input_ptrs])
+    consts = (ctypes.c_float * max(len(constants), 1))(*[float(c) for c in constants])
+    v = lib.symplex_simd_fused_elementwise_f32(arr, len(ops), ptrs, len(input_ptrs), consts, len(constants), int(n),
+                                               int(reduce_op), int(dst_ptr) if dst_ptr else None)
+    if math.isnan(v) and _capi.last_error() != "no error":
+        raise _capi.SymplexB200Error(_capi.ERR_EXEC, _capi.last_error())
+    return float(v)

@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 #include <mutex>
 
 #include "../../include/symplex_b200.h"
@@ -84,8 +85,11 @@ struct DeviceState {
   int* status = nullptr;  // device word written by kernels that unwind
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  char* fe_scratch = nullptr;  // FE_SCRATCH_SETS reduction scratch areas of the fused elementwise kernels
+  std::atomic<unsigned> fe_next{0};
 };
 static DeviceState g_dev[16];
+constexpr int FE_SCRATCH_SETS = 8;
 
 static int device_state(DeviceState** out) {
   int dev = 0;
@@ -100,6 +104,8 @@ static int device_state(DeviceState** out) {
     SX_CUDA(cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev));
     SX_CUDA(cudaMalloc(&st.status, sizeof(int)));
     SX_CUDA(cudaMemset(st.status, 0, sizeof(int)));
+    SX_CUDA(cudaMalloc(&st.fe_scratch, FE_SCRATCH_SETS * FE_REDUCE_SCRATCH_BYTES));
+    SX_CUDA(cudaMemset(st.fe_scratch, 0, FE_SCRATCH_SETS * FE_REDUCE_SCRATCH_BYTES));
     st.ready = true;
   }
   *out = &st;
@@ -338,8 +344,8 @@ struct HostCtx {
   cudaStream_t h2d = nullptr, d2h = nullptr;      // copy streams of the row-chunked pipeline
   cudaEvent_t ev_in[64] = {}, ev_out[64] = {};    // chunk c: inputs landed / result ready
   bool pipeline_ready = false;
-  void* buf[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};  // A, B, C, bias, residual
-  size_t cap[5] = {0, 0, 0, 0, 0};
+  void* buf[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // A, B, C, bias, residual, elementwise arena
+  size_t cap[6] = {0, 0, 0, 0, 0, 0};
   int dev = -1;
 };
 static thread_local HostCtx t_host;
@@ -377,7 +383,7 @@ static int gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, v
   if (h.stream == nullptr || h.dev != dev) {
     SX_CUDA(cudaStreamCreateWithFlags(&h.stream, cudaStreamNonBlocking));
     h.dev = dev;
-    for (int i = 0; i < 5; ++i) { h.buf[i] = nullptr; h.cap[i] = 0; }
+    for (int i = 0; i < 6; ++i) { h.buf[i] = nullptr; h.cap[i] = 0; }
   }
   const size_t in_elt = p.f32_in ? 4 : 2, out_elt = p.bf16_out ? 2 : 4;
   // Extent of each host operand including batch strides.
@@ -498,6 +504,118 @@ static int64_t sgemm_host(const float* a, const float* b, float* c, int64_t m, i
   symplex_gemm_desc d;
   symplex_b200_gemm_desc_init(&d, m, n, k, SYMPLEX_DT_F32, SYMPLEX_DT_F32);
   return gemm_host(&d, a, b, c, nullptr, nullptr);
+}
+
+// ------------------------------------------------------------------ fused elementwise programs
+static_assert(sizeof(symplex_fused_op) == 8 && sizeof(FeSrcOp) == 8, "FusedOpDesc is 8 bytes");
+
+static void* fe_reduce_scratch(DeviceState* st) {
+  return st->fe_scratch + (st->fe_next.fetch_add(1) % FE_SCRATCH_SETS) * FE_REDUCE_SCRATCH_BYTES;
+}
+
+static int fe_device(const symplex_fused_op* ops, size_t n_ops, const float* const* inputs, size_t n_inputs,
+                     const float* constants, size_t n_constants, int64_t n, int reduce_op, float* dst, double* result,
+                     cudaStream_t stream) {
+  if (n < 0) return fail(SX_ERR_INVALID, "negative element count");
+  if (n == 0 || n_ops == 0) return SX_OK;  // the reference returns before touching anything
+  auto prog = std::make_unique<FeProgram>();
+  int rc = compile_fused_program(reinterpret_cast<const FeSrcOp*>(ops), n_ops, n_inputs, constants, n_constants,
+                                 prog.get());
+  if (rc != SX_OK) return rc;
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != SX_OK) return rc;
+  void* red = reduce_op != FE_REDUCE_NONE ? fe_reduce_scratch(st) : nullptr;
+  rc = launch_fused_elementwise(*prog, inputs, n, reduce_op, dst, result, red, st->status, st->num_sms, stream);
+  if (rc == SX_OK) ++g_launches;
+  return rc;
+}
+
+// Host arrays in, host array (or the reduced scalar) out. The element range is cut into chunks that run as a
+// three-stream pipeline: copy-in of chunk c+1, the kernel on chunk c and copy-out of chunk c-1 overlap.
+static int fe_host(const symplex_fused_op* ops, size_t n_ops, const float* const* inputs, size_t n_inputs,
+                   const float* constants, size_t n_constants, size_t n, int reduce_op, float* dst, double* value) {
+  *value = 0.0;
+  if (n == 0 || n_ops == 0) return SX_OK;
+  const bool reduce = reduce_op != FE_REDUCE_NONE;
+  if (reduce && (reduce_op < 0 || reduce_op > 2)) return fail(SX_ERR_INVALID, "reduce_op must be 0, 1, 2 or 255");
+  if (!reduce && dst == nullptr) return fail(SX_ERR_INVALID, "null dst");
+  auto prog = std::make_unique<FeProgram>();
+  int rc = compile_fused_program(reinterpret_cast<const FeSrcOp*>(ops), n_ops, n_inputs, constants, n_constants,
+                                 prog.get());
+  if (rc != SX_OK) return rc;
+  for (int i = 0; i < prog->n_inputs; ++i)
+    if (inputs == nullptr || inputs[prog->input_map[i]] == nullptr) return fail(SX_ERR_INVALID, "null input array");
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != SX_OK) return rc;
+  HostCtx& h = t_host;
+  int dev = 0;
+  SX_CUDA(cudaGetDevice(&dev));
+  if (h.stream == nullptr || h.dev != dev) {
+    SX_CUDA(cudaStreamCreateWithFlags(&h.stream, cudaStreamNonBlocking));
+    h.dev = dev;
+    for (int i = 0; i < 6; ++i) { h.buf[i] = nullptr; h.cap[i] = 0; }
+  }
+  if (!h.pipeline_ready) {
+    SX_CUDA(cudaStreamCreateWithFlags(&h.h2d, cudaStreamNonBlocking));
+    SX_CUDA(cudaStreamCreateWithFlags(&h.d2h, cudaStreamNonBlocking));
+    for (int i = 0; i < 64; ++i) {
+      SX_CUDA(cudaEventCreateWithFlags(&h.ev_in[i], cudaEventDisableTiming));
+      SX_CUDA(cudaEventCreateWithFlags(&h.ev_out[i], cudaEventDisableTiming));
+    }
+    h.pipeline_ready = true;
+  }
+  // Arena: one device array per used input, the output array, one double per chunk.
+  const int ni = prog->n_inputs;
+  const size_t arr = align256(n * sizeof(float));
+  void* arena = nullptr;
+  if ((rc = host_buf(5, arr * (size_t)(ni + 1) + 64 * sizeof(double), &arena)) != SX_OK) return rc;
+  char* base = static_cast<char*>(arena);
+  double* d_res = reinterpret_cast<double*>(base + arr * (size_t)(ni + 1));
+  size_t chunk = size_t(8) << 20;  // elements per chunk: 32 MiB per array
+  if (chunk * 64 < n) chunk = ((n + 63) / 64 + 4095) / 4096 * 4096;
+  const int nchunks = (int)((n + chunk - 1) / chunk);
+  // Device arrays are numbered like the compacted program inputs.
+  auto dprog = std::make_unique<FeProgram>(*prog);
+  for (int i = 0; i < ni; ++i) dprog->input_map[i] = i;
+  const float* d_in[FE_MAX_INPUTS] = {};
+  void* red = reduce ? fe_reduce_scratch(st) : nullptr;
+  for (int c = 0; c < nchunks; ++c) {
+    const size_t e0 = (size_t)c * chunk, cnt = (e0 + chunk <= n) ? chunk : n - e0;
+    for (int i = 0; i < ni; ++i) {
+      float* d = reinterpret_cast<float*>(base + arr * (size_t)i) + e0;
+      SX_CUDA(cudaMemcpyAsync(d, inputs[prog->input_map[i]] + e0, cnt * sizeof(float), cudaMemcpyHostToDevice, h.h2d));
+      d_in[i] = d;
+    }
+    SX_CUDA(cudaEventRecord(h.ev_in[c], h.h2d));
+    SX_CUDA(cudaStreamWaitEvent(h.stream, h.ev_in[c], 0));
+    float* d_dst = reinterpret_cast<float*>(base + arr * (size_t)ni) + e0;
+    rc = launch_fused_elementwise(*dprog, d_in, (long long)cnt, reduce_op, d_dst, d_res + c, red, st->status,
+                                  st->num_sms, h.stream);
+    if (rc != SX_OK) return rc;
+    ++g_launches;
+    if (!reduce) {
+      SX_CUDA(cudaEventRecord(h.ev_out[c], h.stream));
+      SX_CUDA(cudaStreamWaitEvent(h.d2h, h.ev_out[c], 0));
+      SX_CUDA(cudaMemcpyAsync(dst + e0, d_dst, cnt * sizeof(float), cudaMemcpyDeviceToHost, h.d2h));
+    }
+  }
+  double parts[64];
+  int status = 0;
+  if (reduce) SX_CUDA(cudaMemcpyAsync(parts, d_res, nchunks * sizeof(double), cudaMemcpyDeviceToHost, h.stream));
+  SX_CUDA(cudaMemcpyAsync(&status, st->status, sizeof(int), cudaMemcpyDeviceToHost, h.stream));
+  SX_CUDA(cudaStreamSynchronize(h.stream));
+  SX_CUDA(cudaStreamSynchronize(h.d2h));
+  if (status != 0) {
+    SX_CUDA(cudaMemset(st->status, 0, sizeof(int)));
+    return fail(SX_ERR_TIMEOUT, "device-side wait timed out (status %d)", status);
+  }
+  if (reduce) {
+    double v = parts[0];
+    for (int c = 1; c < nchunks; ++c)
+      v = reduce_op == 0 ? v + parts[c] : reduce_op == 1 ? (parts[c] > v ? parts[c] : v) : (parts[c] < v ? parts[c] : v);
+    *value = v;
+  }
+  return SX_OK;
 }
 
 }  // namespace sx
@@ -701,5 +819,46 @@ int symplex_cuda_device_info(symplex_device_info* out) {
 }
 
 uint64_t symplex_b200_launch_count(void) { return g_launches.load(); }
+
+int symplex_b200_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_ops, const float* const* inputs,
+                                       size_t n_inputs, const float* constants, size_t n_constants, int64_t n,
+                                       int reduce_op, float* dst, double* result, void* stream) {
+  return fe_device(ops, n_ops, inputs, n_inputs, constants, n_constants, n, reduce_op, dst, result,
+                   static_cast<cudaStream_t>(stream));
+}
+
+double symplex_simd_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_ops, const float* const* input_ptrs,
+                                          size_t n_inputs, const float* constants, size_t n_constants, size_t n,
+                                          uint8_t reduce_op, float* dst_ptr) {
+  double v = 0.0;
+  const int rc = fe_host(ops, n_ops, input_ptrs, n_inputs, constants, n_constants, n, reduce_op, dst_ptr, &v);
+  if (rc != SX_OK) return __builtin_nan("");
+  snprintf(g_err, sizeof(g_err), "no error");  // lets a caller tell a computed NaN from a failure
+  return v;
+}
+
+int64_t symplex_cuda_elementwise(const float* a, const float* b, float* dst, int64_t n, int op) {
+  if (n == 0) return 0;
+  if (op < 0 || op > 5) return -2;  // unknown op, like cuda_elementwise_raw
+  if (n < 0 || !a || !b || !dst) {
+    fail(SX_ERR_INVALID, "bad argument");
+    return -1;
+  }
+  const symplex_fused_op prog = {(uint8_t)op, 0, 0, 0, 0, 1};
+  const float* in[2] = {a, b};
+  double v = 0.0;
+  return fe_host(&prog, 1, in, 2, nullptr, 0, (size_t)n, FE_REDUCE_NONE, dst, &v) == SX_OK ? 0 : -1;
+}
+
+int symplex_b200_fused_program_info(const symplex_fused_op* ops, size_t n_ops, size_t n_inputs, int* n_slots,
+                                    int* n_inputs_used) {
+  auto prog = std::make_unique<FeProgram>();
+  static const float zeros[1] = {0.0f};
+  const int rc = compile_fused_program(reinterpret_cast<const FeSrcOp*>(ops), n_ops, n_inputs, zeros, 0, prog.get());
+  if (rc != SX_OK) return rc;
+  if (n_slots) *n_slots = prog->n_slots;
+  if (n_inputs_used) *n_inputs_used = prog->n_inputs;
+  return SX_OK;
+}
 
 }  // extern "C"

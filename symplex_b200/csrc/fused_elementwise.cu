@@ -1,0 +1,608 @@
+// Fused elementwise programs with an optional reduction, as one streaming pass over HBM.
+//
+// Replaces the reference's single-pass AVX2 interpreter for FusedOpDesc chains
+// (rust-engine/src/x86_emitter.rs:1937-2351, entry point simd_fused_elementwise_f32 at :2442-2470) and the
+// elementwise / fma / reduction kernels its PTX generator emits (rust-engine/src/cuda_backend.rs:220-694).
+// A program is a list of ops; each op reads two operands (an input array, a constant, or the result of an
+// earlier op) and produces one value per element. The last op's value is either stored to dst or reduced
+// (sum / max / min) to one scalar.
+//
+// The kernel is HBM-bound: every input element is read exactly once and every output element written once.
+// A producer thread streams 4 or 8 KB chunks of each input into a shared-memory ring with bulk async copies
+// (mbarrier completion), so the bytes in flight per SM are set by the ring size, not by registers; 256
+// consumer threads interpret the program out of the kernel's parameter block (constant bank, warp-uniform
+// control flow) on float4 vectors read from the ring and store results with 16-byte coalesced stores.
+// Values that are consumed by the very next op stay in registers; values with a longer life go to a small
+// per-thread slot file whose slots the host assigns by liveness. Arrays that are not 16-byte aligned take a
+// plain-load variant of the same interpreter.
+//
+// Arithmetic follows the reference op by op: add / sub / mul / div are separately rounded IEEE operations
+// (never contracted into FMAs), sqrt is correctly rounded, min / max follow the AVX2 forms
+// (l < r ? l : r and l > r ? l : r). exp, log, sin, cos, tanh use CUDA's libm (<= 2 ulp).
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#include "gemm_params.h"
+#include "host_api.h"
+#include "sm100_ptx.cuh"
+
+namespace sx {
+
+// ------------------------------------------------------------------------------------------------ host compile
+int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, const float* constants,
+                          size_t n_constants, FeProgram* out) {
+  if (ops == nullptr || n_ops == 0) return set_last_error(SX_ERR_INVALID, "empty program");
+  if (n_ops > (size_t)FE_MAX_OPS) return set_last_error(SX_ERR_INVALID, "program has more than 1024 ops");
+  if (n_constants && constants == nullptr) return set_last_error(SX_ERR_INVALID, "null constants");
+  enum : uint8_t { REF = 200 };  // temporary kind: result of an earlier op
+  struct Operand {
+    uint8_t kind;
+    uint32_t v;
+  };
+  FeProgram& P = *out;
+  P.n_ops = (int)n_ops;
+  P.n_inputs = 0;
+  P.n_slots = 0;
+  std::vector<int> compact;  // caller's input index -> compacted index, filled on first use
+  auto resolve = [&](uint8_t src, uint16_t idx, size_t i, int* err) -> Operand {
+    if (src == 0) {
+      if (idx >= n_inputs) return {FE_IMM, 0u};  // the reference substitutes zero
+      if (compact.empty()) compact.assign(n_inputs < 65536 ? n_inputs : 65536, -1);
+      if (compact[idx] < 0) {
+        if (P.n_inputs == FE_MAX_INPUTS) {
+          *err = 1;
+          return {FE_IMM, 0u};
+        }
+        compact[idx] = P.n_inputs;
+        P.input_map[P.n_inputs++] = idx;
+      }
+      return {FE_IN, (uint32_t)compact[idx]};
+    }
+    if (src == 1) {
+      uint32_t bits = 0;
+      if (idx < n_constants) memcpy(&bits, &constants[idx], 4);
+      return {FE_IMM, bits};
+    }
+    if (src == 2 && idx < i) return {REF, idx};
+    return {FE_IMM, 0u};  // forward references and unknown sources read as zero
+  };
+  std::vector<Operand> L(n_ops), R(n_ops);
+  std::vector<int> last_use(n_ops, -1), slot_of(n_ops, -1);
+  int err = 0;
+  for (size_t i = 0; i < n_ops; ++i) {
+    const bool unary = ops[i].op >= 6;
+    L[i] = resolve(ops[i].lhs_src, ops[i].lhs_idx, i, &err);
+    R[i] = unary ? Operand{FE_IMM, 0u} : resolve(ops[i].rhs_src, ops[i].rhs_idx, i, &err);
+    if (L[i].kind == REF) last_use[L[i].v] = (int)i;
+    if (R[i].kind == REF) last_use[R[i].v] = (int)i;
+  }
+  if (err) return set_last_error(SX_ERR_INVALID, "program reads more than 16 distinct input arrays");
+  int free_slots[FE_MAX_SLOTS], n_free = 0;
+  for (size_t i = 0; i < n_ops; ++i) {
+    FeOp& o = P.ops[i];
+    o.opcode = ops[i].op <= 15 ? ops[i].op : 16;  // 16: pass the left operand through
+    auto lower = [&](const Operand& x, uint8_t* kind, uint32_t* v) {
+      if (x.kind != REF) {
+        *kind = x.kind;
+        *v = x.v;
+      } else if (x.v + 1 == i) {
+        *kind = FE_LAST;
+        *v = 0;
+      } else {
+        *kind = FE_SLOT;
+        *v = (uint32_t)slot_of[x.v];
+      }
+    };
+    lower(L[i], &o.lkind, &o.l);
+    lower(R[i], &o.rkind, &o.r);
+    // Slots whose value dies here can already take this op's result: operands are read before the write.
+    auto release = [&](const Operand& x) {
+      if (x.kind == REF && last_use[x.v] == (int)i && slot_of[x.v] >= 0) {
+        free_slots[n_free++] = slot_of[x.v];
+        slot_of[x.v] = -1;
+      }
+    };
+    release(L[i]);
+    release(R[i]);
+    o.dst = FE_NO_DST;
+    if (last_use[i] > (int)i + 1) {  // used beyond the next op: needs a slot
+      int s;
+      if (n_free > 0) {
+        s = free_slots[--n_free];
+      } else if (P.n_slots < FE_MAX_SLOTS) {
+        s = P.n_slots++;
+      } else {
+        return set_last_error(SX_ERR_INVALID, "program keeps more than 16 intermediate values alive at once");
+      }
+      slot_of[i] = s;
+      o.dst = (uint8_t)s;
+    }
+  }
+  return SX_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ device side
+constexpr int FE_THREADS = 256;       // consumer threads; the ring kernel adds one producer warp
+constexpr int FE_MAX_STAGES = 16;
+
+template <int MAXOPS>
+struct FeKernelArgs {
+  long long n;
+  const float* in[FE_MAX_INPUTS];
+  float* dst;
+  double* partials;
+  unsigned* ticket;
+  double* result;
+  int* status;
+  int n_ops, reduce_op, n_inputs, stages;
+  FeOp ops[MAXOPS];
+};
+
+template <int W>
+__device__ __forceinline__ void fe_apply(uint32_t opcode, const float (&l)[W], const float (&r)[W], float (&o)[W]) {
+  switch (opcode) {
+#define FE_CASE(code, expr)                         \
+  case code:                                        \
+    _Pragma("unroll") for (int w = 0; w < W; ++w) { \
+      const float a = l[w], b = r[w];               \
+      (void)b;                                      \
+      o[w] = (expr);                                \
+    }                                               \
+    break;
+    FE_CASE(0, __fadd_rn(a, b))
+    FE_CASE(1, __fsub_rn(a, b))
+    FE_CASE(2, __fmul_rn(a, b))
+    FE_CASE(3, __fdiv_rn(a, b))
+    FE_CASE(4, (a < b) ? a : b)
+    FE_CASE(5, (a > b) ? a : b)
+    FE_CASE(6, -a)
+    FE_CASE(7, fabsf(a))
+    FE_CASE(8, __fsqrt_rn(a))
+    FE_CASE(9, expf(a))
+    FE_CASE(10, logf(a))
+    FE_CASE(11, sinf(a))
+    FE_CASE(12, cosf(a))
+    FE_CASE(13, tanhf(a))
+    FE_CASE(14, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-a))))
+    FE_CASE(15, fmaxf(a, 0.0f))
+#undef FE_CASE
+    default:
+#pragma unroll
+      for (int w = 0; w < W; ++w) o[w] = l[w];
+      break;
+  }
+}
+
+// Input loaders: hand the interpreter W values of input `idx` for this thread.
+template <int U>
+struct RingLoader {  // float4 vectors out of one ring stage; input i starts at base + i * stride
+  const float* base;
+  int stride;
+  __device__ __forceinline__ void load(uint32_t idx, float (&o)[U * 4]) const {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const float4 q = *reinterpret_cast<const float4*>(base + (size_t)idx * stride + u * (FE_THREADS * 4));
+      o[u * 4 + 0] = q.x, o[u * 4 + 1] = q.y, o[u * 4 + 2] = q.z, o[u * 4 + 3] = q.w;
+    }
+  }
+};
+template <int U>
+struct GlobalLoader {  // scalars straight from global memory at element offsets e[u]
+  const float* const* in;
+  long long e[U];
+  bool ok[U];
+  __device__ __forceinline__ void load(uint32_t idx, float (&o)[U]) const {
+    const float* p = in[idx];
+#pragma unroll
+    for (int u = 0; u < U; ++u) o[u] = ok[u] ? __ldg(p + e[u]) : 0.0f;
+  }
+};
+
+// The six exactly rounded binary ops on operand accessors (callables w -> value). `out` may be the array an
+// accessor reads: element w is read before it is written.
+template <int W, class LF, class RF>
+__device__ __forceinline__ void fe_binary(uint32_t opcode, LF lf, RF rf, float (&out)[W]) {
+  switch (opcode) {
+#define FE_BIN(code, expr)                          \
+  case code:                                        \
+    _Pragma("unroll") for (int w = 0; w < W; ++w) { \
+      const float a = lf(w), b = rf(w);             \
+      out[w] = (expr);                              \
+    }                                               \
+    break;
+    FE_BIN(0, __fadd_rn(a, b))
+    FE_BIN(1, __fsub_rn(a, b))
+    FE_BIN(2, __fmul_rn(a, b))
+    FE_BIN(3, __fdiv_rn(a, b))
+    FE_BIN(4, (a < b) ? a : b)
+    default:
+      FE_BIN(5, (a > b) ? a : b)
+#undef FE_BIN
+  }
+}
+
+// Interpret the program for W values per thread; the last op's values end up in `last`.
+// Binary arithmetic ops are dispatched on (left kind, right kind, opcode) to loops that read their operands
+// in place - registers of `last`, an immediate, a slot, or freshly loaded input values - so an op costs one
+// arithmetic instruction per element plus a warp-uniform dispatch; unary ops copy their operand first.
+template <int W, int MAXOPS, class Loader>
+__device__ __forceinline__ void fe_eval(const FeKernelArgs<MAXOPS>& P, const Loader& ld, float (&last)[W]) {
+  float slots[FE_MAX_SLOTS][W];
+#pragma unroll
+  for (int w = 0; w < W; ++w) last[w] = 0.0f;
+  for (int i = 0; i < P.n_ops; ++i) {
+    const FeOp op = P.ops[i];
+    if (op.opcode < 6) {
+      auto with_left = [&](auto lf) {
+        switch (op.rkind) {
+          case FE_IMM: {
+            const float c = __uint_as_float(op.r);
+            fe_binary<W>(op.opcode, lf, [=](int) { return c; }, last);
+          } break;
+          case FE_LAST:
+            fe_binary<W>(op.opcode, lf, [&](int w) { return last[w]; }, last);
+            break;
+          case FE_SLOT:
+            fe_binary<W>(op.opcode, lf, [&](int w) { return slots[op.r][w]; }, last);
+            break;
+          default: {
+            float t[W];
+            ld.load(op.r, t);
+            fe_binary<W>(op.opcode, lf, [&](int w) { return t[w]; }, last);
+          } break;
+        }
+      };
+      switch (op.lkind) {
+        case FE_IMM: {
+          const float c = __uint_as_float(op.l);
+          with_left([=](int) { return c; });
+        } break;
+        case FE_LAST:
+          with_left([&](int w) { return last[w]; });
+          break;
+        case FE_SLOT:
+          with_left([&](int w) { return slots[op.l][w]; });
+          break;
+        default: {
+          float t[W];
+          ld.load(op.l, t);
+          with_left([&](int w) { return t[w]; });
+        } break;
+      }
+    } else {
+      float l[W];
+      if (op.lkind == FE_IN) {
+        ld.load(op.l, l);
+      } else if (op.lkind == FE_IMM) {
+#pragma unroll
+        for (int w = 0; w < W; ++w) l[w] = __uint_as_float(op.l);
+      } else if (op.lkind == FE_LAST) {
+#pragma unroll
+        for (int w = 0; w < W; ++w) l[w] = last[w];
+      } else {
+#pragma unroll
+        for (int w = 0; w < W; ++w) l[w] = slots[op.l][w];
+      }
+      fe_apply<W>(op.opcode, l, l, last);
+    }
+    if (op.dst != FE_NO_DST) {
+#pragma unroll
+      for (int w = 0; w < W; ++w) slots[op.dst][w] = last[w];
+    }
+  }
+}
+
+__device__ __forceinline__ float fe_identity(int reduce_op) {
+  return reduce_op == 1 ? -INFINITY : reduce_op == 2 ? INFINITY : 0.0f;
+}
+__device__ __forceinline__ float fe_combine(int reduce_op, float a, float b) {
+  return reduce_op == 0 ? __fadd_rn(a, b) : reduce_op == 1 ? fmaxf(a, b) : fminf(a, b);
+}
+__device__ __forceinline__ double fe_combine(int reduce_op, double a, double b) {
+  return reduce_op == 0 ? a + b : reduce_op == 1 ? fmax(a, b) : fmin(a, b);
+}
+
+// acc[w] = combine(acc[w], v[w]) with the choice of the operation hoisted out of the element loop.
+template <int W>
+__device__ __forceinline__ void fe_accumulate(int reduce_op, float (&acc)[W], const float (&v)[W]) {
+  if (reduce_op == 0) {
+#pragma unroll
+    for (int w = 0; w < W; ++w) acc[w] = __fadd_rn(acc[w], v[w]);
+  } else if (reduce_op == 1) {
+#pragma unroll
+    for (int w = 0; w < W; ++w) acc[w] = fmaxf(acc[w], v[w]);
+  } else {
+#pragma unroll
+    for (int w = 0; w < W; ++w) acc[w] = fminf(acc[w], v[w]);
+  }
+}
+
+// Block-wide reduction in a fixed order; every thread of the block must call it. Result valid in thread 0.
+__device__ __forceinline__ double fe_block_reduce(int reduce_op, double v, double* smem) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = fe_combine(reduce_op, v, __shfl_xor_sync(0xffffffffu, v, off));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    v = lane < nw ? smem[lane] : (double)fe_identity(reduce_op);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fe_combine(reduce_op, v, __shfl_xor_sync(0xffffffffu, v, off));
+  }
+  return v;
+}
+
+// Fold the per-thread accumulators of the whole grid into *P.result: per block in a fixed order, then the
+// block that arrives last folds the per-block partials in index order - the same bits on every run.
+template <int W, int MAXOPS>
+__device__ __forceinline__ void fe_grid_reduce(const FeKernelArgs<MAXOPS>& P, const float (&acc)[W]) {
+  __shared__ double red[32];
+  __shared__ bool is_last;
+  double v = (double)acc[0];
+#pragma unroll
+  for (int w = 1; w < W; ++w) v = fe_combine(P.reduce_op, v, (double)acc[w]);
+  v = fe_block_reduce(P.reduce_op, v, red);
+  if (threadIdx.x == 0) {
+    P.partials[blockIdx.x] = v;
+    __threadfence();
+    is_last = atomicAdd(P.ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    double s = (double)fe_identity(P.reduce_op);
+    for (unsigned i = threadIdx.x; i < gridDim.x; i += blockDim.x) s = fe_combine(P.reduce_op, s, __ldcg(P.partials + i));
+    s = fe_block_reduce(P.reduce_op, s, red);
+    if (threadIdx.x == 0) {
+      *P.result = s;
+      *P.ticket = 0u;
+    }
+  }
+}
+
+// Elements [first, n) one per thread with plain loads: the whole array when it is not 16-byte aligned,
+// otherwise what is left after the last full chunk.
+template <int MAXOPS>
+__device__ __forceinline__ void fe_scalar_range(const FeKernelArgs<MAXOPS>& P, long long first, long long gtid,
+                                                long long nthreads, bool reduce, float& acc) {
+  for (long long t = first + gtid; t < P.n; t += nthreads) {
+    GlobalLoader<1> ld;
+    ld.in = P.in;
+    ld.e[0] = t;
+    ld.ok[0] = true;
+    float r1[1];
+    fe_eval<1, MAXOPS>(P, ld, r1);
+    if (reduce)
+      acc = fe_combine(P.reduce_op, acc, r1[0]);
+    else
+      P.dst[t] = r1[0];
+  }
+}
+
+// Ring kernel. Shared memory: [0,128) full barriers, [128,256) empty barriers, then `stages` stages of
+// n_inputs x CHUNK floats. Chunk c of the arrays goes to CTA c mod gridDim.x.
+template <int U, int MAXOPS>
+__global__ void __launch_bounds__(FE_THREADS + 32) fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<MAXOPS> P) {
+  constexpr int W = U * 4;
+  constexpr int CHUNK = FE_THREADS * W;  // floats per input per stage
+  extern __shared__ __align__(128) uint8_t fe_smem[];
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(fe_smem);
+  uint64_t* empty_bar = reinterpret_cast<uint64_t*>(fe_smem + 128);
+  float* ring = reinterpret_cast<float*>(fe_smem + 256);
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool reduce = P.reduce_op != FE_REDUCE_NONE;
+  const int ni = P.n_inputs, stages = P.stages;
+  const long long nchunks = P.n / CHUNK;
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], FE_THREADS / 32);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  float acc[W];
+#pragma unroll
+  for (int w = 0; w < W; ++w) acc[w] = fe_identity(P.reduce_op);
+
+  if (warp == FE_THREADS / 32) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, armed = 0, armed_phase = 0;
+      bool ok = true;
+      for (long long c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) {
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(ni * CHUNK * 4));
+        armed |= 1u << stage;
+        armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+        float* dst = ring + (size_t)stage * ni * CHUNK;
+        for (int i = 0; i < ni; ++i) bulk_load_1d(dst + (size_t)i * CHUNK, P.in[i] + c * CHUNK, CHUNK * 4, &full_bar[stage]);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok || abort_flag) {
+        // Unwinding: give copies that were already issued a bounded time to land.
+        const uint64_t t0 = globaltimer_ns();
+        for (int s = 0; s < stages; ++s) {
+          if (!(armed & (1u << s))) continue;
+          while (!mbar_try_wait(&full_bar[s], (armed_phase >> s) & 1u)) {
+            if (globaltimer_ns() - t0 > 2000000ull) break;
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- consumers
+    int stage = 0;
+    uint32_t phase = 0;
+    for (long long c = blockIdx.x; c < nchunks; c += gridDim.x) {
+      if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) break;
+      RingLoader<U> ld;
+      ld.base = ring + (size_t)stage * ni * CHUNK + tid * 4;
+      ld.stride = CHUNK;
+      float res[W];
+      fe_eval<W, MAXOPS>(P, ld, res);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp's reads of the stage are done
+      if (reduce) {
+        fe_accumulate<W>(P.reduce_op, acc, res);
+      } else {
+        float* out = P.dst + c * CHUNK + tid * 4;
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          __stcs(reinterpret_cast<float4*>(out + u * (FE_THREADS * 4)),
+                 make_float4(res[u * 4 + 0], res[u * 4 + 1], res[u * 4 + 2], res[u * 4 + 3]));
+      }
+      if (++stage == stages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+    fe_scalar_range<MAXOPS>(P, nchunks * CHUNK, (long long)blockIdx.x * FE_THREADS + tid, (long long)gridDim.x * FE_THREADS,
+                            reduce, acc[0]);
+  }
+  if (reduce) fe_grid_reduce<W, MAXOPS>(P, acc);
+  __syncthreads();
+  if (tid == 0 && abort_flag != 0 && P.status != nullptr) atomicExch(P.status, int(ST_WAIT_TIMEOUT));
+}
+
+// Plain-load kernel for arrays that are not 16-byte aligned and for programs without inputs.
+template <int MAXOPS>
+__global__ void __launch_bounds__(FE_THREADS) fused_elementwise_plain_kernel(const __grid_constant__ FeKernelArgs<MAXOPS> P) {
+  constexpr int U = 4;
+  const bool reduce = P.reduce_op != FE_REDUCE_NONE;
+  const long long T = (long long)gridDim.x * blockDim.x;
+  const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  float acc[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) acc[u] = fe_identity(P.reduce_op);
+  for (long long base = gtid; base < P.n; base += T * U) {
+    GlobalLoader<U> ld;
+    ld.in = P.in;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      ld.e[u] = base + (long long)u * T;
+      ld.ok[u] = ld.e[u] < P.n;
+    }
+    float res[U];
+    fe_eval<U, MAXOPS>(P, ld, res);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!ld.ok[u]) continue;
+      if (reduce)
+        acc[u] = fe_combine(P.reduce_op, acc[u], res[u]);
+      else
+        P.dst[ld.e[u]] = res[u];
+    }
+  }
+  if (reduce) fe_grid_reduce<U, MAXOPS>(P, acc);
+}
+
+// ------------------------------------------------------------------------------------------------ launcher
+template <int MAXOPS>
+static void fill_args(FeKernelArgs<MAXOPS>& a, const FeProgram& prog, const float* const* inputs, long long n,
+                      int reduce_op, float* dst, double* result, void* reduce_scratch, int* status) {
+  a.n = n;
+  for (int i = 0; i < FE_MAX_INPUTS; ++i) a.in[i] = i < prog.n_inputs ? inputs[prog.input_map[i]] : nullptr;
+  a.dst = dst;
+  a.partials = static_cast<double*>(reduce_scratch);
+  a.ticket = reduce_scratch
+                 ? reinterpret_cast<unsigned*>(static_cast<char*>(reduce_scratch) + FE_MAX_BLOCKS * sizeof(double))
+                 : nullptr;
+  a.result = result;
+  a.status = status;
+  a.n_ops = prog.n_ops;
+  a.reduce_op = reduce_op;
+  a.n_inputs = prog.n_inputs;
+  a.stages = 0;
+  memcpy(a.ops, prog.ops, sizeof(FeOp) * (size_t)prog.n_ops);
+}
+
+static long long clamp_blocks(long long want, long long cap) {
+  if (want > cap) want = cap;
+  if (want > FE_MAX_BLOCKS) want = FE_MAX_BLOCKS;
+  return want < 1 ? 1 : want;
+}
+
+template <int U, int MAXOPS>
+static int launch_ring(const FeProgram& prog, const float* const* inputs, long long n, int reduce_op, float* dst,
+                       double* result, void* reduce_scratch, int* status, int num_sms, cudaStream_t stream) {
+  auto kern = fused_elementwise_ring_kernel<U, MAXOPS>;
+  constexpr int CHUNK_BYTES = FE_THREADS * U * 16;
+  SX_ENSURE_DYN_SMEM(kern, 160 * 1024);  // the largest ring is 2 stages x 16 inputs x 4 KB + barriers
+  const int stage_bytes = prog.n_inputs * CHUNK_BYTES;
+  // Ring budget per CTA: a third of an SM's shared memory (three CTAs per SM), or half of it for the widest
+  // variant, whose stages are 16 KB per input.
+  int stages = ((U == 4 ? 104 : 72) * 1024) / stage_bytes;
+  stages = stages < 2 ? 2 : stages > FE_MAX_STAGES ? FE_MAX_STAGES : stages;
+  const int smem = 256 + stages * stage_bytes;
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FE_THREADS + 32, smem) != cudaSuccess || per_sm < 1)
+    return set_last_error(SX_ERR_DRIVER, "occupancy query failed for the fused elementwise ring kernel");
+  auto args = std::make_unique<FeKernelArgs<MAXOPS>>();
+  fill_args(*args, prog, inputs, n, reduce_op, dst, result, reduce_scratch, status);
+  args->stages = stages;
+  const long long nchunks = n / (CHUNK_BYTES / 4);
+  const long long blocks = clamp_blocks(nchunks, (long long)num_sms * per_sm);
+  kern<<<(unsigned)blocks, FE_THREADS + 32, smem, stream>>>(*args);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_last_error(SX_ERR_EXEC, cudaGetErrorString(e));
+  return SX_OK;
+}
+
+template <int MAXOPS>
+static int launch_plain(const FeProgram& prog, const float* const* inputs, long long n, int reduce_op, float* dst,
+                        double* result, void* reduce_scratch, int* status, int num_sms, cudaStream_t stream) {
+  auto kern = fused_elementwise_plain_kernel<MAXOPS>;
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FE_THREADS, 0) != cudaSuccess || per_sm < 1)
+    return set_last_error(SX_ERR_DRIVER, "occupancy query failed for the fused elementwise kernel");
+  auto args = std::make_unique<FeKernelArgs<MAXOPS>>();
+  fill_args(*args, prog, inputs, n, reduce_op, dst, result, reduce_scratch, status);
+  const long long blocks = clamp_blocks((n + FE_THREADS * 4 - 1) / (FE_THREADS * 4), (long long)num_sms * per_sm);
+  kern<<<(unsigned)blocks, FE_THREADS, 0, stream>>>(*args);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_last_error(SX_ERR_EXEC, cudaGetErrorString(e));
+  return SX_OK;
+}
+
+int launch_fused_elementwise(const FeProgram& prog, const float* const* inputs, long long n, int reduce_op,
+                             float* dst, double* result, void* reduce_scratch, int* status, int num_sms,
+                             cudaStream_t stream) {
+  const bool reduce = reduce_op != FE_REDUCE_NONE;
+  if (n <= 0) return set_last_error(SX_ERR_INVALID, "element count must be positive");
+  if (reduce && (reduce_op < 0 || reduce_op > 2)) return set_last_error(SX_ERR_INVALID, "reduce_op must be 0, 1, 2 or 255");
+  if (reduce && (result == nullptr || reduce_scratch == nullptr))
+    return set_last_error(SX_ERR_INVALID, "null reduction output");
+  if (!reduce && dst == nullptr) return set_last_error(SX_ERR_INVALID, "null dst");
+  uintptr_t bits = reduce ? 0 : reinterpret_cast<uintptr_t>(dst);
+  for (int i = 0; i < prog.n_inputs; ++i) {
+    const float* p = inputs ? inputs[prog.input_map[i]] : nullptr;
+    if (p == nullptr) return set_last_error(SX_ERR_INVALID, "null input array");
+    bits |= reinterpret_cast<uintptr_t>(p);
+  }
+  if (bits % 4) return set_last_error(SX_ERR_INVALID, "arrays must be 4-byte aligned");
+  const bool ring = bits % 16 == 0 && prog.n_inputs > 0;
+  const bool small = prog.n_ops <= FE_SMALL_OPS;
+#define FE_ARGS prog, inputs, n, reduce_op, dst, result, reduce_scratch, status, num_sms, stream
+  if (!ring) return small ? launch_plain<FE_SMALL_OPS>(FE_ARGS) : launch_plain<FE_MAX_OPS>(FE_ARGS);
+  // Values per thread and step: 16 for one or two inputs (the dispatch of an op is paid once per 16 elements,
+  // which matters when few bytes move per element), 8 for three or four, 4 beyond.
+  if (prog.n_inputs <= 2) return small ? launch_ring<4, FE_SMALL_OPS>(FE_ARGS) : launch_ring<4, FE_MAX_OPS>(FE_ARGS);
+  if (prog.n_inputs <= 4) return small ? launch_ring<2, FE_SMALL_OPS>(FE_ARGS) : launch_ring<2, FE_MAX_OPS>(FE_ARGS);
+  return small ? launch_ring<1, FE_SMALL_OPS>(FE_ARGS) : launch_ring<1, FE_MAX_OPS>(FE_ARGS);
+#undef FE_ARGS
+}
+
+}  // namespace sx

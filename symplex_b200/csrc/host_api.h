@@ -16,7 +16,7 @@
     cudaGetDevice(&dev__);                                                                                     \
     if (dev__ < 0 || dev__ >= 32 || !((done__.load(std::memory_order_relaxed) >> dev__) & 1u)) {                \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)       \
-        return SX_ERR_DRIVER;                                                                                  \
+        return sx::set_last_error(-1, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed for " #kern);   \
       if (dev__ >= 0 && dev__ < 32) done__.fetch_or(1u << dev__);                                              \
     }                                                                                                          \
   } while (0)
@@ -101,5 +101,43 @@ int launch_repack_16(const void* in, long long ld_in, long long batch_stride_in,
 // fp32 -> bf16 (round to nearest even), same shape conventions as launch_repack_16.
 int launch_f32_to_bf16(const float* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
                        int rows, int cols, int batch, cudaStream_t stream);
+
+// ---- fused elementwise programs (fused_elementwise.cu) -------------------------------------------------------
+// One op of a compiled program. Operand kinds: input array (value = compacted input index), immediate
+// (value = the float's bits), slot (value = index into the per-thread slot file) or the previous op's result.
+enum : uint8_t { FE_IN = 0, FE_IMM = 1, FE_SLOT = 2, FE_LAST = 3 };
+constexpr int FE_MAX_INPUTS = 16;
+constexpr int FE_MAX_SLOTS = 16;
+constexpr int FE_SMALL_OPS = 64;
+constexpr int FE_MAX_OPS = 1024;
+constexpr int FE_MAX_BLOCKS = 2048;        // upper bound of the grid, sizes the reduction scratch
+constexpr uint8_t FE_NO_DST = 0xff;
+constexpr int FE_REDUCE_NONE = 255;
+struct FeOp {
+  uint8_t opcode, lkind, rkind, dst;  // dst: slot that receives the result, or FE_NO_DST
+  uint32_t l, r;
+};
+struct FeProgram {
+  int n_ops = 0, n_inputs = 0, n_slots = 0;
+  int input_map[FE_MAX_INPUTS];  // compacted index -> index in the caller's input list
+  FeOp ops[FE_MAX_OPS];
+};
+struct FeSrcOp {  // layout of the reference's #[repr(C)] FusedOpDesc
+  uint8_t op, lhs_src;
+  uint16_t lhs_idx;
+  uint8_t rhs_src, pad_;
+  uint16_t rhs_idx;
+};
+// Resolve constants, compact the inputs that are used, and assign slots by liveness. Pure host code.
+int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, const float* constants,
+                          size_t n_constants, FeProgram* out);
+// Device scratch of one reduction: FE_MAX_BLOCKS doubles followed by a ticket word (zero between launches).
+constexpr size_t FE_REDUCE_SCRATCH_BYTES = FE_MAX_BLOCKS * sizeof(double) + 256;
+// Evaluate the program over n elements. inputs[] follow the caller's numbering. reduce_op 255: store to dst;
+// 0 / 1 / 2: sum / max / min of the final value into *result (a device double), nothing stored to dst.
+// status: device word that receives ST_WAIT_TIMEOUT if a bounded wait inside the kernel runs out.
+int launch_fused_elementwise(const FeProgram& prog, const float* const* inputs, long long n, int reduce_op,
+                             float* dst, double* result, void* reduce_scratch, int* status, int num_sms,
+                             cudaStream_t stream);
 
 }  // namespace sx

@@ -150,6 +150,15 @@ __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorM
       : "memory");
 }
 
+// Untiled bulk copy global -> shared::cta of the issuing CTA, completion on `bar`. Both addresses must be
+// 16-byte aligned and `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 // 3-D tiled store shared::cta -> global (this GPU's memory or a peer's mapped memory), bulk-group completion.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tm, const void* smem_src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(

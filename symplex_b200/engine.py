@@ -61,3 +61,17 @@ class FusedMatMulBiasReLUKernel(_KernelBase):
 def cuda_matmul_raw(a_ptr: int, b_ptr: int, c_ptr: int, m: int, n: int, k: int) -> int:
     """``rust-engine/src/lib.rs:1589-1592``: 0 or -1."""
     return int(_capi.load().symplex_cuda_matmul(a_ptr, b_ptr, c_ptr, m, n, k))
+
+
+_BINOPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "min": 4, "max": 5}
+
+
+def cuda_elementwise_raw(a_ptr: int, b_ptr: int, dst_ptr: int, n: int, op: str) -> int:
+    """``rust-engine/src/lib.rs:1597-1626``: ``dst = a <op> b`` on host float32 arrays; 0, -1 (CUDA error)
+    or -2 (unknown op)."""
+    if n == 0:
+        return 0
+    code = _BINOPS.get(op)
+    if code is None:
+        return -2
+    return int(_capi.load().symplex_cuda_elementwise(a_ptr, b_ptr, dst_ptr, n, code))
