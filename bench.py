@@ -59,6 +59,10 @@ NCU_TRAFFIC_BYTES = {
     "cfg2_fp32_4096_cube_colmajor_b": 1103.19e6 + 62.13e6,
     # fused fp32 kernel, 2048 x 64^3: 67.19 MB read + 5.14 MB written (C stays in L2 during the launch)
     "cfg4_batched_fp32_2048x64_cube": 67.19e6 + 5.14e6,
+    # fused elementwise ring kernel: 800.09 MB read (+ 4.09 MB of earlier dirty lines written back);
+    # 805.38 MB read + 240.92 MB written (the last 27 MB of dst are still in L2 when the kernel ends)
+    "f3_fused_axpb_sum_200M": 800.09e6 + 4.09e6,
+    "f3_fused_mul_add_relu_64M": 805.38e6 + 240.92e6,
 }
 
 # Fused elementwise chains (single HBM pass; not GEMMs): (op, lhs_src, lhs_idx, rhs_src, rhs_idx) programs of the
