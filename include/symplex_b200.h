@@ -242,6 +242,59 @@ int64_t symplex_cuda_elementwise(const float* a, const float* b, float* dst, int
 int symplex_b200_fused_program_info(const symplex_fused_op* ops, size_t n_ops, size_t n_inputs, int* n_slots,
                                     int* n_inputs_used);
 
+/* ---- planning queries (host only, no GPU needed) ----------------------------------------------- */
+
+/* hardware::HardwareTarget::B200() (include/symplex/hardware/hardware_target.h:303-329) with the figures of the
+ * real part: 148 SMs (the reference says 160), 228 KB shared memory and 256 KB tensor memory per SM, the
+ * tcgen05.mma atom 128 x 256 x 16 for bf16 (256 rows for a CTA pair; the reference assumes the 16 x 8 x 32
+ * warp-level mma), measured HBM copy bandwidth and bf16 throughput next to the nominal ones. num_sms is read
+ * from the current device when one is present (from_device = 1). */
+typedef struct symplex_b200_target {
+  int32_t num_sms, warp_size, max_warps_per_sm, max_threads_per_sm;
+  int32_t shared_mem_bytes_per_sm, max_shared_mem_per_block, register_file_bytes_per_sm, tensor_memory_bytes_per_sm;
+  int32_t max_registers_per_thread, num_fp32_lanes_per_sm;
+  int32_t mma_m, mma_n, mma_k, mma_pair_m;
+  char mma_dtype[8];
+  double global_bw_gbps, global_bw_nominal_gbps;
+  double bf16_dense_tflops, bf16_dense_tflops_sustained, bf16_dense_tflops_nominal;
+  double global_capacity_gb;
+  int32_t l2_cache_kb;
+  double nvlink_gbps_per_direction;
+  int32_t has_tma, has_async_copy, has_tensor_memory, pipeline_stages, from_device;
+} symplex_b200_target;
+int symplex_b200_hardware_target(symplex_b200_target* out);
+
+/* poly_get_micro_kernel_config (rust-engine/src/ffi.rs:695-717; table in rust-engine/src/polyhedral.rs:4375-4422).
+ * target 0 ServerX86, 1 EdgeDevice, 2 TensorAccelerator answer exactly as the reference does; target 3 = B200
+ * answers with what this library's kernels use: the tcgen05.mma atom (128 x 256 x 16 for 2-byte elements,
+ * 128 x 128 x 8 for tf32), the accumulator size in tensor-memory columns, and the pipeline depth - 1 as the
+ * prefetch distance. Null output pointers are skipped. */
+void symplex_b200_micro_kernel_config(uint8_t target, size_t element_bytes, size_t* out_tile_m, size_t* out_tile_n,
+                                      size_t* out_tile_k, size_t* out_acc_regs, size_t* out_prefetch_dist);
+
+/* training::CompilerPipeline::compile_matmul -> PipelineResult (include/symplex/training/compiler_pipeline.h:18-33,70)
+ * and cuda_backend::LaunchConfig::matmul (rust-engine/src/cuda_backend.rs:144-154) for this library: which
+ * precompiled kernel a descriptor dispatches to, its tile, launch geometry, shared / tensor memory, scratch need,
+ * and a latency estimate from the measured roofline. There is no ptx_source: nothing is generated at run time.
+ * The decision is made by the same function the launch path uses. num_sms <= 0 means 148. */
+typedef struct symplex_gemm_plan {
+  char kernel_name[64];
+  int32_t tile_m, tile_n, tile_k;      /* output tile per CTA (per CTA pair if cluster_size == 2), K per stage */
+  int32_t mma_m, mma_n, mma_k;         /* one tcgen05.mma */
+  int32_t cluster_size, stages;
+  int32_t grid_dims[3], block_dims[3]; /* persistent grid: min(tiles, SMs) CTAs */
+  int32_t shared_mem_bytes, tmem_columns;
+  int32_t prepass_launches;            /* operand preparation kernels launched before the GEMM */
+  int32_t bound;                       /* 0 tensor, 1 HBM */
+  int64_t tiles;
+  size_t workspace_bytes;
+  double flops, bytes;                 /* 2MNK x batch; operands read once + output written once */
+  double estimated_latency_ns, estimated_tflops, speedup_vs_naive;
+  int32_t valid;
+  char error[128];
+} symplex_gemm_plan;
+int symplex_b200_gemm_plan(const symplex_gemm_desc* desc, int num_sms, symplex_gemm_plan* out);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -53,6 +53,41 @@ class FusedOp(ctypes.Structure):
                 ("reserved", c_uint8), ("rhs_idx", c_uint16)]
 
 
+class Target(ctypes.Structure):
+    """``symplex_b200_target``."""
+    _fields_ = [
+        ("num_sms", c_int32), ("warp_size", c_int32), ("max_warps_per_sm", c_int32), ("max_threads_per_sm", c_int32),
+        ("shared_mem_bytes_per_sm", c_int32), ("max_shared_mem_per_block", c_int32),
+        ("register_file_bytes_per_sm", c_int32), ("tensor_memory_bytes_per_sm", c_int32),
+        ("max_registers_per_thread", c_int32), ("num_fp32_lanes_per_sm", c_int32),
+        ("mma_m", c_int32), ("mma_n", c_int32), ("mma_k", c_int32), ("mma_pair_m", c_int32),
+        ("mma_dtype", c_char * 8),
+        ("global_bw_gbps", c_double), ("global_bw_nominal_gbps", c_double),
+        ("bf16_dense_tflops", c_double), ("bf16_dense_tflops_sustained", c_double),
+        ("bf16_dense_tflops_nominal", c_double), ("global_capacity_gb", c_double),
+        ("l2_cache_kb", c_int32), ("nvlink_gbps_per_direction", c_double),
+        ("has_tma", c_int32), ("has_async_copy", c_int32), ("has_tensor_memory", c_int32),
+        ("pipeline_stages", c_int32), ("from_device", c_int32),
+    ]
+
+
+class GemmPlan(ctypes.Structure):
+    """``symplex_gemm_plan``."""
+    _fields_ = [
+        ("kernel_name", c_char * 64),
+        ("tile_m", c_int32), ("tile_n", c_int32), ("tile_k", c_int32),
+        ("mma_m", c_int32), ("mma_n", c_int32), ("mma_k", c_int32),
+        ("cluster_size", c_int32), ("stages", c_int32),
+        ("grid_dims", c_int32 * 3), ("block_dims", c_int32 * 3),
+        ("shared_mem_bytes", c_int32), ("tmem_columns", c_int32),
+        ("prepass_launches", c_int32), ("bound", c_int32),
+        ("tiles", c_int64), ("workspace_bytes", c_size_t),
+        ("flops", c_double), ("bytes", c_double),
+        ("estimated_latency_ns", c_double), ("estimated_tflops", c_double), ("speedup_vs_naive", c_double),
+        ("valid", c_int32), ("error", c_char * 128),
+    ]
+
+
 REDUCE_SUM, REDUCE_MAX, REDUCE_MIN, REDUCE_NONE = 0, 1, 2, 255
 
 _F32P = c_void_p  # raw addresses; callers pass ints (numpy ``.ctypes.data`` / torch ``.data_ptr()``)
@@ -91,6 +126,9 @@ SIGNATURES = {
     "symplex_cuda_elementwise": (c_int64, [_F32P, _F32P, _F32P, c_int64, c_int]),
     "symplex_b200_fused_program_info": (c_int, [ctypes.POINTER(FusedOp), c_size_t, c_size_t, ctypes.POINTER(c_int),
                                                 ctypes.POINTER(c_int)]),
+    "symplex_b200_hardware_target": (c_int, [ctypes.POINTER(Target)]),
+    "symplex_b200_micro_kernel_config": (None, [c_uint8, c_size_t] + [ctypes.POINTER(c_size_t)] * 5),
+    "symplex_b200_gemm_plan": (c_int, [ctypes.POINTER(GemmDesc), c_int, ctypes.POINTER(GemmPlan)]),
 }
 
 

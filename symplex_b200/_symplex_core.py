@@ -83,3 +83,9 @@ def simd_fused_elementwise_f32(ops, input_ptrs, constants, n: int, reduce_op: in
     if math.isnan(v) and _capi.last_error() != "no error":
         raise _capi.SymplexB200Error(_capi.ERR_EXEC, _capi.last_error())
     return float(v)
+
+
+def micro_kernel_config(target: str = "server", element_type: str = "fp32") -> dict:
+    """``python/src/lib.rs:531-553``; target ``"b200"`` is added (see ``symplex_b200.planner``)."""
+    from . import planner
+    return planner.micro_kernel_config(target, element_type)

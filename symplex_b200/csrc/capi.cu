@@ -212,6 +212,41 @@ static void debug_desc_override(TcGemmArgs* g) {
   }
 }
 
+// Which kernel serves a problem. One place decides, for the launch path and for the planning query alike.
+enum KernelKind { KK_F32_FUSED, KK_F32_SPLIT, KK_BF16_TC, KK_BF16_PAIR256, KK_BF16_PAIR512 };
+struct KernelChoice {
+  KernelKind kind;
+  int bn;  // tile width of the single-CTA kernels
+};
+
+static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_peers, bool f32_fused_ok) {
+  int forced = tile_n;
+  if (const char* e = getenv("SYMPLEX_B200_TILE")) forced = atoi(e);
+  if (p.f32_in) {
+    // Small and batched problems (each operand element feeds only a few tiles): split inside the GEMM kernel.
+    bool fused = (p.M + 127) / 128 <= 8 && (p.N + 63) / 64 <= 16 && f32_fused_ok;
+    if (const char* e = getenv("SYMPLEX_B200_F32_FUSED")) fused = atoi(e) != 0 && f32_fused_ok;
+    if (fused) return {KK_F32_FUSED, 64};
+    if (forced == 64 || forced == 128) return {KK_F32_SPLIT, forced};
+    const bool wide = p.N > 64 && ((p.M + 127) / 128) * ((p.N + 127) / 128) * p.batch >= num_sms;
+    return {KK_F32_SPLIT, wide ? 128 : 64};
+  }
+  const int bn = pick_bn(p.M, p.N, p.batch, num_sms, forced);
+  // Tile shape by how much work there is: 512x256 per CTA pair when that still fills the machine at least
+  // twice over (least L2 -> SM traffic per flop), 256x256 pairs for mid-size problems, single-CTA tiles
+  // (down to 128x64) when only those give every SM something to do.
+  int mode = 0;  // 0 single CTA, 1 pair 256x256, 2 pair 512x256
+  if (forced == 0 && bn == 256 && p.M > 128) {
+    const long long pairs = num_sms / 2;
+    const long long nt = (p.N + 255) / 256;
+    if (((p.M + 511) / 512) * nt * p.batch >= 2 * pairs) mode = 2;
+    else if (((p.M + 255) / 256) * nt * p.batch >= pairs) mode = 1;
+  }
+  if (const char* e = getenv("SYMPLEX_B200_PAIR")) mode = atoi(e);
+  if (n_peers > 0 && mode == 0) mode = 1;  // only the pair kernels carry the peer-store epilogue
+  return {mode == 2 ? KK_BF16_PAIR512 : mode == 1 ? KK_BF16_PAIR256 : KK_BF16_TC, bn};
+}
+
 static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, const void* B, void* C,
                     const float* bias, const void* residual, void* ws, DeviceState* st, cudaStream_t stream,
                     const void* const* peer_C = nullptr, int n_peers = 0) {
@@ -237,9 +272,7 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
       f.b_mn = !p.b_col;
       f.A = A; f.lda = p.lda; f.a_plane_stride = p.a_bs;
       f.B = B; f.ldb = p.ldb; f.b_plane_stride = p.b_bs;
-      bool fused = (p.M + 127) / 128 <= 8 && (p.N + 63) / 64 <= 16 && f32_fused_operands_ok(f);
-      if (const char* e = getenv("SYMPLEX_B200_F32_FUSED")) fused = atoi(e) != 0 && f32_fused_operands_ok(f);
-      if (fused) {
+      if (choose_kernel(p, d->tile_n, st->num_sms, 0, f32_fused_operands_ok(f)).kind == KK_F32_FUSED) {
         int rc = launch_gemm_f32_fused(f, stream);
         if (rc == SX_ERR_EXEC) return fail(rc, "GEMM kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         if (rc != SX_OK) return rc;
@@ -266,10 +299,7 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
     }
     g.A = Ap; g.lda = p.a_ldp; g.a_plane_stride = p.M * p.a_ldp;
     g.B = Bp; g.ldb = p.b_ldp; g.b_plane_stride = p.N * p.b_ldp;
-    int forced = d->tile_n;
-    if (const char* e = getenv("SYMPLEX_B200_TILE")) forced = atoi(e);
-    if (forced == 64 || forced == 128) g.bn = forced;
-    else g.bn = (p.N > 64 && ((p.M + 127) / 128) * ((p.N + 127) / 128) * p.batch >= st->num_sms) ? 128 : 64;
+    g.bn = choose_kernel(p, d->tile_n, st->num_sms, 0, false).bn;
     rc = launch_gemm_tf32x3(g, stream);
     if (rc == SX_ERR_EXEC) return fail(rc, "GEMM kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     if (rc != SX_OK) return rc;
@@ -301,27 +331,15 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
     g.A = Ause; g.lda = lda; g.a_plane_stride = a_bs;
     g.B = Buse; g.ldb = ldb; g.b_plane_stride = b_bs;
   }
-  int forced = d->tile_n;
-  if (const char* e = getenv("SYMPLEX_B200_TILE")) forced = atoi(e);
-  g.bn = pick_bn(p.M, p.N, p.batch, st->num_sms, forced);
+  if (n_peers > 7) return fail(SX_ERR_INVALID, "at most 7 peer destinations");
+  const KernelChoice kc = choose_kernel(p, d->tile_n, st->num_sms, n_peers, false);
+  g.bn = kc.bn;
+  const int mode = kc.kind == KK_BF16_PAIR512 ? 2 : kc.kind == KK_BF16_PAIR256 ? 1 : 0;
   debug_desc_override(&g);
   if (const char* e = getenv("SYMPLEX_B200_GROUP_M")) g.group_m = atoi(e);
-  // Tile shape by how much work there is: 512x256 per CTA pair when that still fills the machine at least
-  // twice over (least L2 -> SM traffic per flop), 256x256 pairs for mid-size problems, single-CTA tiles
-  // (down to 128x64) when only those give every SM something to do.
-  int mode = 0;  // 0 single CTA, 1 pair 256x256, 2 pair 512x256
-  if (forced == 0 && g.bn == 256 && p.M > 128) {
-    const long long pairs = st->num_sms / 2;
-    const long long nt = (p.N + 255) / 256;
-    if (((p.M + 511) / 512) * nt * p.batch >= 2 * pairs) mode = 2;
-    else if (((p.M + 255) / 256) * nt * p.batch >= pairs) mode = 1;
-  }
-  if (const char* e = getenv("SYMPLEX_B200_PAIR")) mode = atoi(e);
   g.tma_store = 1;
   if (const char* e = getenv("SYMPLEX_B200_TMA_STORE")) g.tma_store = atoi(e);
   if (n_peers > 0) {
-    if (n_peers > 7) return fail(SX_ERR_INVALID, "at most 7 peer destinations");
-    if (mode == 0) mode = 1;  // only the pair kernels carry the peer-store epilogue
     g.n_peers = n_peers;
     for (int i = 0; i < n_peers; ++i) g.peer_C[i] = peer_C[i];
   }
@@ -819,6 +837,143 @@ int symplex_cuda_device_info(symplex_device_info* out) {
 }
 
 uint64_t symplex_b200_launch_count(void) { return g_launches.load(); }
+
+int symplex_b200_hardware_target(symplex_b200_target* t) {
+  if (!t) return fail(SX_ERR_INVALID, "null output");
+  memset(t, 0, sizeof(*t));
+  t->num_sms = 148;
+  t->warp_size = 32;
+  t->max_warps_per_sm = 64;
+  t->max_threads_per_sm = 2048;
+  t->shared_mem_bytes_per_sm = 228 * 1024;
+  t->max_shared_mem_per_block = 227 * 1024;
+  t->register_file_bytes_per_sm = 256 * 1024;
+  t->tensor_memory_bytes_per_sm = 256 * 1024;
+  t->max_registers_per_thread = 255;
+  t->num_fp32_lanes_per_sm = 128;
+  t->mma_m = 128;
+  t->mma_n = 256;
+  t->mma_k = 16;
+  t->mma_pair_m = 256;
+  strncpy(t->mma_dtype, "bf16", sizeof(t->mma_dtype) - 1);
+  t->global_bw_gbps = 6552.0;       // STREAM-style copy measured on this library's target boards
+  t->global_bw_nominal_gbps = 7700.0;
+  t->bf16_dense_tflops = 1663.5;    // cuBLAS bf16, measured burst
+  t->bf16_dense_tflops_sustained = 1396.0;
+  t->bf16_dense_tflops_nominal = 2250.0;
+  t->global_capacity_gb = 180.0;
+  t->l2_cache_kb = 126 * 1024;
+  t->nvlink_gbps_per_direction = 900.0;
+  t->has_tma = 1;
+  t->has_async_copy = 1;
+  t->has_tensor_memory = 1;
+  t->pipeline_stages = 4;
+  int n = 0, dev = 0;
+  if (cudaGetDeviceCount(&n) == cudaSuccess && n > 0 && cudaGetDevice(&dev) == cudaSuccess) {
+    int major = 0, sms = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess && major == 10 &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
+      t->num_sms = sms;
+      t->from_device = 1;
+    }
+  } else {
+    cudaGetLastError();
+  }
+  return SX_OK;
+}
+
+void symplex_b200_micro_kernel_config(uint8_t target, size_t element_bytes, size_t* out_tile_m, size_t* out_tile_n,
+                                      size_t* out_tile_k, size_t* out_acc_regs, size_t* out_prefetch_dist) {
+  size_t m, n, k, acc, pf;
+  if (target == 3) {  // B200: one tcgen05.mma atom, accumulators counted in tensor-memory columns
+    if (element_bytes == 2) {
+      const KernelShape ks = describe_gemm_pair(2);
+      m = 128, n = (size_t)ks.mma_n, k = (size_t)ks.mma_k, acc = (size_t)ks.tmem_cols, pf = (size_t)ks.stages - 1;
+    } else {
+      const KernelShape ks = describe_gemm_tf32x3(128);
+      m = (size_t)ks.mma_m, n = (size_t)ks.mma_n, k = (size_t)ks.mma_k, acc = (size_t)ks.tmem_cols, pf = (size_t)ks.stages - 1;
+    }
+  } else if (target == 1) {  // EdgeDevice
+    m = 4, n = 4, k = 8, acc = 4, pf = 1;
+  } else if (target == 2) {  // TensorAccelerator
+    m = 16, n = 16, k = 16, acc = 8, pf = 4;
+  } else if (element_bytes == 2) {  // ServerX86, 16-bit
+    m = 16, n = 16, k = 32, acc = 8, pf = 2;
+  } else {  // ServerX86, fp32
+    m = 8, n = 8, k = 8, acc = 16, pf = 1;
+  }
+  if (out_tile_m) *out_tile_m = m;
+  if (out_tile_n) *out_tile_n = n;
+  if (out_tile_k) *out_tile_k = k;
+  if (out_acc_regs) *out_acc_regs = acc;
+  if (out_prefetch_dist) *out_prefetch_dist = pf;
+}
+
+int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm_plan* out) {
+  if (!out) return fail(SX_ERR_INVALID, "null output");
+  memset(out, 0, sizeof(*out));
+  Plan p;
+  int rc = make_plan(d, nullptr, nullptr, &p);
+  if (rc != SX_OK) {
+    strncpy(out->error, g_err, sizeof(out->error) - 1);
+    return rc;
+  }
+  if (p.K == 0 || p.M == 0 || p.N == 0 || p.batch == 0) {
+    rc = fail(SX_ERR_INVALID, "empty problem: nothing to plan");
+    strncpy(out->error, g_err, sizeof(out->error) - 1);
+    return rc;
+  }
+  if (num_sms <= 0) num_sms = 148;
+  const KernelChoice kc = choose_kernel(p, d->tile_n, num_sms, 0, true);
+  KernelShape ks;
+  double eff;  // fraction of the tensor peak the variant sustains on large problems (measured)
+  switch (kc.kind) {
+    case KK_F32_FUSED: ks = describe_gemm_f32_fused(); eff = 0.45; break;
+    case KK_F32_SPLIT: ks = describe_gemm_tf32x3(kc.bn); eff = 0.71; break;
+    case KK_BF16_PAIR512: ks = describe_gemm_pair(2); eff = 0.90; break;
+    case KK_BF16_PAIR256: ks = describe_gemm_pair(1); eff = 0.82; break;
+    default: ks = describe_gemm_tc(kc.bn); eff = 0.70; break;
+  }
+  strncpy(out->kernel_name, ks.name, sizeof(out->kernel_name) - 1);
+  out->tile_m = ks.tile_m; out->tile_n = ks.tile_n; out->tile_k = ks.tile_k;
+  out->mma_m = ks.mma_m; out->mma_n = ks.mma_n; out->mma_k = ks.mma_k;
+  out->cluster_size = ks.cluster;
+  out->stages = ks.stages;
+  out->shared_mem_bytes = ks.smem_bytes;
+  out->tmem_columns = ks.tmem_cols;
+  const long long mt = (p.M + ks.tile_m - 1) / ks.tile_m, nt = (p.N + ks.tile_n - 1) / ks.tile_n;
+  out->tiles = mt * nt * p.batch;
+  const long long units = ks.cluster == 2 ? num_sms / 2 : num_sms;  // persistent: one CTA (or pair) per SM (pair)
+  const long long active = out->tiles < units ? out->tiles : units;
+  out->grid_dims[0] = (int32_t)(active * ks.cluster); out->grid_dims[1] = 1; out->grid_dims[2] = 1;
+  out->block_dims[0] = ks.threads; out->block_dims[1] = 1; out->block_dims[2] = 1;
+  out->prepass_launches = kc.kind == KK_F32_SPLIT ? 2 : (p.a_prep ? 1 : 0) + (p.b_prep ? 1 : 0);
+  if (kc.kind == KK_F32_FUSED) out->prepass_launches = 0;
+  out->workspace_bytes = kc.kind == KK_F32_FUSED ? 0 : p.total;
+  const double in_elt = p.f32_in ? 4.0 : 2.0, out_elt = p.bf16_out ? 2.0 : 4.0;
+  out->flops = 2.0 * (double)p.M * (double)p.N * (double)p.K * p.batch;
+  out->bytes = ((double)p.M * p.K + (double)p.K * p.N) * in_elt * p.batch + (double)p.M * p.N * out_elt * p.batch;
+  // Roofline estimate from the measured peaks: tensor time at the variant's sustained efficiency and at the
+  // fraction of the machine the tiles can occupy (whole waves), HBM time for the algorithmic bytes (plus the
+  // pre-pass's extra read and write of the operands), a fixed launch cost per kernel.
+  const double peak = p.f32_in ? 1663.5e12 / 6.0 : 1663.5e12;
+  const long long waves = (out->tiles + units - 1) / units;
+  const double occupancy = (double)out->tiles / (double)(waves * units);
+  const double t_tensor = out->flops / (peak * eff * occupancy);
+  double hbm_bytes = out->bytes;
+  if (kc.kind == KK_F32_SPLIT) hbm_bytes += 3.0 * ((double)p.M * p.K + (double)p.K * p.N) * 4.0 * p.batch;
+  const double t_hbm = hbm_bytes / (kc.kind == KK_F32_FUSED ? 0.4 * 6552e9 : 6552e9);
+  const double t = (t_tensor > t_hbm ? t_tensor : t_hbm) + 4e-6 * (1 + out->prepass_launches);
+  out->estimated_latency_ns = t * 1e9;
+  out->estimated_tflops = out->flops / t / 1e12;
+  out->bound = t_tensor >= t_hbm ? 0 : 1;
+  // "Naive" = the one-thread-per-output scalar-FMA kernel the reference's PTX generator describes
+  // (rust-engine/src/cuda_backend.rs:300-504): two shared-memory loads per FMA, i.e. at most
+  // 148 SMs x 128 B/clk / 8 B x 2 flop x 1.9 GHz = 9 TFLOP/s.
+  out->speedup_vs_naive = (out->flops / 9e12 + 4e-6) / t;
+  out->valid = 1;
+  return SX_OK;
+}
 
 int symplex_b200_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_ops, const float* const* inputs,
                                        size_t n_inputs, const float* constants, size_t n_constants, int64_t n,

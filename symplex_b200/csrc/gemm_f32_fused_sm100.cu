@@ -347,4 +347,10 @@ int launch_gemm_f32_fused(const TcGemmArgs& a, cudaStream_t stream) {
                 : launch_fused<float, false>(tmA, tmB, p, grid, stream);
 }
 
+
+KernelShape describe_gemm_f32_fused() {
+  using C = FusedCfg;
+  return KernelShape{"gemm_f32_fused_kernel", C::BM, C::BN, C::BK, C::BM, C::BN, C::UMMA_K, C::THREADS, 1, C::STAGES, C::DYN_SMEM, C::TMEM_COLS};
+}
+
 }  // namespace sx

@@ -485,4 +485,14 @@ int launch_gemm_pair(const TcGemmArgs& a, cudaStream_t stream) {
                 : launch_pair_mb<float, false>(mb, tmA, tmB, dmaps, p, pairs, stream);
 }
 
+
+KernelShape describe_gemm_pair(int kmb) {
+  auto mk = [](auto cfg) {
+    using C = decltype(cfg);
+    // cta_group::2: one instruction spans both CTAs, 256 rows x 256 columns x 16
+    return KernelShape{"gemm_pair_kernel", C::BM, C::BN, C::BK, 256, C::BN, C::UMMA_K, C::THREADS, 2, C::STAGES, C::DYN_SMEM, C::TMEM_COLS};
+  };
+  return kmb == 2 ? mk(PairCfg<2>{}) : mk(PairCfg<1>{});
+}
+
 }  // namespace sx

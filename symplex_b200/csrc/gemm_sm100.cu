@@ -321,4 +321,13 @@ int launch_gemm_tc(const TcGemmArgs& a, cudaStream_t stream) {
   return SX_ERR_INVALID;  // fp32 operands go through launch_gemm_tf32x3
 }
 
+
+KernelShape describe_gemm_tc(int bn) {
+  auto mk = [](auto cfg) {
+    using C = decltype(cfg);
+    return KernelShape{"gemm_tc_kernel", C::BM, C::BN, C::BK, C::BM, C::BN, C::UMMA_K, 192, 1, C::STAGES, C::DYN_SMEM, C::TMEM_COLS};
+  };
+  return bn == 256 ? mk(TileCfg<256, 0>{}) : bn == 128 ? mk(TileCfg<128, 0>{}) : mk(TileCfg<64, 0>{});
+}
+
 }  // namespace sx

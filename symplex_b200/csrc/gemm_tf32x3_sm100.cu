@@ -291,4 +291,13 @@ int launch_gemm_tf32x3(const TcGemmArgs& a, cudaStream_t stream) {
   return bn == 128 ? launch_x3<float, 128>(tmA, tmB, p, grid, stream) : launch_x3<float, 64>(tmA, tmB, p, grid, stream);
 }
 
+
+KernelShape describe_gemm_tf32x3(int bn) {
+  auto mk = [](auto cfg) {
+    using C = decltype(cfg);
+    return KernelShape{"gemm_tf32x3_kernel", C::BM, C::BN, C::BK, C::BM, C::BN, C::UMMA_K, 192, 1, C::STAGES, C::DYN_SMEM, C::TMEM_COLS};
+  };
+  return bn == 128 ? mk(X3Cfg<128>{}) : mk(X3Cfg<64>{});
+}
+
 }  // namespace sx

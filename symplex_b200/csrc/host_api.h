@@ -102,6 +102,18 @@ int launch_repack_16(const void* in, long long ld_in, long long batch_stride_in,
 int launch_f32_to_bf16(const float* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
                        int rows, int cols, int batch, cudaStream_t stream);
 
+// Static shape of one GEMM kernel variant, for the planning queries of the C ABI (no GPU needed).
+struct KernelShape {
+  const char* name;
+  int tile_m, tile_n, tile_k;  // output tile per CTA (per CTA pair when cluster == 2) and K per pipeline stage
+  int mma_m, mma_n, mma_k;     // one tcgen05.mma instruction
+  int threads, cluster, stages, smem_bytes, tmem_cols;
+};
+KernelShape describe_gemm_tc(int bn);      // gemm_sm100.cu: bf16, one CTA per tile
+KernelShape describe_gemm_pair(int kmb);   // gemm_pair_sm100.cu: bf16, CTA pair, kmb = 1 (256x256) or 2 (512x256)
+KernelShape describe_gemm_tf32x3(int bn);  // gemm_tf32x3_sm100.cu: fp32 from pre-split planes
+KernelShape describe_gemm_f32_fused();     // gemm_f32_fused_sm100.cu: fp32, split in shared memory
+
 // ---- fused elementwise programs (fused_elementwise.cu) -------------------------------------------------------
 // One op of a compiled program. Operand kinds: input array (value = compacted input index), immediate
 // (value = the float's bits), slot (value = index into the per-thread slot file) or the previous op's result.

@@ -447,3 +447,36 @@ def test_tensor_matmul_wire_record(lib, oracle, ety, rhs_layout):
         assert rel_frobenius(oracle.bf16_bits_to_f32(C), oracle.bf16_round(ref)) <= TOL_BF16
     else:
         assert rel_frobenius(C, ref) <= TOL_F32
+
+
+@pytest.mark.parametrize("M,N,K,dtype,batch", [
+    (512, 512, 512, "fp32", 1), (64, 64, 64, "fp32", 64), (2048, 1536, 1024, "fp32", 1),
+    (300, 300, 300, "bf16", 1), (2048, 2048, 2048, "bf16", 1), (4096, 4096, 1024, "bf16", 1),
+    (8192, 4096, 512, "bf16", 1),
+])
+def test_plan_describes_what_is_launched(lib, M, N, K, dtype, batch):
+    """symplex_b200_gemm_plan and the launch path share one decision function: the number of kernels a call
+    launches must be the plan's pre-pass count + 1, and the plan's latency estimate must be within a factor of
+    three of the measured time (it is a roofline model, not a simulator)."""
+    from symplex_b200 import planner
+    plan = planner.compile_matmul(M, N, K, dtype=dtype, batch=batch)
+    assert plan.valid
+    tdt = torch.float32 if dtype == "fp32" else torch.bfloat16
+    shape_a = (batch, M, K) if batch > 1 else (M, K)
+    shape_b = (batch, K, N) if batch > 1 else (K, N)
+    A = torch.randn(shape_a, device="cuda").to(tdt)
+    B = torch.randn(shape_b, device="cuda").to(tdt)
+    out = sx.gemm(A, B)
+    before = sx.launch_count()
+    sx.gemm(A, B, out=out)
+    assert sx.launch_count() - before == plan.prepass_launches + 1
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(10):
+        sx.gemm(A, B, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    sx.sync_status()
+    measured_ns = e0.elapsed_time(e1) / 10 * 1e6
+    assert plan.estimated_latency_ns / 3 <= measured_ns <= plan.estimated_latency_ns * 3, (measured_ns, plan)
