@@ -242,6 +242,12 @@ int64_t symplex_cuda_elementwise(const float* a, const float* b, float* dst, int
 int symplex_b200_fused_program_info(const symplex_fused_op* ops, size_t n_ops, size_t n_inputs, int* n_slots,
                                     int* n_inputs_used);
 
+/* Launch geometry of the fused elementwise kernels for chains that read n_inputs distinct arrays of n elements
+ * (cuda_backend::LaunchConfig::elementwise, rust-engine/src/cuda_backend.rs:134-141, for this library: a
+ * persistent grid, 256 consumer threads + one producer warp per CTA, a shared-memory ring). Host only. */
+int symplex_b200_fused_elementwise_plan(int n_inputs, int64_t n, int num_sms, int32_t grid_dims[3],
+                                        int32_t block_dims[3], int32_t* shared_mem_bytes);
+
 /* ---- planning queries (host only, no GPU needed) ----------------------------------------------- */
 
 /* hardware::HardwareTarget::B200() (include/symplex/hardware/hardware_target.h:303-329) with the figures of the

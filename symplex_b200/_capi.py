@@ -126,6 +126,8 @@ SIGNATURES = {
     "symplex_cuda_elementwise": (c_int64, [_F32P, _F32P, _F32P, c_int64, c_int]),
     "symplex_b200_fused_program_info": (c_int, [ctypes.POINTER(FusedOp), c_size_t, c_size_t, ctypes.POINTER(c_int),
                                                 ctypes.POINTER(c_int)]),
+    "symplex_b200_fused_elementwise_plan": (c_int, [c_int, c_int64, c_int, ctypes.POINTER(c_int32 * 3),
+                                                    ctypes.POINTER(c_int32 * 3), ctypes.POINTER(c_int32)]),
     "symplex_b200_hardware_target": (c_int, [ctypes.POINTER(Target)]),
     "symplex_b200_micro_kernel_config": (None, [c_uint8, c_size_t] + [ctypes.POINTER(c_size_t)] * 5),
     "symplex_b200_gemm_plan": (c_int, [ctypes.POINTER(GemmDesc), c_int, ctypes.POINTER(GemmPlan)]),

@@ -89,3 +89,10 @@ def micro_kernel_config(target: str = "server", element_type: str = "fp32") -> d
     """``python/src/lib.rs:531-553``; target ``"b200"`` is added (see ``symplex_b200.planner``)."""
     from . import planner
     return planner.micro_kernel_config(target, element_type)
+
+
+def cuda_compile_ptx(pattern_type: str, shape_info: dict, sm_arch: str = "sm_100a") -> str:
+    """``python/src/lib.rs:1762-1832`` returns generated PTX text; this library runs precompiled kernels, so the
+    string is a one-line description of the kernel that serves the pattern (``engine.cuda_compile_kernel``)."""
+    from . import engine
+    return engine.cuda_compile_kernel(pattern_type, shape_info, sm_arch).ptx_source()

@@ -838,6 +838,18 @@ int symplex_cuda_device_info(symplex_device_info* out) {
 
 uint64_t symplex_b200_launch_count(void) { return g_launches.load(); }
 
+int symplex_b200_fused_elementwise_plan(int n_inputs, int64_t n, int num_sms, int32_t grid_dims[3],
+                                        int32_t block_dims[3], int32_t* shared_mem_bytes) {
+  if (n_inputs < 0 || n_inputs > FE_MAX_INPUTS || n <= 0 || !grid_dims || !block_dims || !shared_mem_bytes)
+    return fail(SX_ERR_INVALID, "bad argument (0..16 input arrays, n > 0)");
+  int g = 0, b = 0, sm = 0;
+  describe_fused_elementwise(n_inputs, n, num_sms > 0 ? num_sms : 148, &g, &b, &sm);
+  grid_dims[0] = g; grid_dims[1] = 1; grid_dims[2] = 1;
+  block_dims[0] = b; block_dims[1] = 1; block_dims[2] = 1;
+  *shared_mem_bytes = sm;
+  return SX_OK;
+}
+
 int symplex_b200_hardware_target(symplex_b200_target* t) {
   if (!t) return fail(SX_ERR_INVALID, "null output");
   memset(t, 0, sizeof(*t));

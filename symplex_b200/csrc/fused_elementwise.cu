@@ -535,18 +535,53 @@ static long long clamp_blocks(long long want, long long cap) {
   return want < 1 ? 1 : want;
 }
 
+// Ring geometry for a program with n_inputs arrays: values per thread and step (4 * U), stages, bytes.
+struct RingGeometry {
+  int u, chunk_elems, stages, smem_bytes;
+};
+static RingGeometry ring_geometry(int n_inputs) {
+  // Values per thread and step: 16 for one or two inputs (the dispatch of an op is paid once per 16 elements,
+  // which matters when few bytes move per element), 8 for three or four, 4 beyond.
+  RingGeometry g;
+  g.u = n_inputs <= 2 ? 4 : n_inputs <= 4 ? 2 : 1;
+  g.chunk_elems = FE_THREADS * 4 * g.u;
+  const int stage_bytes = n_inputs * g.chunk_elems * 4;
+  // Ring budget per CTA: a third of an SM's shared memory (three CTAs per SM), or half of it for the widest
+  // variant, whose stages are 16 KB per input.
+  g.stages = ((g.u == 4 ? 104 : 72) * 1024) / stage_bytes;
+  g.stages = g.stages < 2 ? 2 : g.stages > FE_MAX_STAGES ? FE_MAX_STAGES : g.stages;
+  g.smem_bytes = 256 + g.stages * stage_bytes;
+  return g;
+}
+
+void describe_fused_elementwise(int n_inputs, long long n, int num_sms, int* grid, int* block, int* smem_bytes) {
+  if (n_inputs < 1) {  // plain-load kernel
+    const long long want = (n + FE_THREADS * 4 - 1) / (FE_THREADS * 4), cap = (long long)num_sms * 8;
+    *grid = (int)(want < 1 ? 1 : want > cap ? cap : want > FE_MAX_BLOCKS ? FE_MAX_BLOCKS : want);
+    *block = FE_THREADS;
+    *smem_bytes = 0;
+    return;
+  }
+  const RingGeometry g = ring_geometry(n_inputs > FE_MAX_INPUTS ? FE_MAX_INPUTS : n_inputs);
+  int per_sm = (228 * 1024) / (g.smem_bytes + 1024 + 512);  // + per-CTA reservation and static shared memory
+  if (per_sm > 7) per_sm = 7;                               // 2048 threads / 288
+  if (per_sm < 1) per_sm = 1;
+  const long long chunks = n / g.chunk_elems, cap = (long long)num_sms * per_sm;
+  long long b = chunks < cap ? chunks : cap;
+  if (b > FE_MAX_BLOCKS) b = FE_MAX_BLOCKS;
+  *grid = (int)(b < 1 ? 1 : b);
+  *block = FE_THREADS + 32;
+  *smem_bytes = g.smem_bytes;
+}
+
 template <int U, int MAXOPS>
 static int launch_ring(const FeProgram& prog, const float* const* inputs, long long n, int reduce_op, float* dst,
                        double* result, void* reduce_scratch, int* status, int num_sms, cudaStream_t stream) {
   auto kern = fused_elementwise_ring_kernel<U, MAXOPS>;
   constexpr int CHUNK_BYTES = FE_THREADS * U * 16;
   SX_ENSURE_DYN_SMEM(kern, 160 * 1024);  // the largest ring is 2 stages x 16 inputs x 4 KB + barriers
-  const int stage_bytes = prog.n_inputs * CHUNK_BYTES;
-  // Ring budget per CTA: a third of an SM's shared memory (three CTAs per SM), or half of it for the widest
-  // variant, whose stages are 16 KB per input.
-  int stages = ((U == 4 ? 104 : 72) * 1024) / stage_bytes;
-  stages = stages < 2 ? 2 : stages > FE_MAX_STAGES ? FE_MAX_STAGES : stages;
-  const int smem = 256 + stages * stage_bytes;
+  const RingGeometry geo = ring_geometry(prog.n_inputs);
+  const int stages = geo.stages, smem = geo.smem_bytes;
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FE_THREADS + 32, smem) != cudaSuccess || per_sm < 1)
     return set_last_error(SX_ERR_DRIVER, "occupancy query failed for the fused elementwise ring kernel");
@@ -597,11 +632,11 @@ int launch_fused_elementwise(const FeProgram& prog, const float* const* inputs, 
   const bool small = prog.n_ops <= FE_SMALL_OPS;
 #define FE_ARGS prog, inputs, n, reduce_op, dst, result, reduce_scratch, status, num_sms, stream
   if (!ring) return small ? launch_plain<FE_SMALL_OPS>(FE_ARGS) : launch_plain<FE_MAX_OPS>(FE_ARGS);
-  // Values per thread and step: 16 for one or two inputs (the dispatch of an op is paid once per 16 elements,
-  // which matters when few bytes move per element), 8 for three or four, 4 beyond.
-  if (prog.n_inputs <= 2) return small ? launch_ring<4, FE_SMALL_OPS>(FE_ARGS) : launch_ring<4, FE_MAX_OPS>(FE_ARGS);
-  if (prog.n_inputs <= 4) return small ? launch_ring<2, FE_SMALL_OPS>(FE_ARGS) : launch_ring<2, FE_MAX_OPS>(FE_ARGS);
-  return small ? launch_ring<1, FE_SMALL_OPS>(FE_ARGS) : launch_ring<1, FE_MAX_OPS>(FE_ARGS);
+  switch (ring_geometry(prog.n_inputs).u) {
+    case 4: return small ? launch_ring<4, FE_SMALL_OPS>(FE_ARGS) : launch_ring<4, FE_MAX_OPS>(FE_ARGS);
+    case 2: return small ? launch_ring<2, FE_SMALL_OPS>(FE_ARGS) : launch_ring<2, FE_MAX_OPS>(FE_ARGS);
+    default: return small ? launch_ring<1, FE_SMALL_OPS>(FE_ARGS) : launch_ring<1, FE_MAX_OPS>(FE_ARGS);
+  }
 #undef FE_ARGS
 }
 

@@ -143,6 +143,9 @@ struct FeSrcOp {  // layout of the reference's #[repr(C)] FusedOpDesc
 // Resolve constants, compact the inputs that are used, and assign slots by liveness. Pure host code.
 int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, const float* constants,
                           size_t n_constants, FeProgram* out);
+// Launch geometry the kernels use for a program with n_inputs arrays of n elements (host only; the launch
+// path asks the occupancy calculator for the CTAs per SM, this uses the shared-memory arithmetic).
+void describe_fused_elementwise(int n_inputs, long long n, int num_sms, int* grid, int* block, int* smem_bytes);
 // Device scratch of one reduction: FE_MAX_BLOCKS doubles followed by a ticket word (zero between launches).
 constexpr size_t FE_REDUCE_SCRATCH_BYTES = FE_MAX_BLOCKS * sizeof(double) + 256;
 // Evaluate the program over n elements. inputs[] follow the caller's numbering. reduce_op 255: store to dst;

@@ -106,3 +106,24 @@ def test_invalid_requests_are_reported_in_the_result(lib):
     assert not r.valid and "empty" in r.error
     r = planner.compile_matmul(64, 64, 64, dtype="bf16", activation="swish")
     assert not r.valid and "activation" in r.error
+
+
+def test_cuda_compile_kernel_descriptions(lib):
+    from symplex_b200 import engine
+    k = engine.cuda_compile_kernel("matmul", {"M": 128, "N": 128, "K": 64, "tile_m": 32, "tile_n": 32, "tile_k": 8})
+    assert k.kernel_name() == "gemm_f32_fused_kernel" and k.estimated_gflops() > 0 and k.ptx_size() == len(k.ptx_source())
+    assert k.block_dims() == (320, 1, 1) and k.grid_dims()[0] == 2
+    e = engine.cuda_compile_kernel("elementwise", {"op": "add", "n": 1 << 24})
+    assert e.kernel_name() == "fused_elementwise_ring_kernel" and e.block_dims() == (288, 1, 1)
+    assert e.grid_dims()[0] == 148 * 2 and e.shared_mem_bytes() == 256 + 3 * 2 * 16384
+    f = engine.cuda_compile_kernel("fma", {"n": 1 << 24})
+    assert f.grid_dims()[0] == 148 * 3 and f.shared_mem_bytes() == 256 + 3 * 3 * 8192
+    r = engine.cuda_compile_kernel("reduction", {"op": "max", "n": 1000})
+    assert r.grid_dims()[0] == 1
+    with pytest.raises(ValueError):
+        engine.cuda_compile_kernel("elementwise", {"op": "pow", "n": 10})
+    with pytest.raises(ValueError):
+        engine.cuda_compile_kernel("reduction", {"op": "mul", "n": 10})
+    with pytest.raises(ValueError):
+        engine.cuda_compile_kernel("conv9d", {})
+    assert "fused_elementwise_ring_kernel" in _symplex_core.cuda_compile_ptx("fma", {"n": 512})
