@@ -223,6 +223,12 @@ double symplex_simd_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_
                                           size_t n_inputs, const float* constants, size_t n_constants, size_t n,
                                           uint8_t reduce_op, float* dst_ptr);
 
+/* The f64 twin (rust-engine/src/x86_emitter.rs:2799-2828, python/src/lib.rs:1700-1709): same chain encoding on
+ * double arrays and double constants; this is what the reference's Python layer calls for float64 NumPy data. */
+double symplex_simd_fused_elementwise_f64(const symplex_fused_op* ops, size_t n_ops, const double* const* input_ptrs,
+                                          size_t n_inputs, const double* constants, size_t n_constants, size_t n,
+                                          uint8_t reduce_op, double* dst_ptr);
+
 /* Same computation on DEVICE arrays, asynchronous on `stream`. `result` (device double, 8-byte aligned)
  * receives the reduced value when reduce_op != 255; `dst` receives the values otherwise and may alias an
  * input. Arrays that are all 16-byte aligned take the bulk-copy kernel, others a plain-load kernel.
@@ -230,6 +236,9 @@ double symplex_simd_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_
 int symplex_b200_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_ops, const float* const* inputs,
                                        size_t n_inputs, const float* constants, size_t n_constants, int64_t n,
                                        int reduce_op, float* dst, double* result, void* stream);
+int symplex_b200_fused_elementwise_f64(const symplex_fused_op* ops, size_t n_ops, const double* const* inputs,
+                                       size_t n_inputs, const double* constants, size_t n_constants, int64_t n,
+                                       int reduce_op, double* dst, double* result, void* stream);
 
 /* cuda_backend::cuda_elementwise / symplex_engine.cuda_elementwise_raw (rust-engine/src/cuda_backend.rs:1420-1455,
  * rust-engine/src/lib.rs:1597-1626): dst[i] = a[i] <op> b[i] on host arrays, op 0 add, 1 sub, 2 mul, 3 div,
@@ -245,8 +254,8 @@ int symplex_b200_fused_program_info(const symplex_fused_op* ops, size_t n_ops, s
 /* Launch geometry of the fused elementwise kernels for chains that read n_inputs distinct arrays of n elements
  * (cuda_backend::LaunchConfig::elementwise, rust-engine/src/cuda_backend.rs:134-141, for this library: a
  * persistent grid, 256 consumer threads + one producer warp per CTA, a shared-memory ring). Host only. */
-int symplex_b200_fused_elementwise_plan(int n_inputs, int64_t n, int num_sms, int32_t grid_dims[3],
-                                        int32_t block_dims[3], int32_t* shared_mem_bytes);
+int symplex_b200_fused_elementwise_plan(int n_inputs, int64_t n, int element_bytes, int num_sms,
+                                        int32_t grid_dims[3], int32_t block_dims[3], int32_t* shared_mem_bytes);
 
 /* ---- planning queries (host only, no GPU needed) ----------------------------------------------- */
 

@@ -45,21 +45,25 @@ class Oracle:
         lib.oracle_max_threads.restype = _int
         lib.oracle_fused_elementwise_f32.argtypes = [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _int, _vp, _int]
         lib.oracle_fused_elementwise_f32.restype = ctypes.c_double
+        lib.oracle_fused_elementwise_f64.argtypes = [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _int, _vp, _int]
+        lib.oracle_fused_elementwise_f64.restype = ctypes.c_double
         self.threads = max(1, int(lib.oracle_max_threads()))
 
-    def fused_elementwise(self, ops, inputs, constants, reduce_op=255, exact=False):
+    def fused_elementwise(self, ops, inputs, constants, reduce_op=255, exact=False, dtype=np.float32):
         """The reference's fused op chain on host arrays: returns the result array (reduce_op 255) or the reduced
-        value as the reference computes it (``exact=True``: the true max / min even when n % 8 != 0)."""
+        value as the reference computes it (``exact=True``: the true max / min even when n % 8 != 0).
+        ``dtype=np.float64`` selects the f64 twin."""
         rec = np.zeros(max(len(ops), 1), dtype=np.dtype([("op", "u1"), ("ls", "u1"), ("li", "<u2"), ("rs", "u1"),
                                                           ("pad", "u1"), ("ri", "<u2")]))
         for i, (op, ls, li, rs, ri) in enumerate(ops):
             rec[i] = (op, ls, li, rs, 0, ri)
-        arrs = [np.ascontiguousarray(a, dtype=np.float32).ravel() for a in inputs]
+        arrs = [np.ascontiguousarray(a, dtype=dtype).ravel() for a in inputs]
         n = arrs[0].size if arrs else 0
         ptrs = (ctypes.c_void_p * max(len(arrs), 1))(*[a.ctypes.data for a in arrs])
-        consts = np.ascontiguousarray(np.asarray(list(constants) + [0.0], dtype=np.float32))
-        dst = np.zeros(n, np.float32)
-        v = self.lib.oracle_fused_elementwise_f32(_ptr(rec), len(ops), ctypes.cast(ptrs, _vp), len(arrs), _ptr(consts),
+        consts = np.ascontiguousarray(np.asarray(list(constants) + [0.0], dtype=dtype))
+        dst = np.zeros(n, dtype)
+        fn = self.lib.oracle_fused_elementwise_f64 if dtype == np.float64 else self.lib.oracle_fused_elementwise_f32
+        v = fn(_ptr(rec), len(ops), ctypes.cast(ptrs, _vp), len(arrs), _ptr(consts),
                                                   len(constants), n, int(reduce_op), _ptr(dst), int(bool(exact)))
         return dst if reduce_op == 255 else float(v)
 

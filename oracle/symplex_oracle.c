@@ -434,6 +434,112 @@ double oracle_fused_elementwise_f32(const oracle_fused_op* ops, int64_t n_ops, c
   return (double)r + scalar_acc;
 }
 
+/* The f64 twin, fused_elem_f64_avx2_core (rust-engine/src/x86_emitter.rs:2478-2727): same chain rules in double;
+ * four 4-lane accumulators over blocks of 16, accumulator 0 for the remaining blocks of 4, a scalar for the last
+ * n mod 4, then acc0+acc1, +acc2, +acc3, lanes l + (l+2), then lane 0 + lane 1, "+ scalar_acc". */
+static double fe_unop64(uint8_t op, double v) {
+  switch (op) {
+    case 6: return -v;
+    case 7: return fabs(v);
+    case 8: return sqrt(v);
+    case 9: return exp(v);
+    case 10: return log(v);
+    case 11: return sin(v);
+    case 12: return cos(v);
+    case 13: return tanh(v);
+    case 14: return 1.0 / (1.0 + exp(-v));
+    case 15: return v > 0.0 ? v : 0.0;
+    default: return v;
+  }
+}
+
+static double fe_element64(const oracle_fused_op* ops, int64_t n_ops, const double* const* in, int64_t n_in,
+                           const double* consts, int64_t n_consts, int64_t i, double* tmp) {
+  for (int64_t o = 0; o < n_ops; ++o) {
+    double v[2];
+    for (int side = 0; side < 2; ++side) {
+      const uint8_t src = side ? ops[o].rhs_src : ops[o].lhs_src;
+      const uint16_t idx = side ? ops[o].rhs_idx : ops[o].lhs_idx;
+      double x = 0.0;
+      if (src == 0) x = idx < n_in ? in[idx][i] : 0.0;
+      else if (src == 1) x = idx < n_consts ? consts[idx] : 0.0;
+      else if (src == 2) x = idx < o ? tmp[idx] : 0.0;
+      v[side] = x;
+    }
+    double r;
+    if (ops[o].op >= 6) r = fe_unop64(ops[o].op, v[0]);
+    else switch (ops[o].op) {
+      case 0: r = v[0] + v[1]; break;
+      case 1: r = v[0] - v[1]; break;
+      case 2: r = v[0] * v[1]; break;
+      case 3: r = v[0] / v[1]; break;
+      case 4: r = v[0] < v[1] ? v[0] : v[1]; break;
+      default: r = v[0] > v[1] ? v[0] : v[1]; break;
+    }
+    tmp[o] = r;
+  }
+  return tmp[n_ops - 1];
+}
+
+static double fe_red64(int reduce_op, double a, double b) {
+  if (reduce_op == 0) return a + b;
+  if (reduce_op == 1) return a > b ? a : b;
+  return a < b ? a : b;
+}
+
+double oracle_fused_elementwise_f64(const oracle_fused_op* ops, int64_t n_ops, const double* const* in, int64_t n_in,
+                                    const double* consts, int64_t n_consts, int64_t n, int reduce_op, double* dst,
+                                    int exact) {
+  if (n <= 0 || n_ops <= 0) return 0.0;
+  double* tmp = (double*)malloc(sizeof(double) * (size_t)n_ops);
+  const int has_reduce = reduce_op != 255;
+  const double init = reduce_op == 1 ? -INFINITY : reduce_op == 2 ? INFINITY : 0.0;
+  double acc[4][4];
+  for (int a = 0; a < 4; ++a) for (int l = 0; l < 4; ++l) acc[a][l] = init;
+  int64_t i = 0;
+  const int64_t n16 = n & ~(int64_t)15, n4 = n & ~(int64_t)3;
+  for (; i < n16; i += 16)
+    for (int u = 0; u < 4; ++u)
+      for (int l = 0; l < 4; ++l) {
+        const int64_t e = i + u * 4 + l;
+        const double v = fe_element64(ops, n_ops, in, n_in, consts, n_consts, e, tmp);
+        if (has_reduce) acc[u][l] = fe_red64(reduce_op, acc[u][l], v);
+        else dst[e] = v;
+      }
+  for (; i < n4; i += 4)
+    for (int l = 0; l < 4; ++l) {
+      const double v = fe_element64(ops, n_ops, in, n_in, consts, n_consts, i + l, tmp);
+      if (has_reduce) acc[0][l] = fe_red64(reduce_op, acc[0][l], v);
+      else dst[i + l] = v;
+    }
+  double scalar_acc = 0.0;
+  int first = 1;
+  for (; i < n; ++i) {
+    const double v = fe_element64(ops, n_ops, in, n_in, consts, n_consts, i, tmp);
+    if (!has_reduce) { dst[i] = v; continue; }
+    if (reduce_op == 0) scalar_acc += v;
+    else if (first) scalar_acc = v;
+    else scalar_acc = fe_red64(reduce_op, scalar_acc, v);
+    first = 0;
+  }
+  free(tmp);
+  if (!has_reduce) return 0.0;
+  double a0[4];
+  for (int l = 0; l < 4; ++l) {
+    double t = fe_red64(reduce_op, acc[0][l], acc[1][l]);
+    t = fe_red64(reduce_op, t, acc[2][l]);
+    a0[l] = fe_red64(reduce_op, t, acc[3][l]);
+  }
+  const double s0 = fe_red64(reduce_op, a0[0], a0[2]), s1 = fe_red64(reduce_op, a0[1], a0[3]);
+  const double r = fe_red64(reduce_op, s0, s1);
+  if (exact && reduce_op != 0) {
+    if (first) return r;
+    if (n4 == 0) return scalar_acc;
+    return fe_red64(reduce_op, r, scalar_acc);
+  }
+  return r + scalar_acc;
+}
+
 int oracle_max_threads(void) {
   long n = sysconf(_SC_NPROCESSORS_ONLN);
   return n > 0 ? (int)n : 1;

@@ -207,7 +207,7 @@ def sync_status(stream=None) -> None:
 
 def fused_elementwise(ops, inputs, constants=(), *, reduce_op=_capi.REDUCE_NONE, out=None, stream=None):
     """Run a fused op chain (the reference's ``FusedOpDesc`` program, ``rust-engine/src/x86_emitter.rs:1937-1953``)
-    over CUDA ``float32`` tensors of equal size in one kernel.
+    over CUDA ``float32`` (or ``float64``) tensors of equal size and dtype in one kernel.
 
     ``ops``: ``[(op, lhs_src, lhs_idx, rhs_src, rhs_idx), ...]``. With ``reduce_op`` 255 returns the result
     tensor (``out`` or a new one, shaped like ``inputs[0]``); with 0 / 1 / 2 returns a 0-d ``float64`` CUDA
@@ -218,13 +218,17 @@ def fused_elementwise(ops, inputs, constants=(), *, reduce_op=_capi.REDUCE_NONE,
     if not inputs:
         raise ValueError("fused_elementwise() needs at least one input tensor")
     n = inputs[0].numel()
+    dt = inputs[0].dtype
+    if dt not in (torch.float32, torch.float64):
+        raise ValueError("inputs must be float32 or float64")
+    f64 = dt == torch.float64
     for t in inputs:
-        if not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n:
-            raise ValueError("inputs must be contiguous CUDA float32 tensors of equal size")
+        if not t.is_cuda or t.dtype != dt or not t.is_contiguous() or t.numel() != n:
+            raise ValueError("inputs must be contiguous CUDA tensors of one dtype and equal size")
     dev = inputs[0].device
     arr = _capi.pack_fused_ops(ops)
     ptrs = (ctypes.c_void_p * len(inputs))(*[t.data_ptr() for t in inputs])
-    consts = (ctypes.c_float * max(len(constants), 1))(*[float(c) for c in constants])
+    consts = ((ctypes.c_double if f64 else ctypes.c_float) * max(len(constants), 1))(*[float(c) for c in constants])
     reduce = reduce_op != _capi.REDUCE_NONE
     if reduce:
         res = torch.zeros((), device=dev, dtype=torch.float64)
@@ -232,12 +236,13 @@ def fused_elementwise(ops, inputs, constants=(), *, reduce_op=_capi.REDUCE_NONE,
     else:
         if out is None:
             out = torch.empty_like(inputs[0])
-        elif not out.is_cuda or out.dtype != torch.float32 or not out.is_contiguous() or out.numel() != n:
-            raise ValueError("out must be a contiguous CUDA float32 tensor of the inputs' size")
+        elif not out.is_cuda or out.dtype != dt or not out.is_contiguous() or out.numel() != n:
+            raise ValueError("out must be a contiguous CUDA tensor of the inputs' dtype and size")
         dst_ptr, res_ptr = out.data_ptr(), None
     s = stream if stream is not None else torch.cuda.current_stream(dev).cuda_stream
     with torch.cuda.device(dev):
-        rc = _capi.load().symplex_b200_fused_elementwise_f32(arr, len(ops), ptrs, len(inputs), consts, len(constants), n,
-                                                             int(reduce_op), dst_ptr, res_ptr, s)
+        lib = _capi.load()
+        fn = lib.symplex_b200_fused_elementwise_f64 if f64 else lib.symplex_b200_fused_elementwise_f32
+        rc = fn(arr, len(ops), ptrs, len(inputs), consts, len(constants), n, int(reduce_op), dst_ptr, res_ptr, s)
     _capi.check(rc)
     return res if reduce else out

@@ -120,13 +120,18 @@ SIGNATURES = {
     "symplex_b200_launch_count": (c_uint64, []),
     "symplex_simd_fused_elementwise_f32": (c_double, [ctypes.POINTER(FusedOp), c_size_t, ctypes.POINTER(c_void_p), c_size_t,
                                                       ctypes.POINTER(c_float), c_size_t, c_size_t, c_uint8, _F32P]),
+    "symplex_simd_fused_elementwise_f64": (c_double, [ctypes.POINTER(FusedOp), c_size_t, ctypes.POINTER(c_void_p), c_size_t,
+                                                      ctypes.POINTER(c_double), c_size_t, c_size_t, c_uint8, _F32P]),
+    "symplex_b200_fused_elementwise_f64": (c_int, [ctypes.POINTER(FusedOp), c_size_t, ctypes.POINTER(c_void_p), c_size_t,
+                                                   ctypes.POINTER(c_double), c_size_t, c_int64, c_int, _F32P, c_void_p,
+                                                   c_void_p]),
     "symplex_b200_fused_elementwise_f32": (c_int, [ctypes.POINTER(FusedOp), c_size_t, ctypes.POINTER(c_void_p), c_size_t,
                                                    ctypes.POINTER(c_float), c_size_t, c_int64, c_int, _F32P, c_void_p,
                                                    c_void_p]),
     "symplex_cuda_elementwise": (c_int64, [_F32P, _F32P, _F32P, c_int64, c_int]),
     "symplex_b200_fused_program_info": (c_int, [ctypes.POINTER(FusedOp), c_size_t, c_size_t, ctypes.POINTER(c_int),
                                                 ctypes.POINTER(c_int)]),
-    "symplex_b200_fused_elementwise_plan": (c_int, [c_int, c_int64, c_int, ctypes.POINTER(c_int32 * 3),
+    "symplex_b200_fused_elementwise_plan": (c_int, [c_int, c_int64, c_int, c_int, ctypes.POINTER(c_int32 * 3),
                                                     ctypes.POINTER(c_int32 * 3), ctypes.POINTER(c_int32)]),
     "symplex_b200_hardware_target": (c_int, [ctypes.POINTER(Target)]),
     "symplex_b200_micro_kernel_config": (None, [c_uint8, c_size_t] + [ctypes.POINTER(c_size_t)] * 5),

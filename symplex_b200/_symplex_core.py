@@ -65,6 +65,21 @@ def cuda_info() -> str:
             "symplex_b200 tcgen05 GEMM library")
 
 
+def _simd_fused_elementwise(ops, input_ptrs, constants, n, reduce_op, dst_ptr, f64: bool) -> float:
+    import math
+    lib = _capi.load()
+    arr = _capi.pack_fused_ops(ops)
+    ptrs = (ctypes.c_void_p * max(len(input_ptrs), 1))(*[int(p) for p in input_ptrs])
+    ctype = ctypes.c_double if f64 else ctypes.c_float
+    consts = (ctype * max(len(constants), 1))(*[float(c) for c in constants])
+    fn = lib.symplex_simd_fused_elementwise_f64 if f64 else lib.symplex_simd_fused_elementwise_f32
+    v = fn(arr, len(ops), ptrs, len(input_ptrs), consts, len(constants), int(n), int(reduce_op),
+           int(dst_ptr) if dst_ptr else None)
+    if math.isnan(v) and _capi.last_error() != "no error":
+        raise _capi.SymplexB200Error(_capi.ERR_EXEC, _capi.last_error())
+    return float(v)
+
+
 def simd_fused_elementwise_f32(ops, input_ptrs, constants, n: int, reduce_op: int, dst_ptr: int) -> float:
     """``python/src/lib.rs:1686-1695``: run a fused op chain over ``n`` elements of host ``float32`` arrays.
 
@@ -72,17 +87,12 @@ def simd_fused_elementwise_f32(ops, input_ptrs, constants, n: int, reduce_op: in
     ints; ``reduce_op`` 0 / 1 / 2 returns the sum / max / min, 255 writes to ``dst_ptr`` and returns 0.0.
     One GPU pass per chunk of the arrays (single kernel: loads, the whole chain, store or reduction).
     """
-    import ctypes
-    import math
-    lib = _capi.load()
-    arr = _capi.pack_fused_ops(ops)
-    ptrs = (ctypes.c_void_p * max(len(input_ptrs), 1))(*[int(p) for p in input_ptrs])
-    consts = (ctypes.c_float * max(len(constants), 1))(*[float(c) for c in constants])
-    v = lib.symplex_simd_fused_elementwise_f32(arr, len(ops), ptrs, len(input_ptrs), consts, len(constants), int(n),
-                                               int(reduce_op), int(dst_ptr) if dst_ptr else None)
-    if math.isnan(v) and _capi.last_error() != "no error":
-        raise _capi.SymplexB200Error(_capi.ERR_EXEC, _capi.last_error())
-    return float(v)
+    return _simd_fused_elementwise(ops, input_ptrs, constants, n, reduce_op, dst_ptr, False)
+
+
+def simd_fused_elementwise_f64(ops, input_ptrs, constants, n: int, reduce_op: int, dst_ptr: int) -> float:
+    """``python/src/lib.rs:1700-1709``: the same for ``float64`` arrays and constants."""
+    return _simd_fused_elementwise(ops, input_ptrs, constants, n, reduce_op, dst_ptr, True)
 
 
 def micro_kernel_config(target: str = "server", element_type: str = "fp32") -> dict:

@@ -531,27 +531,29 @@ static void* fe_reduce_scratch(DeviceState* st) {
   return st->fe_scratch + (st->fe_next.fetch_add(1) % FE_SCRATCH_SETS) * FE_REDUCE_SCRATCH_BYTES;
 }
 
-static int fe_device(const symplex_fused_op* ops, size_t n_ops, const float* const* inputs, size_t n_inputs,
-                     const float* constants, size_t n_constants, int64_t n, int reduce_op, float* dst, double* result,
-                     cudaStream_t stream) {
+static int fe_device(const symplex_fused_op* ops, size_t n_ops, const void* const* inputs, size_t n_inputs,
+                     const void* constants, size_t n_constants, int64_t n, int reduce_op, void* dst, double* result,
+                     int elem_bytes, cudaStream_t stream) {
   if (n < 0) return fail(SX_ERR_INVALID, "negative element count");
   if (n == 0 || n_ops == 0) return SX_OK;  // the reference returns before touching anything
   auto prog = std::make_unique<FeProgram>();
   int rc = compile_fused_program(reinterpret_cast<const FeSrcOp*>(ops), n_ops, n_inputs, constants, n_constants,
-                                 prog.get());
+                                 elem_bytes, prog.get());
   if (rc != SX_OK) return rc;
   DeviceState* st = nullptr;
   if ((rc = device_state(&st)) != SX_OK) return rc;
   void* red = reduce_op != FE_REDUCE_NONE ? fe_reduce_scratch(st) : nullptr;
-  rc = launch_fused_elementwise(*prog, inputs, n, reduce_op, dst, result, red, st->status, st->num_sms, stream);
+  rc = launch_fused_elementwise(*prog, inputs, n, reduce_op, dst, result, red, st->status, st->num_sms, elem_bytes,
+                                stream);
   if (rc == SX_OK) ++g_launches;
   return rc;
 }
 
 // Host arrays in, host array (or the reduced scalar) out. The element range is cut into chunks that run as a
 // three-stream pipeline: copy-in of chunk c+1, the kernel on chunk c and copy-out of chunk c-1 overlap.
-static int fe_host(const symplex_fused_op* ops, size_t n_ops, const float* const* inputs, size_t n_inputs,
-                   const float* constants, size_t n_constants, size_t n, int reduce_op, float* dst, double* value) {
+static int fe_host(const symplex_fused_op* ops, size_t n_ops, const void* const* inputs, size_t n_inputs,
+                   const void* constants, size_t n_constants, size_t n, int reduce_op, void* dst, int elem_bytes,
+                   double* value) {
   *value = 0.0;
   if (n == 0 || n_ops == 0) return SX_OK;
   const bool reduce = reduce_op != FE_REDUCE_NONE;
@@ -559,7 +561,7 @@ static int fe_host(const symplex_fused_op* ops, size_t n_ops, const float* const
   if (!reduce && dst == nullptr) return fail(SX_ERR_INVALID, "null dst");
   auto prog = std::make_unique<FeProgram>();
   int rc = compile_fused_program(reinterpret_cast<const FeSrcOp*>(ops), n_ops, n_inputs, constants, n_constants,
-                                 prog.get());
+                                 elem_bytes, prog.get());
   if (rc != SX_OK) return rc;
   for (int i = 0; i < prog->n_inputs; ++i)
     if (inputs == nullptr || inputs[prog->input_map[i]] == nullptr) return fail(SX_ERR_INVALID, "null input array");
@@ -584,37 +586,39 @@ static int fe_host(const symplex_fused_op* ops, size_t n_ops, const float* const
   }
   // Arena: one device array per used input, the output array, one double per chunk.
   const int ni = prog->n_inputs;
-  const size_t arr = align256(n * sizeof(float));
+  const size_t eb = (size_t)elem_bytes;
+  const size_t arr = align256(n * eb);
   void* arena = nullptr;
   if ((rc = host_buf(5, arr * (size_t)(ni + 1) + 64 * sizeof(double), &arena)) != SX_OK) return rc;
   char* base = static_cast<char*>(arena);
   double* d_res = reinterpret_cast<double*>(base + arr * (size_t)(ni + 1));
-  size_t chunk = size_t(8) << 20;  // elements per chunk: 32 MiB per array
+  size_t chunk = (size_t(32) << 20) / eb;  // elements per chunk: 32 MiB per array
   if (chunk * 64 < n) chunk = ((n + 63) / 64 + 4095) / 4096 * 4096;
   const int nchunks = (int)((n + chunk - 1) / chunk);
   // Device arrays are numbered like the compacted program inputs.
   auto dprog = std::make_unique<FeProgram>(*prog);
   for (int i = 0; i < ni; ++i) dprog->input_map[i] = i;
-  const float* d_in[FE_MAX_INPUTS] = {};
+  const void* d_in[FE_MAX_INPUTS] = {};
   void* red = reduce ? fe_reduce_scratch(st) : nullptr;
   for (int c = 0; c < nchunks; ++c) {
     const size_t e0 = (size_t)c * chunk, cnt = (e0 + chunk <= n) ? chunk : n - e0;
     for (int i = 0; i < ni; ++i) {
-      float* d = reinterpret_cast<float*>(base + arr * (size_t)i) + e0;
-      SX_CUDA(cudaMemcpyAsync(d, inputs[prog->input_map[i]] + e0, cnt * sizeof(float), cudaMemcpyHostToDevice, h.h2d));
+      char* d = base + arr * (size_t)i + e0 * eb;
+      SX_CUDA(cudaMemcpyAsync(d, static_cast<const char*>(inputs[prog->input_map[i]]) + e0 * eb, cnt * eb,
+                              cudaMemcpyHostToDevice, h.h2d));
       d_in[i] = d;
     }
     SX_CUDA(cudaEventRecord(h.ev_in[c], h.h2d));
     SX_CUDA(cudaStreamWaitEvent(h.stream, h.ev_in[c], 0));
-    float* d_dst = reinterpret_cast<float*>(base + arr * (size_t)ni) + e0;
+    char* d_dst = base + arr * (size_t)ni + e0 * eb;
     rc = launch_fused_elementwise(*dprog, d_in, (long long)cnt, reduce_op, d_dst, d_res + c, red, st->status,
-                                  st->num_sms, h.stream);
+                                  st->num_sms, elem_bytes, h.stream);
     if (rc != SX_OK) return rc;
     ++g_launches;
     if (!reduce) {
       SX_CUDA(cudaEventRecord(h.ev_out[c], h.stream));
       SX_CUDA(cudaStreamWaitEvent(h.d2h, h.ev_out[c], 0));
-      SX_CUDA(cudaMemcpyAsync(dst + e0, d_dst, cnt * sizeof(float), cudaMemcpyDeviceToHost, h.d2h));
+      SX_CUDA(cudaMemcpyAsync(static_cast<char*>(dst) + e0 * eb, d_dst, cnt * eb, cudaMemcpyDeviceToHost, h.d2h));
     }
   }
   double parts[64];
@@ -838,12 +842,13 @@ int symplex_cuda_device_info(symplex_device_info* out) {
 
 uint64_t symplex_b200_launch_count(void) { return g_launches.load(); }
 
-int symplex_b200_fused_elementwise_plan(int n_inputs, int64_t n, int num_sms, int32_t grid_dims[3],
-                                        int32_t block_dims[3], int32_t* shared_mem_bytes) {
-  if (n_inputs < 0 || n_inputs > FE_MAX_INPUTS || n <= 0 || !grid_dims || !block_dims || !shared_mem_bytes)
-    return fail(SX_ERR_INVALID, "bad argument (0..16 input arrays, n > 0)");
+int symplex_b200_fused_elementwise_plan(int n_inputs, int64_t n, int element_bytes, int num_sms,
+                                        int32_t grid_dims[3], int32_t block_dims[3], int32_t* shared_mem_bytes) {
+  if (n_inputs < 0 || n_inputs > FE_MAX_INPUTS || n <= 0 || (element_bytes != 4 && element_bytes != 8) || !grid_dims ||
+      !block_dims || !shared_mem_bytes)
+    return fail(SX_ERR_INVALID, "bad argument (0..16 input arrays, n > 0, 4- or 8-byte elements)");
   int g = 0, b = 0, sm = 0;
-  describe_fused_elementwise(n_inputs, n, num_sms > 0 ? num_sms : 148, &g, &b, &sm);
+  describe_fused_elementwise(n_inputs, n, element_bytes, num_sms > 0 ? num_sms : 148, &g, &b, &sm);
   grid_dims[0] = g; grid_dims[1] = 1; grid_dims[2] = 1;
   block_dims[0] = b; block_dims[1] = 1; block_dims[2] = 1;
   *shared_mem_bytes = sm;
@@ -990,18 +995,36 @@ int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm
 int symplex_b200_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_ops, const float* const* inputs,
                                        size_t n_inputs, const float* constants, size_t n_constants, int64_t n,
                                        int reduce_op, float* dst, double* result, void* stream) {
-  return fe_device(ops, n_ops, inputs, n_inputs, constants, n_constants, n, reduce_op, dst, result,
-                   static_cast<cudaStream_t>(stream));
+  return fe_device(ops, n_ops, reinterpret_cast<const void* const*>(inputs), n_inputs, constants, n_constants, n,
+                   reduce_op, dst, result, 4, static_cast<cudaStream_t>(stream));
+}
+int symplex_b200_fused_elementwise_f64(const symplex_fused_op* ops, size_t n_ops, const double* const* inputs,
+                                       size_t n_inputs, const double* constants, size_t n_constants, int64_t n,
+                                       int reduce_op, double* dst, double* result, void* stream) {
+  return fe_device(ops, n_ops, reinterpret_cast<const void* const*>(inputs), n_inputs, constants, n_constants, n,
+                   reduce_op, dst, result, 8, static_cast<cudaStream_t>(stream));
 }
 
-double symplex_simd_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_ops, const float* const* input_ptrs,
-                                          size_t n_inputs, const float* constants, size_t n_constants, size_t n,
-                                          uint8_t reduce_op, float* dst_ptr) {
+static double fe_host_value(const symplex_fused_op* ops, size_t n_ops, const void* const* inputs, size_t n_inputs,
+                            const void* constants, size_t n_constants, size_t n, int reduce_op, void* dst,
+                            int elem_bytes) {
   double v = 0.0;
-  const int rc = fe_host(ops, n_ops, input_ptrs, n_inputs, constants, n_constants, n, reduce_op, dst_ptr, &v);
+  const int rc = fe_host(ops, n_ops, inputs, n_inputs, constants, n_constants, n, reduce_op, dst, elem_bytes, &v);
   if (rc != SX_OK) return __builtin_nan("");
   snprintf(g_err, sizeof(g_err), "no error");  // lets a caller tell a computed NaN from a failure
   return v;
+}
+double symplex_simd_fused_elementwise_f32(const symplex_fused_op* ops, size_t n_ops, const float* const* input_ptrs,
+                                          size_t n_inputs, const float* constants, size_t n_constants, size_t n,
+                                          uint8_t reduce_op, float* dst_ptr) {
+  return fe_host_value(ops, n_ops, reinterpret_cast<const void* const*>(input_ptrs), n_inputs, constants, n_constants,
+                       n, reduce_op, dst_ptr, 4);
+}
+double symplex_simd_fused_elementwise_f64(const symplex_fused_op* ops, size_t n_ops, const double* const* input_ptrs,
+                                          size_t n_inputs, const double* constants, size_t n_constants, size_t n,
+                                          uint8_t reduce_op, double* dst_ptr) {
+  return fe_host_value(ops, n_ops, reinterpret_cast<const void* const*>(input_ptrs), n_inputs, constants, n_constants,
+                       n, reduce_op, dst_ptr, 8);
 }
 
 int64_t symplex_cuda_elementwise(const float* a, const float* b, float* dst, int64_t n, int op) {
@@ -1012,16 +1035,16 @@ int64_t symplex_cuda_elementwise(const float* a, const float* b, float* dst, int
     return -1;
   }
   const symplex_fused_op prog = {(uint8_t)op, 0, 0, 0, 0, 1};
-  const float* in[2] = {a, b};
+  const void* in[2] = {a, b};
   double v = 0.0;
-  return fe_host(&prog, 1, in, 2, nullptr, 0, (size_t)n, FE_REDUCE_NONE, dst, &v) == SX_OK ? 0 : -1;
+  return fe_host(&prog, 1, in, 2, nullptr, 0, (size_t)n, FE_REDUCE_NONE, dst, 4, &v) == SX_OK ? 0 : -1;
 }
 
 int symplex_b200_fused_program_info(const symplex_fused_op* ops, size_t n_ops, size_t n_inputs, int* n_slots,
                                     int* n_inputs_used) {
   auto prog = std::make_unique<FeProgram>();
   static const float zeros[1] = {0.0f};
-  const int rc = compile_fused_program(reinterpret_cast<const FeSrcOp*>(ops), n_ops, n_inputs, zeros, 0, prog.get());
+  const int rc = compile_fused_program(reinterpret_cast<const FeSrcOp*>(ops), n_ops, n_inputs, zeros, 0, 4, prog.get());
   if (rc != SX_OK) return rc;
   if (n_slots) *n_slots = prog->n_slots;
   if (n_inputs_used) *n_inputs_used = prog->n_inputs;

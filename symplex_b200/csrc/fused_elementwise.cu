@@ -19,6 +19,7 @@
 // Arithmetic follows the reference op by op: add / sub / mul / div are separately rounded IEEE operations
 // (never contracted into FMAs), sqrt is correctly rounded, min / max follow the AVX2 forms
 // (l < r ? l : r and l > r ? l : r). exp, log, sin, cos, tanh use CUDA's libm (<= 2 ulp).
+// Everything is templated on the element type: float (simd_fused_elementwise_f32) and double (the _f64 twin).
 #include <cstring>
 #include <memory>
 #include <vector>
@@ -30,15 +31,16 @@
 namespace sx {
 
 // ------------------------------------------------------------------------------------------------ host compile
-int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, const float* constants,
-                          size_t n_constants, FeProgram* out) {
+int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, const void* constants,
+                          size_t n_constants, int elem_bytes, FeProgram* out) {
   if (ops == nullptr || n_ops == 0) return set_last_error(SX_ERR_INVALID, "empty program");
+  if (elem_bytes != 4 && elem_bytes != 8) return set_last_error(SX_ERR_INVALID, "element size must be 4 or 8");
   if (n_ops > (size_t)FE_MAX_OPS) return set_last_error(SX_ERR_INVALID, "program has more than 1024 ops");
   if (n_constants && constants == nullptr) return set_last_error(SX_ERR_INVALID, "null constants");
   enum : uint8_t { REF = 200 };  // temporary kind: result of an earlier op
   struct Operand {
     uint8_t kind;
-    uint32_t v;
+    uint64_t v;
   };
   FeProgram& P = *out;
   P.n_ops = (int)n_ops;
@@ -57,11 +59,11 @@ int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, con
         compact[idx] = P.n_inputs;
         P.input_map[P.n_inputs++] = idx;
       }
-      return {FE_IN, (uint32_t)compact[idx]};
+      return {FE_IN, (uint64_t)compact[idx]};
     }
     if (src == 1) {
-      uint32_t bits = 0;
-      if (idx < n_constants) memcpy(&bits, &constants[idx], 4);
+      uint64_t bits = 0;  // a float's bits sit in the low word
+      if (idx < n_constants) memcpy(&bits, static_cast<const char*>(constants) + (size_t)idx * elem_bytes, elem_bytes);
       return {FE_IMM, bits};
     }
     if (src == 2 && idx < i) return {REF, idx};
@@ -82,7 +84,7 @@ int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, con
   for (size_t i = 0; i < n_ops; ++i) {
     FeOp& o = P.ops[i];
     o.opcode = ops[i].op <= 15 ? ops[i].op : 16;  // 16: pass the left operand through
-    auto lower = [&](const Operand& x, uint8_t* kind, uint32_t* v) {
+    auto lower = [&](const Operand& x, uint8_t* kind, uint64_t* v) {
       if (x.kind != REF) {
         *kind = x.kind;
         *v = x.v;
@@ -91,7 +93,7 @@ int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, con
         *v = 0;
       } else {
         *kind = FE_SLOT;
-        *v = (uint32_t)slot_of[x.v];
+        *v = (uint64_t)slot_of[x.v];
       }
     };
     lower(L[i], &o.lkind, &o.l);
@@ -123,14 +125,14 @@ int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, con
 }
 
 // ------------------------------------------------------------------------------------------------ device side
-constexpr int FE_THREADS = 256;       // consumer threads; the ring kernel adds one producer warp
+constexpr int FE_THREADS = 256;  // consumer threads; the ring kernel adds one producer warp
 constexpr int FE_MAX_STAGES = 16;
 
-template <int MAXOPS>
+template <typename T, int MAXOPS>
 struct FeKernelArgs {
   long long n;
-  const float* in[FE_MAX_INPUTS];
-  float* dst;
+  const T* in[FE_MAX_INPUTS];
+  T* dst;
   double* partials;
   unsigned* ticket;
   double* result;
@@ -139,33 +141,84 @@ struct FeKernelArgs {
   FeOp ops[MAXOPS];
 };
 
-template <int W>
-__device__ __forceinline__ void fe_apply(uint32_t opcode, const float (&l)[W], const float (&r)[W], float (&o)[W]) {
+// Per-type arithmetic: explicitly rounded intrinsics so that nothing is contracted into an FMA.
+template <typename T>
+struct FeMath;
+template <>
+struct FeMath<float> {
+  static constexpr int VE = 4;  // elements per 16-byte vector
+  __device__ static float imm(uint64_t bits) { return __uint_as_float((uint32_t)bits); }
+  __device__ static float add(float a, float b) { return __fadd_rn(a, b); }
+  __device__ static float sub(float a, float b) { return __fsub_rn(a, b); }
+  __device__ static float mul(float a, float b) { return __fmul_rn(a, b); }
+  __device__ static float div(float a, float b) { return __fdiv_rn(a, b); }
+  __device__ static float sqrt(float a) { return __fsqrt_rn(a); }
+  __device__ static float abs(float a) { return fabsf(a); }
+  __device__ static float exp(float a) { return expf(a); }
+  __device__ static float log(float a) { return logf(a); }
+  __device__ static float sin(float a) { return sinf(a); }
+  __device__ static float cos(float a) { return cosf(a); }
+  __device__ static float tanh(float a) { return tanhf(a); }
+  __device__ static float max(float a, float b) { return fmaxf(a, b); }
+  __device__ static float min(float a, float b) { return fminf(a, b); }
+  __device__ static float inf() { return INFINITY; }
+  __device__ static void load16(const float* p, float (&o)[4]) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    o[0] = q.x, o[1] = q.y, o[2] = q.z, o[3] = q.w;
+  }
+  __device__ static void store16_streaming(float* p, const float (&v)[4]) {
+    __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
+  }
+};
+template <>
+struct FeMath<double> {
+  static constexpr int VE = 2;
+  __device__ static double imm(uint64_t bits) { return __longlong_as_double((long long)bits); }
+  __device__ static double add(double a, double b) { return __dadd_rn(a, b); }
+  __device__ static double sub(double a, double b) { return __dsub_rn(a, b); }
+  __device__ static double mul(double a, double b) { return __dmul_rn(a, b); }
+  __device__ static double div(double a, double b) { return __ddiv_rn(a, b); }
+  __device__ static double sqrt(double a) { return __dsqrt_rn(a); }
+  __device__ static double abs(double a) { return fabs(a); }
+  __device__ static double exp(double a) { return ::exp(a); }
+  __device__ static double log(double a) { return ::log(a); }
+  __device__ static double sin(double a) { return ::sin(a); }
+  __device__ static double cos(double a) { return ::cos(a); }
+  __device__ static double tanh(double a) { return ::tanh(a); }
+  __device__ static double max(double a, double b) { return fmax(a, b); }
+  __device__ static double min(double a, double b) { return fmin(a, b); }
+  __device__ static double inf() { return (double)INFINITY; }
+  __device__ static void load16(const double* p, double (&o)[2]) {
+    const double2 q = *reinterpret_cast<const double2*>(p);
+    o[0] = q.x, o[1] = q.y;
+  }
+  __device__ static void store16_streaming(double* p, const double (&v)[2]) {
+    __stcs(reinterpret_cast<double2*>(p), make_double2(v[0], v[1]));
+  }
+};
+
+// Unary ops (and the pass-through for unknown codes) on W values.
+template <typename T, int W>
+__device__ __forceinline__ void fe_unary(uint32_t opcode, const T (&l)[W], T (&o)[W]) {
+  using M = FeMath<T>;
   switch (opcode) {
 #define FE_CASE(code, expr)                         \
   case code:                                        \
     _Pragma("unroll") for (int w = 0; w < W; ++w) { \
-      const float a = l[w], b = r[w];               \
-      (void)b;                                      \
+      const T a = l[w];                             \
       o[w] = (expr);                                \
     }                                               \
     break;
-    FE_CASE(0, __fadd_rn(a, b))
-    FE_CASE(1, __fsub_rn(a, b))
-    FE_CASE(2, __fmul_rn(a, b))
-    FE_CASE(3, __fdiv_rn(a, b))
-    FE_CASE(4, (a < b) ? a : b)
-    FE_CASE(5, (a > b) ? a : b)
     FE_CASE(6, -a)
-    FE_CASE(7, fabsf(a))
-    FE_CASE(8, __fsqrt_rn(a))
-    FE_CASE(9, expf(a))
-    FE_CASE(10, logf(a))
-    FE_CASE(11, sinf(a))
-    FE_CASE(12, cosf(a))
-    FE_CASE(13, tanhf(a))
-    FE_CASE(14, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-a))))
-    FE_CASE(15, fmaxf(a, 0.0f))
+    FE_CASE(7, M::abs(a))
+    FE_CASE(8, M::sqrt(a))
+    FE_CASE(9, M::exp(a))
+    FE_CASE(10, M::log(a))
+    FE_CASE(11, M::sin(a))
+    FE_CASE(12, M::cos(a))
+    FE_CASE(13, M::tanh(a))
+    FE_CASE(14, M::div(T(1), M::add(T(1), M::exp(-a))))
+    FE_CASE(15, M::max(a, T(0)))
 #undef FE_CASE
     default:
 #pragma unroll
@@ -174,47 +227,23 @@ __device__ __forceinline__ void fe_apply(uint32_t opcode, const float (&l)[W], c
   }
 }
 
-// Input loaders: hand the interpreter W values of input `idx` for this thread.
-template <int U>
-struct RingLoader {  // float4 vectors out of one ring stage; input i starts at base + i * stride
-  const float* base;
-  int stride;
-  __device__ __forceinline__ void load(uint32_t idx, float (&o)[U * 4]) const {
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const float4 q = *reinterpret_cast<const float4*>(base + (size_t)idx * stride + u * (FE_THREADS * 4));
-      o[u * 4 + 0] = q.x, o[u * 4 + 1] = q.y, o[u * 4 + 2] = q.z, o[u * 4 + 3] = q.w;
-    }
-  }
-};
-template <int U>
-struct GlobalLoader {  // scalars straight from global memory at element offsets e[u]
-  const float* const* in;
-  long long e[U];
-  bool ok[U];
-  __device__ __forceinline__ void load(uint32_t idx, float (&o)[U]) const {
-    const float* p = in[idx];
-#pragma unroll
-    for (int u = 0; u < U; ++u) o[u] = ok[u] ? __ldg(p + e[u]) : 0.0f;
-  }
-};
-
 // The six exactly rounded binary ops on operand accessors (callables w -> value). `out` may be the array an
 // accessor reads: element w is read before it is written.
-template <int W, class LF, class RF>
-__device__ __forceinline__ void fe_binary(uint32_t opcode, LF lf, RF rf, float (&out)[W]) {
+template <typename T, int W, class LF, class RF>
+__device__ __forceinline__ void fe_binary(uint32_t opcode, LF lf, RF rf, T (&out)[W]) {
+  using M = FeMath<T>;
   switch (opcode) {
 #define FE_BIN(code, expr)                          \
   case code:                                        \
     _Pragma("unroll") for (int w = 0; w < W; ++w) { \
-      const float a = lf(w), b = rf(w);             \
+      const T a = lf(w), b = rf(w);                 \
       out[w] = (expr);                              \
     }                                               \
     break;
-    FE_BIN(0, __fadd_rn(a, b))
-    FE_BIN(1, __fsub_rn(a, b))
-    FE_BIN(2, __fmul_rn(a, b))
-    FE_BIN(3, __fdiv_rn(a, b))
+    FE_BIN(0, M::add(a, b))
+    FE_BIN(1, M::sub(a, b))
+    FE_BIN(2, M::mul(a, b))
+    FE_BIN(3, M::div(a, b))
     FE_BIN(4, (a < b) ? a : b)
     default:
       FE_BIN(5, (a > b) ? a : b)
@@ -222,40 +251,69 @@ __device__ __forceinline__ void fe_binary(uint32_t opcode, LF lf, RF rf, float (
   }
 }
 
+// Input loaders: hand the interpreter W values of input `idx` for this thread.
+template <typename T, int U>
+struct RingLoader {  // 16-byte vectors out of one ring stage; input i starts at base + i * stride
+  static constexpr int VE = FeMath<T>::VE;
+  const T* base;
+  int stride;
+  __device__ __forceinline__ void load(uint32_t idx, T (&o)[U * VE]) const {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      T q[VE];
+      FeMath<T>::load16(base + (size_t)idx * stride + u * (FE_THREADS * VE), q);
+#pragma unroll
+      for (int k = 0; k < VE; ++k) o[u * VE + k] = q[k];
+    }
+  }
+};
+template <typename T, int U>
+struct GlobalLoader {  // scalars straight from global memory at element offsets e[u]
+  const T* const* in;
+  long long e[U];
+  bool ok[U];
+  __device__ __forceinline__ void load(uint32_t idx, T (&o)[U]) const {
+    const T* p = in[idx];
+#pragma unroll
+    for (int u = 0; u < U; ++u) o[u] = ok[u] ? __ldg(p + e[u]) : T(0);
+  }
+};
+
 // Interpret the program for W values per thread; the last op's values end up in `last`.
 // Binary arithmetic ops are dispatched on (left kind, right kind, opcode) to loops that read their operands
 // in place - registers of `last`, an immediate, a slot, or freshly loaded input values - so an op costs one
 // arithmetic instruction per element plus a warp-uniform dispatch; unary ops copy their operand first.
-template <int W, int MAXOPS, class Loader>
-__device__ __forceinline__ void fe_eval(const FeKernelArgs<MAXOPS>& P, const Loader& ld, float (&last)[W]) {
-  float slots[FE_MAX_SLOTS][W];
+template <typename T, int W, int MAXOPS, class Loader>
+__device__ __forceinline__ void fe_eval(const FeKernelArgs<T, MAXOPS>& P, const Loader& ld, T (&last)[W]) {
+  using M = FeMath<T>;
+  T slots[FE_MAX_SLOTS][W];
 #pragma unroll
-  for (int w = 0; w < W; ++w) last[w] = 0.0f;
+  for (int w = 0; w < W; ++w) last[w] = T(0);
   for (int i = 0; i < P.n_ops; ++i) {
     const FeOp op = P.ops[i];
     if (op.opcode < 6) {
       auto with_left = [&](auto lf) {
         switch (op.rkind) {
           case FE_IMM: {
-            const float c = __uint_as_float(op.r);
-            fe_binary<W>(op.opcode, lf, [=](int) { return c; }, last);
+            const T c = M::imm(op.r);
+            fe_binary<T, W>(op.opcode, lf, [=](int) { return c; }, last);
           } break;
           case FE_LAST:
-            fe_binary<W>(op.opcode, lf, [&](int w) { return last[w]; }, last);
+            fe_binary<T, W>(op.opcode, lf, [&](int w) { return last[w]; }, last);
             break;
           case FE_SLOT:
-            fe_binary<W>(op.opcode, lf, [&](int w) { return slots[op.r][w]; }, last);
+            fe_binary<T, W>(op.opcode, lf, [&](int w) { return slots[op.r][w]; }, last);
             break;
           default: {
-            float t[W];
-            ld.load(op.r, t);
-            fe_binary<W>(op.opcode, lf, [&](int w) { return t[w]; }, last);
+            T t[W];
+            ld.load((uint32_t)op.r, t);
+            fe_binary<T, W>(op.opcode, lf, [&](int w) { return t[w]; }, last);
           } break;
         }
       };
       switch (op.lkind) {
         case FE_IMM: {
-          const float c = __uint_as_float(op.l);
+          const T c = M::imm(op.l);
           with_left([=](int) { return c; });
         } break;
         case FE_LAST:
@@ -265,18 +323,18 @@ __device__ __forceinline__ void fe_eval(const FeKernelArgs<MAXOPS>& P, const Loa
           with_left([&](int w) { return slots[op.l][w]; });
           break;
         default: {
-          float t[W];
-          ld.load(op.l, t);
+          T t[W];
+          ld.load((uint32_t)op.l, t);
           with_left([&](int w) { return t[w]; });
         } break;
       }
     } else {
-      float l[W];
+      T l[W];
       if (op.lkind == FE_IN) {
-        ld.load(op.l, l);
+        ld.load((uint32_t)op.l, l);
       } else if (op.lkind == FE_IMM) {
 #pragma unroll
-        for (int w = 0; w < W; ++w) l[w] = __uint_as_float(op.l);
+        for (int w = 0; w < W; ++w) l[w] = M::imm(op.l);
       } else if (op.lkind == FE_LAST) {
 #pragma unroll
         for (int w = 0; w < W; ++w) l[w] = last[w];
@@ -284,7 +342,7 @@ __device__ __forceinline__ void fe_eval(const FeKernelArgs<MAXOPS>& P, const Loa
 #pragma unroll
         for (int w = 0; w < W; ++w) l[w] = slots[op.l][w];
       }
-      fe_apply<W>(op.opcode, l, l, last);
+      fe_unary<T, W>(op.opcode, l, last);
     }
     if (op.dst != FE_NO_DST) {
 #pragma unroll
@@ -293,28 +351,27 @@ __device__ __forceinline__ void fe_eval(const FeKernelArgs<MAXOPS>& P, const Loa
   }
 }
 
-__device__ __forceinline__ float fe_identity(int reduce_op) {
-  return reduce_op == 1 ? -INFINITY : reduce_op == 2 ? INFINITY : 0.0f;
-}
-__device__ __forceinline__ float fe_combine(int reduce_op, float a, float b) {
-  return reduce_op == 0 ? __fadd_rn(a, b) : reduce_op == 1 ? fmaxf(a, b) : fminf(a, b);
+template <typename T>
+__device__ __forceinline__ T fe_identity(int reduce_op) {
+  return reduce_op == 1 ? -FeMath<T>::inf() : reduce_op == 2 ? FeMath<T>::inf() : T(0);
 }
 __device__ __forceinline__ double fe_combine(int reduce_op, double a, double b) {
   return reduce_op == 0 ? a + b : reduce_op == 1 ? fmax(a, b) : fmin(a, b);
 }
 
 // acc[w] = combine(acc[w], v[w]) with the choice of the operation hoisted out of the element loop.
-template <int W>
-__device__ __forceinline__ void fe_accumulate(int reduce_op, float (&acc)[W], const float (&v)[W]) {
+template <typename T, int W>
+__device__ __forceinline__ void fe_accumulate(int reduce_op, T (&acc)[W], const T (&v)[W]) {
+  using M = FeMath<T>;
   if (reduce_op == 0) {
 #pragma unroll
-    for (int w = 0; w < W; ++w) acc[w] = __fadd_rn(acc[w], v[w]);
+    for (int w = 0; w < W; ++w) acc[w] = M::add(acc[w], v[w]);
   } else if (reduce_op == 1) {
 #pragma unroll
-    for (int w = 0; w < W; ++w) acc[w] = fmaxf(acc[w], v[w]);
+    for (int w = 0; w < W; ++w) acc[w] = M::max(acc[w], v[w]);
   } else {
 #pragma unroll
-    for (int w = 0; w < W; ++w) acc[w] = fminf(acc[w], v[w]);
+    for (int w = 0; w < W; ++w) acc[w] = M::min(acc[w], v[w]);
   }
 }
 
@@ -328,7 +385,7 @@ __device__ __forceinline__ double fe_block_reduce(int reduce_op, double v, doubl
   __syncthreads();
   if (warp == 0) {
     const int nw = (blockDim.x + 31) >> 5;
-    v = lane < nw ? smem[lane] : (double)fe_identity(reduce_op);
+    v = lane < nw ? smem[lane] : fe_identity<double>(reduce_op);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v = fe_combine(reduce_op, v, __shfl_xor_sync(0xffffffffu, v, off));
   }
@@ -337,8 +394,8 @@ __device__ __forceinline__ double fe_block_reduce(int reduce_op, double v, doubl
 
 // Fold the per-thread accumulators of the whole grid into *P.result: per block in a fixed order, then the
 // block that arrives last folds the per-block partials in index order - the same bits on every run.
-template <int W, int MAXOPS>
-__device__ __forceinline__ void fe_grid_reduce(const FeKernelArgs<MAXOPS>& P, const float (&acc)[W]) {
+template <typename T, int W, int MAXOPS>
+__device__ __forceinline__ void fe_grid_reduce(const FeKernelArgs<T, MAXOPS>& P, const T (&acc)[W]) {
   __shared__ double red[32];
   __shared__ bool is_last;
   double v = (double)acc[0];
@@ -353,7 +410,7 @@ __device__ __forceinline__ void fe_grid_reduce(const FeKernelArgs<MAXOPS>& P, co
   __syncthreads();
   if (is_last) {
     __threadfence();
-    double s = (double)fe_identity(P.reduce_op);
+    double s = fe_identity<double>(P.reduce_op);
     for (unsigned i = threadIdx.x; i < gridDim.x; i += blockDim.x) s = fe_combine(P.reduce_op, s, __ldcg(P.partials + i));
     s = fe_block_reduce(P.reduce_op, s, red);
     if (threadIdx.x == 0) {
@@ -363,35 +420,38 @@ __device__ __forceinline__ void fe_grid_reduce(const FeKernelArgs<MAXOPS>& P, co
   }
 }
 
-// Elements [first, n) one per thread with plain loads: the whole array when it is not 16-byte aligned,
-// otherwise what is left after the last full chunk.
-template <int MAXOPS>
-__device__ __forceinline__ void fe_scalar_range(const FeKernelArgs<MAXOPS>& P, long long first, long long gtid,
-                                                long long nthreads, bool reduce, float& acc) {
+// Elements [first, n) one per thread with plain loads: what is left after the last full chunk.
+template <typename T, int MAXOPS>
+__device__ __forceinline__ void fe_scalar_range(const FeKernelArgs<T, MAXOPS>& P, long long first, long long gtid,
+                                                long long nthreads, bool reduce, T& acc) {
   for (long long t = first + gtid; t < P.n; t += nthreads) {
-    GlobalLoader<1> ld;
+    GlobalLoader<T, 1> ld;
     ld.in = P.in;
     ld.e[0] = t;
     ld.ok[0] = true;
-    float r1[1];
-    fe_eval<1, MAXOPS>(P, ld, r1);
-    if (reduce)
-      acc = fe_combine(P.reduce_op, acc, r1[0]);
-    else
+    T r1[1], a1[1] = {acc};
+    fe_eval<T, 1, MAXOPS>(P, ld, r1);
+    if (reduce) {
+      fe_accumulate<T, 1>(P.reduce_op, a1, r1);
+      acc = a1[0];
+    } else {
       P.dst[t] = r1[0];
+    }
   }
 }
 
 // Ring kernel. Shared memory: [0,128) full barriers, [128,256) empty barriers, then `stages` stages of
-// n_inputs x CHUNK floats. Chunk c of the arrays goes to CTA c mod gridDim.x.
-template <int U, int MAXOPS>
-__global__ void __launch_bounds__(FE_THREADS + 32) fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<MAXOPS> P) {
-  constexpr int W = U * 4;
-  constexpr int CHUNK = FE_THREADS * W;  // floats per input per stage
+// n_inputs x CHUNK elements (16 bytes x U per consumer thread). Chunk c of the arrays goes to CTA c mod gridDim.x.
+template <typename T, int U, int MAXOPS>
+__global__ void __launch_bounds__(FE_THREADS + 32)
+fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P) {
+  constexpr int VE = FeMath<T>::VE;
+  constexpr int W = U * VE;
+  constexpr int CHUNK = FE_THREADS * W;  // elements per input per stage
   extern __shared__ __align__(128) uint8_t fe_smem[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(fe_smem);
   uint64_t* empty_bar = reinterpret_cast<uint64_t*>(fe_smem + 128);
-  float* ring = reinterpret_cast<float*>(fe_smem + 256);
+  T* ring = reinterpret_cast<T*>(fe_smem + 256);
   __shared__ int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool reduce = P.reduce_op != FE_REDUCE_NONE;
@@ -406,9 +466,9 @@ __global__ void __launch_bounds__(FE_THREADS + 32) fused_elementwise_ring_kernel
     fence_mbar_init();
   }
   __syncthreads();
-  float acc[W];
+  T acc[W];
 #pragma unroll
-  for (int w = 0; w < W; ++w) acc[w] = fe_identity(P.reduce_op);
+  for (int w = 0; w < W; ++w) acc[w] = fe_identity<T>(P.reduce_op);
 
   if (warp == FE_THREADS / 32) {
     // ---------------------------------------------------------------- producer
@@ -421,11 +481,12 @@ __global__ void __launch_bounds__(FE_THREADS + 32) fused_elementwise_ring_kernel
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(ni * CHUNK * 4));
+        mbar_arrive_expect_tx(&full_bar[stage], (uint32_t)(ni * CHUNK * sizeof(T)));
         armed |= 1u << stage;
         armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
-        float* dst = ring + (size_t)stage * ni * CHUNK;
-        for (int i = 0; i < ni; ++i) bulk_load_1d(dst + (size_t)i * CHUNK, P.in[i] + c * CHUNK, CHUNK * 4, &full_bar[stage]);
+        T* dst = ring + (size_t)stage * ni * CHUNK;
+        for (int i = 0; i < ni; ++i)
+          bulk_load_1d(dst + (size_t)i * CHUNK, P.in[i] + c * CHUNK, CHUNK * sizeof(T), &full_bar[stage]);
         if (++stage == stages) {
           stage = 0;
           phase ^= 1;
@@ -448,74 +509,81 @@ __global__ void __launch_bounds__(FE_THREADS + 32) fused_elementwise_ring_kernel
     uint32_t phase = 0;
     for (long long c = blockIdx.x; c < nchunks; c += gridDim.x) {
       if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) break;
-      RingLoader<U> ld;
-      ld.base = ring + (size_t)stage * ni * CHUNK + tid * 4;
+      RingLoader<T, U> ld;
+      ld.base = ring + (size_t)stage * ni * CHUNK + tid * VE;
       ld.stride = CHUNK;
-      float res[W];
-      fe_eval<W, MAXOPS>(P, ld, res);
+      T res[W];
+      fe_eval<T, W, MAXOPS>(P, ld, res);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp's reads of the stage are done
       if (reduce) {
-        fe_accumulate<W>(P.reduce_op, acc, res);
+        fe_accumulate<T, W>(P.reduce_op, acc, res);
       } else {
-        float* out = P.dst + c * CHUNK + tid * 4;
+        T* out = P.dst + c * CHUNK + tid * VE;
 #pragma unroll
-        for (int u = 0; u < U; ++u)
-          __stcs(reinterpret_cast<float4*>(out + u * (FE_THREADS * 4)),
-                 make_float4(res[u * 4 + 0], res[u * 4 + 1], res[u * 4 + 2], res[u * 4 + 3]));
+        for (int u = 0; u < U; ++u) {
+          T v[VE];
+#pragma unroll
+          for (int k = 0; k < VE; ++k) v[k] = res[u * VE + k];
+          FeMath<T>::store16_streaming(out + u * (FE_THREADS * VE), v);
+        }
       }
       if (++stage == stages) {
         stage = 0;
         phase ^= 1;
       }
     }
-    fe_scalar_range<MAXOPS>(P, nchunks * CHUNK, (long long)blockIdx.x * FE_THREADS + tid, (long long)gridDim.x * FE_THREADS,
-                            reduce, acc[0]);
+    fe_scalar_range<T, MAXOPS>(P, nchunks * CHUNK, (long long)blockIdx.x * FE_THREADS + tid,
+                               (long long)gridDim.x * FE_THREADS, reduce, acc[0]);
   }
-  if (reduce) fe_grid_reduce<W, MAXOPS>(P, acc);
+  if (reduce) fe_grid_reduce<T, W, MAXOPS>(P, acc);
   __syncthreads();
   if (tid == 0 && abort_flag != 0 && P.status != nullptr) atomicExch(P.status, int(ST_WAIT_TIMEOUT));
 }
 
 // Plain-load kernel for arrays that are not 16-byte aligned and for programs without inputs.
-template <int MAXOPS>
-__global__ void __launch_bounds__(FE_THREADS) fused_elementwise_plain_kernel(const __grid_constant__ FeKernelArgs<MAXOPS> P) {
+template <typename T, int MAXOPS>
+__global__ void __launch_bounds__(FE_THREADS)
+fused_elementwise_plain_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P) {
   constexpr int U = 4;
   const bool reduce = P.reduce_op != FE_REDUCE_NONE;
-  const long long T = (long long)gridDim.x * blockDim.x;
+  const long long nt = (long long)gridDim.x * blockDim.x;
   const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  float acc[U];
+  T acc[U];
 #pragma unroll
-  for (int u = 0; u < U; ++u) acc[u] = fe_identity(P.reduce_op);
-  for (long long base = gtid; base < P.n; base += T * U) {
-    GlobalLoader<U> ld;
+  for (int u = 0; u < U; ++u) acc[u] = fe_identity<T>(P.reduce_op);
+  for (long long base = gtid; base < P.n; base += nt * U) {
+    GlobalLoader<T, U> ld;
     ld.in = P.in;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      ld.e[u] = base + (long long)u * T;
+      ld.e[u] = base + (long long)u * nt;
       ld.ok[u] = ld.e[u] < P.n;
     }
-    float res[U];
-    fe_eval<U, MAXOPS>(P, ld, res);
+    T res[U];
+    fe_eval<T, U, MAXOPS>(P, ld, res);
+    if (reduce) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (!ld.ok[u]) continue;
-      if (reduce)
-        acc[u] = fe_combine(P.reduce_op, acc[u], res[u]);
-      else
-        P.dst[ld.e[u]] = res[u];
+      for (int u = 0; u < U; ++u)
+        if (!ld.ok[u]) res[u] = fe_identity<T>(P.reduce_op);
+      fe_accumulate<T, U>(P.reduce_op, acc, res);
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (ld.ok[u]) P.dst[ld.e[u]] = res[u];
     }
   }
-  if (reduce) fe_grid_reduce<U, MAXOPS>(P, acc);
+  if (reduce) fe_grid_reduce<T, U, MAXOPS>(P, acc);
 }
 
 // ------------------------------------------------------------------------------------------------ launcher
-template <int MAXOPS>
-static void fill_args(FeKernelArgs<MAXOPS>& a, const FeProgram& prog, const float* const* inputs, long long n,
-                      int reduce_op, float* dst, double* result, void* reduce_scratch, int* status) {
+template <typename T, int MAXOPS>
+static void fill_args(FeKernelArgs<T, MAXOPS>& a, const FeProgram& prog, const void* const* inputs, long long n,
+                      int reduce_op, void* dst, double* result, void* reduce_scratch, int* status) {
   a.n = n;
-  for (int i = 0; i < FE_MAX_INPUTS; ++i) a.in[i] = i < prog.n_inputs ? inputs[prog.input_map[i]] : nullptr;
-  a.dst = dst;
+  for (int i = 0; i < FE_MAX_INPUTS; ++i)
+    a.in[i] = i < prog.n_inputs ? static_cast<const T*>(inputs[prog.input_map[i]]) : nullptr;
+  a.dst = static_cast<T*>(dst);
   a.partials = static_cast<double*>(reduce_scratch);
   a.ticket = reduce_scratch
                  ? reinterpret_cast<unsigned*>(static_cast<char*>(reduce_scratch) + FE_MAX_BLOCKS * sizeof(double))
@@ -535,17 +603,18 @@ static long long clamp_blocks(long long want, long long cap) {
   return want < 1 ? 1 : want;
 }
 
-// Ring geometry for a program with n_inputs arrays: values per thread and step (4 * U), stages, bytes.
+// Ring geometry for a program with n_inputs arrays: 16-byte vectors per thread and step (U), stages, bytes.
+// The same for both element types: a chunk is FE_THREADS x U x 16 bytes per input.
 struct RingGeometry {
-  int u, chunk_elems, stages, smem_bytes;
+  int u, chunk_bytes, stages, smem_bytes;
 };
 static RingGeometry ring_geometry(int n_inputs) {
-  // Values per thread and step: 16 for one or two inputs (the dispatch of an op is paid once per 16 elements,
-  // which matters when few bytes move per element), 8 for three or four, 4 beyond.
+  // Vectors per thread and step: 4 for one or two inputs (the dispatch of an op is paid once per 16 floats,
+  // which matters when few bytes move per element), 2 for three or four, 1 beyond.
   RingGeometry g;
   g.u = n_inputs <= 2 ? 4 : n_inputs <= 4 ? 2 : 1;
-  g.chunk_elems = FE_THREADS * 4 * g.u;
-  const int stage_bytes = n_inputs * g.chunk_elems * 4;
+  g.chunk_bytes = FE_THREADS * 16 * g.u;
+  const int stage_bytes = n_inputs * g.chunk_bytes;
   // Ring budget per CTA: a third of an SM's shared memory (three CTAs per SM), or half of it for the widest
   // variant, whose stages are 16 KB per input.
   g.stages = ((g.u == 4 ? 104 : 72) * 1024) / stage_bytes;
@@ -554,10 +623,11 @@ static RingGeometry ring_geometry(int n_inputs) {
   return g;
 }
 
-void describe_fused_elementwise(int n_inputs, long long n, int num_sms, int* grid, int* block, int* smem_bytes) {
+void describe_fused_elementwise(int n_inputs, long long n, int elem_bytes, int num_sms, int* grid, int* block,
+                                int* smem_bytes) {
   if (n_inputs < 1) {  // plain-load kernel
     const long long want = (n + FE_THREADS * 4 - 1) / (FE_THREADS * 4), cap = (long long)num_sms * 8;
-    *grid = (int)(want < 1 ? 1 : want > cap ? cap : want > FE_MAX_BLOCKS ? FE_MAX_BLOCKS : want);
+    *grid = (int)clamp_blocks(want, cap);
     *block = FE_THREADS;
     *smem_bytes = 0;
     return;
@@ -566,44 +636,40 @@ void describe_fused_elementwise(int n_inputs, long long n, int num_sms, int* gri
   int per_sm = (228 * 1024) / (g.smem_bytes + 1024 + 512);  // + per-CTA reservation and static shared memory
   if (per_sm > 7) per_sm = 7;                               // 2048 threads / 288
   if (per_sm < 1) per_sm = 1;
-  const long long chunks = n / g.chunk_elems, cap = (long long)num_sms * per_sm;
-  long long b = chunks < cap ? chunks : cap;
-  if (b > FE_MAX_BLOCKS) b = FE_MAX_BLOCKS;
-  *grid = (int)(b < 1 ? 1 : b);
+  *grid = (int)clamp_blocks(n / (g.chunk_bytes / elem_bytes), (long long)num_sms * per_sm);
   *block = FE_THREADS + 32;
   *smem_bytes = g.smem_bytes;
 }
 
-template <int U, int MAXOPS>
-static int launch_ring(const FeProgram& prog, const float* const* inputs, long long n, int reduce_op, float* dst,
+template <typename T, int U, int MAXOPS>
+static int launch_ring(const FeProgram& prog, const void* const* inputs, long long n, int reduce_op, void* dst,
                        double* result, void* reduce_scratch, int* status, int num_sms, cudaStream_t stream) {
-  auto kern = fused_elementwise_ring_kernel<U, MAXOPS>;
-  constexpr int CHUNK_BYTES = FE_THREADS * U * 16;
+  auto kern = fused_elementwise_ring_kernel<T, U, MAXOPS>;
   SX_ENSURE_DYN_SMEM(kern, 160 * 1024);  // the largest ring is 2 stages x 16 inputs x 4 KB + barriers
   const RingGeometry geo = ring_geometry(prog.n_inputs);
-  const int stages = geo.stages, smem = geo.smem_bytes;
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FE_THREADS + 32, smem) != cudaSuccess || per_sm < 1)
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FE_THREADS + 32, geo.smem_bytes) != cudaSuccess ||
+      per_sm < 1)
     return set_last_error(SX_ERR_DRIVER, "occupancy query failed for the fused elementwise ring kernel");
-  auto args = std::make_unique<FeKernelArgs<MAXOPS>>();
+  auto args = std::make_unique<FeKernelArgs<T, MAXOPS>>();
   fill_args(*args, prog, inputs, n, reduce_op, dst, result, reduce_scratch, status);
-  args->stages = stages;
-  const long long nchunks = n / (CHUNK_BYTES / 4);
+  args->stages = geo.stages;
+  const long long nchunks = n / (geo.chunk_bytes / (int)sizeof(T));
   const long long blocks = clamp_blocks(nchunks, (long long)num_sms * per_sm);
-  kern<<<(unsigned)blocks, FE_THREADS + 32, smem, stream>>>(*args);
+  kern<<<(unsigned)blocks, FE_THREADS + 32, geo.smem_bytes, stream>>>(*args);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_last_error(SX_ERR_EXEC, cudaGetErrorString(e));
   return SX_OK;
 }
 
-template <int MAXOPS>
-static int launch_plain(const FeProgram& prog, const float* const* inputs, long long n, int reduce_op, float* dst,
+template <typename T, int MAXOPS>
+static int launch_plain(const FeProgram& prog, const void* const* inputs, long long n, int reduce_op, void* dst,
                         double* result, void* reduce_scratch, int* status, int num_sms, cudaStream_t stream) {
-  auto kern = fused_elementwise_plain_kernel<MAXOPS>;
+  auto kern = fused_elementwise_plain_kernel<T, MAXOPS>;
   int per_sm = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FE_THREADS, 0) != cudaSuccess || per_sm < 1)
     return set_last_error(SX_ERR_DRIVER, "occupancy query failed for the fused elementwise kernel");
-  auto args = std::make_unique<FeKernelArgs<MAXOPS>>();
+  auto args = std::make_unique<FeKernelArgs<T, MAXOPS>>();
   fill_args(*args, prog, inputs, n, reduce_op, dst, result, reduce_scratch, status);
   const long long blocks = clamp_blocks((n + FE_THREADS * 4 - 1) / (FE_THREADS * 4), (long long)num_sms * per_sm);
   kern<<<(unsigned)blocks, FE_THREADS, 0, stream>>>(*args);
@@ -612,8 +678,31 @@ static int launch_plain(const FeProgram& prog, const float* const* inputs, long 
   return SX_OK;
 }
 
-int launch_fused_elementwise(const FeProgram& prog, const float* const* inputs, long long n, int reduce_op,
-                             float* dst, double* result, void* reduce_scratch, int* status, int num_sms,
+template <typename T>
+static int launch_typed(const FeProgram& prog, const void* const* inputs, long long n, int reduce_op, void* dst,
+                        double* result, void* reduce_scratch, int* status, int num_sms, cudaStream_t stream) {
+  const bool reduce = reduce_op != FE_REDUCE_NONE;
+  uintptr_t bits = reduce ? 0 : reinterpret_cast<uintptr_t>(dst);
+  for (int i = 0; i < prog.n_inputs; ++i) {
+    const void* p = inputs ? inputs[prog.input_map[i]] : nullptr;
+    if (p == nullptr) return set_last_error(SX_ERR_INVALID, "null input array");
+    bits |= reinterpret_cast<uintptr_t>(p);
+  }
+  if (bits % sizeof(T)) return set_last_error(SX_ERR_INVALID, "arrays must be aligned to the element size");
+  const bool ring = bits % 16 == 0 && prog.n_inputs > 0;
+  const bool small = prog.n_ops <= FE_SMALL_OPS;
+#define FE_ARGS prog, inputs, n, reduce_op, dst, result, reduce_scratch, status, num_sms, stream
+  if (!ring) return small ? launch_plain<T, FE_SMALL_OPS>(FE_ARGS) : launch_plain<T, FE_MAX_OPS>(FE_ARGS);
+  switch (ring_geometry(prog.n_inputs).u) {
+    case 4: return small ? launch_ring<T, 4, FE_SMALL_OPS>(FE_ARGS) : launch_ring<T, 4, FE_MAX_OPS>(FE_ARGS);
+    case 2: return small ? launch_ring<T, 2, FE_SMALL_OPS>(FE_ARGS) : launch_ring<T, 2, FE_MAX_OPS>(FE_ARGS);
+    default: return small ? launch_ring<T, 1, FE_SMALL_OPS>(FE_ARGS) : launch_ring<T, 1, FE_MAX_OPS>(FE_ARGS);
+  }
+#undef FE_ARGS
+}
+
+int launch_fused_elementwise(const FeProgram& prog, const void* const* inputs, long long n, int reduce_op, void* dst,
+                             double* result, void* reduce_scratch, int* status, int num_sms, int elem_bytes,
                              cudaStream_t stream) {
   const bool reduce = reduce_op != FE_REDUCE_NONE;
   if (n <= 0) return set_last_error(SX_ERR_INVALID, "element count must be positive");
@@ -621,23 +710,11 @@ int launch_fused_elementwise(const FeProgram& prog, const float* const* inputs, 
   if (reduce && (result == nullptr || reduce_scratch == nullptr))
     return set_last_error(SX_ERR_INVALID, "null reduction output");
   if (!reduce && dst == nullptr) return set_last_error(SX_ERR_INVALID, "null dst");
-  uintptr_t bits = reduce ? 0 : reinterpret_cast<uintptr_t>(dst);
-  for (int i = 0; i < prog.n_inputs; ++i) {
-    const float* p = inputs ? inputs[prog.input_map[i]] : nullptr;
-    if (p == nullptr) return set_last_error(SX_ERR_INVALID, "null input array");
-    bits |= reinterpret_cast<uintptr_t>(p);
-  }
-  if (bits % 4) return set_last_error(SX_ERR_INVALID, "arrays must be 4-byte aligned");
-  const bool ring = bits % 16 == 0 && prog.n_inputs > 0;
-  const bool small = prog.n_ops <= FE_SMALL_OPS;
-#define FE_ARGS prog, inputs, n, reduce_op, dst, result, reduce_scratch, status, num_sms, stream
-  if (!ring) return small ? launch_plain<FE_SMALL_OPS>(FE_ARGS) : launch_plain<FE_MAX_OPS>(FE_ARGS);
-  switch (ring_geometry(prog.n_inputs).u) {
-    case 4: return small ? launch_ring<4, FE_SMALL_OPS>(FE_ARGS) : launch_ring<4, FE_MAX_OPS>(FE_ARGS);
-    case 2: return small ? launch_ring<2, FE_SMALL_OPS>(FE_ARGS) : launch_ring<2, FE_MAX_OPS>(FE_ARGS);
-    default: return small ? launch_ring<1, FE_SMALL_OPS>(FE_ARGS) : launch_ring<1, FE_MAX_OPS>(FE_ARGS);
-  }
-#undef FE_ARGS
+  if (elem_bytes == 4)
+    return launch_typed<float>(prog, inputs, n, reduce_op, dst, result, reduce_scratch, status, num_sms, stream);
+  if (elem_bytes == 8)
+    return launch_typed<double>(prog, inputs, n, reduce_op, dst, result, reduce_scratch, status, num_sms, stream);
+  return set_last_error(SX_ERR_INVALID, "element size must be 4 or 8");
 }
 
 }  // namespace sx

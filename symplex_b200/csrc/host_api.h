@@ -127,7 +127,8 @@ constexpr uint8_t FE_NO_DST = 0xff;
 constexpr int FE_REDUCE_NONE = 255;
 struct FeOp {
   uint8_t opcode, lkind, rkind, dst;  // dst: slot that receives the result, or FE_NO_DST
-  uint32_t l, r;
+  uint32_t pad_;
+  uint64_t l, r;                      // index, or the immediate's bits (a float's in the low word)
 };
 struct FeProgram {
   int n_ops = 0, n_inputs = 0, n_slots = 0;
@@ -141,18 +142,20 @@ struct FeSrcOp {  // layout of the reference's #[repr(C)] FusedOpDesc
   uint16_t rhs_idx;
 };
 // Resolve constants, compact the inputs that are used, and assign slots by liveness. Pure host code.
-int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, const float* constants,
-                          size_t n_constants, FeProgram* out);
+// `constants` holds n_constants values of elem_bytes (4: float, 8: double) each.
+int compile_fused_program(const FeSrcOp* ops, size_t n_ops, size_t n_inputs, const void* constants,
+                          size_t n_constants, int elem_bytes, FeProgram* out);
 // Launch geometry the kernels use for a program with n_inputs arrays of n elements (host only; the launch
 // path asks the occupancy calculator for the CTAs per SM, this uses the shared-memory arithmetic).
-void describe_fused_elementwise(int n_inputs, long long n, int num_sms, int* grid, int* block, int* smem_bytes);
+void describe_fused_elementwise(int n_inputs, long long n, int elem_bytes, int num_sms, int* grid, int* block,
+                                int* smem_bytes);
 // Device scratch of one reduction: FE_MAX_BLOCKS doubles followed by a ticket word (zero between launches).
 constexpr size_t FE_REDUCE_SCRATCH_BYTES = FE_MAX_BLOCKS * sizeof(double) + 256;
-// Evaluate the program over n elements. inputs[] follow the caller's numbering. reduce_op 255: store to dst;
+// Evaluate the program over n elements of elem_bytes (4 or 8) each. inputs[] follow the caller's numbering. reduce_op 255: store to dst;
 // 0 / 1 / 2: sum / max / min of the final value into *result (a device double), nothing stored to dst.
 // status: device word that receives ST_WAIT_TIMEOUT if a bounded wait inside the kernel runs out.
-int launch_fused_elementwise(const FeProgram& prog, const float* const* inputs, long long n, int reduce_op,
-                             float* dst, double* result, void* reduce_scratch, int* status, int num_sms,
+int launch_fused_elementwise(const FeProgram& prog, const void* const* inputs, long long n, int reduce_op, void* dst,
+                             double* result, void* reduce_scratch, int* status, int num_sms, int elem_bytes,
                              cudaStream_t stream);
 
 }  // namespace sx

@@ -131,7 +131,7 @@ def cuda_compile_kernel(pattern_type: str, shape_info: dict, sm_arch: str = "sm_
         n_in = {"elementwise": 2, "fma": 3, "reduction": 1}[pattern_type]
         streams = n_in + (0 if pattern_type == "reduction" else 1)
         grid, block, smem = (ctypes.c_int32 * 3)(), (ctypes.c_int32 * 3)(), ctypes.c_int32(0)
-        _capi.check(_capi.load().symplex_b200_fused_elementwise_plan(n_in, n, 0, ctypes.byref(grid), ctypes.byref(block),
+        _capi.check(_capi.load().symplex_b200_fused_elementwise_plan(n_in, n, 4, 0, ctypes.byref(grid), ctypes.byref(block),
                                                                      ctypes.byref(smem)))
         t = planner.hardware_target()
         seconds = 4.0 * streams * n / (t["global_bw_gbps"] * 1e9) + 4e-6

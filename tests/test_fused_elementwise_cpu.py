@@ -156,3 +156,28 @@ def test_empty_requests_return_zero_without_a_gpu(lib):
     from symplex_b200 import _symplex_core
     assert _symplex_core.simd_fused_elementwise_f32([], [], [], 10, SUM, 0) == 0.0
     assert _symplex_core.simd_fused_elementwise_f32([(ADD, IN, 0, IN, 0)], [0], [], 0, SUM, 0) == 0.0
+
+
+# ----------------------------------------------------------------------------- the f64 twin
+
+def test_f64_chain_matches_numpy_bitwise(oracle):
+    x = np.random.default_rng(9).uniform(-2, 2, 1003)
+    y = np.random.default_rng(10).uniform(0.5, 2, 1003)
+    got = oracle.fused_elementwise([(MUL, IN, 0, CONST, 0), (ADD, PREV, 0, CONST, 1), (DIV, PREV, 1, IN, 1)], [x, y],
+                                   [2.0, 1.0], dtype=np.float64)
+    assert got.dtype == np.float64 and np.array_equal(got, (x * 2.0 + 1.0) / y)
+    got = oracle.fused_elementwise([(SQRT, IN, 0, IN, 0), (NEG, PREV, 0, IN, 0)], [y], [], dtype=np.float64)
+    assert np.array_equal(got, -np.sqrt(y))
+
+
+def test_f64_reduction_lane_structure(oracle):
+    for n in [1, 3, 4, 15, 16, 17, 100, 1003]:
+        x = np.arange(1, n + 1, dtype=np.float64)
+        assert oracle.fused_elementwise([(MUL, IN, 0, CONST, 0)], [x], [2.0], reduce_op=SUM, dtype=np.float64) == n * (n + 1)
+    y = np.random.default_rng(11).uniform(-2, 2, 64)
+    assert oracle.fused_elementwise([(ADD, IN, 0, CONST, 0)], [y], [0.0], reduce_op=RMAX, dtype=np.float64) == y.max()
+    z = np.random.default_rng(12).uniform(-2, 2, 67)  # tail of 3: the reference adds the two partial maxima
+    assert oracle.fused_elementwise([(ADD, IN, 0, CONST, 0)], [z], [0.0], reduce_op=RMAX, dtype=np.float64) == \
+        z[:64].max() + z[64:].max()
+    assert oracle.fused_elementwise([(ADD, IN, 0, CONST, 0)], [z], [0.0], reduce_op=RMIN, exact=True,
+                                    dtype=np.float64) == z.min()

@@ -171,3 +171,62 @@ def test_host_entry_points(torch_cuda, oracle):
                      ("min", np.minimum), ("max", np.maximum)]:
         assert engine.cuda_elementwise_raw(a.ctypes.data, b.ctypes.data, out.ctypes.data, n, name) == 0
         assert np.array_equal(out, fn(a, b)), name
+
+
+# ----------------------------------------------------------------------------- the f64 twin
+
+def _run64(torch, ops, arrays, consts, reduce_op=NONE, misalign=False):
+    import symplex_b200 as sx
+    dev = []
+    for a in arrays:
+        if misalign:  # 8 bytes past a 16-byte boundary
+            buf = torch.empty(a.size + 1, device="cuda", dtype=torch.float64)
+            t = buf[1:]
+            t.copy_(torch.from_numpy(a))
+        else:
+            t = torch.from_numpy(a).cuda()
+        dev.append(t)
+    out = sx.fused_elementwise(ops, dev, consts, reduce_op=reduce_op)
+    sx.sync_status()
+    return out.cpu().numpy() if reduce_op == NONE else float(out.item())
+
+
+@pytest.mark.parametrize("name", ["axpb", "bias_relu", "div_sqrt_abs", "slots", "six_inputs"])
+@pytest.mark.parametrize("n", [1, 1023, 1024, 1025, 2048, 5 * 2048 + 7, (1 << 19) + 3])
+def test_f64_exact_programs_bitwise(torch_cuda, oracle, name, n):
+    ops, n_in, consts = EXACT_PROGRAMS[name]
+    arrays = [np.random.default_rng(70 + i).uniform(-2, 2, n) for i in range(n_in)]
+    want = oracle.fused_elementwise(ops, arrays, consts, dtype=np.float64)
+    for misalign in (False, True):
+        got = _run64(torch_cuda, ops, arrays, consts, misalign=misalign)
+        assert got.dtype == np.float64 and np.array_equal(got.view(np.uint64), want.view(np.uint64)), (name, misalign)
+
+
+def test_f64_libm_ops_and_reductions(torch_cuda, oracle):
+    n = 3 * 2048 + 5
+    x = np.random.default_rng(80).uniform(0.05, 6.0, n)
+    for op in (EXP, LOG, SIN, COS, TANH, SIGMOID):
+        want = oracle.fused_elementwise([(op, IN, 0, IN, 0)], [x], [], dtype=np.float64)
+        got = _run64(torch_cuda, [(op, IN, 0, IN, 0)], [x], [])
+        np.testing.assert_allclose(got, want, rtol=1e-14, atol=1e-15, err_msg=f"op {op}")
+    y = np.random.default_rng(81).uniform(-2, 2, n)
+    ops = [(MUL, IN, 0, IN, 1), (ADD, PREV, 0, CONST, 0)]
+    vals = x * y + 0.25
+    got = _run64(torch_cuda, ops, [x, y], [0.25], reduce_op=SUM)
+    assert abs(got - np.sum(vals)) <= 1e-13 * np.abs(vals).sum()
+    assert abs(got - oracle.fused_elementwise(ops, [x, y], [0.25], reduce_op=SUM, dtype=np.float64)) <= 1e-12 * np.abs(vals).sum()
+    assert _run64(torch_cuda, ops, [x, y], [0.25], reduce_op=RMAX) == vals.max()
+    assert _run64(torch_cuda, ops, [x, y], [0.25], reduce_op=RMIN, misalign=True) == vals.min()
+
+
+def test_f64_host_entry_point(torch_cuda, oracle):
+    from symplex_b200 import _symplex_core
+    n = (5 << 20) + 3  # two pipeline chunks (4 Mi doubles each) plus a ragged end
+    a = np.random.default_rng(90).uniform(-2, 2, n)
+    b = np.random.default_rng(91).uniform(0.5, 2, n)
+    ops = [(DIV, IN, 0, IN, 1), (SUB, PREV, 0, CONST, 0)]
+    dst = np.empty(n, np.float64)
+    assert _symplex_core.simd_fused_elementwise_f64(ops, [a.ctypes.data, b.ctypes.data], [0.5], n, NONE, dst.ctypes.data) == 0.0
+    assert np.array_equal(dst, a / b - 0.5)
+    s = _symplex_core.simd_fused_elementwise_f64(ops, [a.ctypes.data, b.ctypes.data], [0.5], n, SUM, 0)
+    assert abs(s - np.sum(dst)) <= 1e-13 * np.abs(dst).sum()
