@@ -44,7 +44,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
         if not force and os.path.exists(obj) and os.path.getmtime(obj) > max(dep_time, os.path.getmtime(src)):
             return obj
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", src, "-o", obj]
+        cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("SYMPLEX_B200_NVCC_EXTRA", "").split(), "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
             print(" ".join(cmd), flush=True)

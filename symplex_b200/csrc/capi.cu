@@ -945,7 +945,10 @@ int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm
   KernelShape ks;
   double eff;  // fraction of the tensor peak the variant sustains on large problems (measured)
   switch (kc.kind) {
-    case KK_F32_FUSED: ks = describe_gemm_f32_fused(); eff = 0.45; break;
+    case KK_F32_FUSED:
+      ks = describe_gemm_f32_fused(f32_fused_split_k((long long)((p.M + 127) / 128) * ((p.N + 63) / 64) * p.batch, p.K, num_sms));
+      eff = 0.45;
+      break;
     case KK_F32_SPLIT: ks = describe_gemm_tf32x3(kc.bn); eff = 0.71; break;
     case KK_BF16_PAIR512: ks = describe_gemm_pair(2); eff = 0.90; break;
     case KK_BF16_PAIR256: ks = describe_gemm_pair(1); eff = 0.82; break;
@@ -960,7 +963,7 @@ int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm
   out->tmem_columns = ks.tmem_cols;
   const long long mt = (p.M + ks.tile_m - 1) / ks.tile_m, nt = (p.N + ks.tile_n - 1) / ks.tile_n;
   out->tiles = mt * nt * p.batch;
-  const long long units = ks.cluster == 2 ? num_sms / 2 : num_sms;  // persistent: one CTA (or pair) per SM (pair)
+  const long long units = num_sms / ks.cluster;  // persistent: one CTA (or one cluster) per SM (group of SMs)
   const long long active = out->tiles < units ? out->tiles : units;
   out->grid_dims[0] = (int32_t)(active * ks.cluster); out->grid_dims[1] = 1; out->grid_dims[2] = 1;
   out->block_dims[0] = ks.threads; out->block_dims[1] = 1; out->block_dims[2] = 1;

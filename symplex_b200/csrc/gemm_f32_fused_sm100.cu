@@ -15,8 +15,20 @@
 // correction accumulator added once per tile, fused epilogue) is the scheme of gemm_tf32x3_kernel.
 //
 //   warp 0      TMA producer (raw tiles)            warp 1      MMA issuer
-//   warps 2..5  accumulate + epilogue               warps 6..9  converters
+//   warps 2..5  accumulate + epilogue               warps 6..13 converters
+//
+// Split-K over a thread-block cluster (kSplit = 2 or 4): when a problem has fewer tiles than a quarter (half)
+// of the SMs but a long K, the per-k-block latency of this pipeline (TMA + conversion + MMA completion), not
+// throughput, sets the run time. The kSplit CTAs of a cluster then work on the SAME output tile, each on its own
+// contiguous range of k-blocks. Ranks 1.. park their fp32 partial tile in their own shared memory and signal the
+// leader's mbarrier; the leader (rank 0) reads the partials over distributed shared memory (ld.shared::cluster),
+// adds them in rank order - a fixed order, so results are reproducible - and runs the epilogue. All cross-CTA
+// hand-offs are mbarriers with the same bounded waits as the pipeline; the only barrier.cluster is at kernel
+// start (barrier initialisation visible cluster-wide) and at the end (nobody's shared memory goes away while a
+// peer may still touch it), which every control path reaches.
 #include <cuda_bf16.h>
+
+#include <cstdlib>
 
 #include "epilogue.cuh"
 #include "gemm_params.h"
@@ -25,7 +37,8 @@
 
 namespace sx {
 
-struct FusedCfg {
+template <int kSplit>
+struct FusedCfgT {
   static constexpr int BM = 128, BN = 64, BK = 32, UMMA_K = 8, CHUNK_KB = 4;
   static constexpr int A_OFF = 0;             // raw A, becomes A hi          16 KB
   static constexpr int ALO_OFF = 16 * 1024;   // A lo                          16 KB
@@ -34,11 +47,31 @@ struct FusedCfg {
   static constexpr int BLO_OFF = 48 * 1024;   // B lo                           8 KB
   static constexpr int STAGE_BYTES = 56 * 1024;
   static constexpr int RAW_BYTES = 16 * 1024 + 8 * 1024;  // bytes the TMA delivers per stage
-  static constexpr int STAGES = 4;
+  static constexpr int STAGES = kSplit > 1 ? 3 : 4;         // split-K trades one stage for the partial-tile buffer
+  static constexpr int PART_BYTES = kSplit > 1 ? BM * BN * 4 : 0;  // this CTA's fp32 partial tile (ranks 1..)
   static constexpr int TMEM_COLS = 4 * BN;  // main[2] + corr[2]
-  static constexpr int THREADS = 320;
-  static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;
+  static constexpr int CONV_WARPS = 8;                      // converter warps (two per scheduler: latency hiding)
+  static constexpr int THREADS = 192 + 32 * CONV_WARPS;
+  static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + PART_BYTES + 1024;
 };
+using FusedCfg = FusedCfgT<1>;
+
+__device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr));  // volatile keeps it after the (volatile) barrier wait that precedes it
+  return v;
+}
+#ifdef SX_FUSED_TRACE
+__device__ unsigned long long g_fused_trace[32];
+#define SX_TRACE(i) do { if (blockIdx.x == 0) g_fused_trace[i] = globaltimer_ns(); else if (blockIdx.x == 1 && (i) < 16) g_fused_trace[16 + (i)] = globaltimer_ns(); } while (0)
+#else
+#define SX_TRACE(i) do { } while (0)
+#endif
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 
 // Round to tf32 (10 mantissa bits), nearest with ties away from zero - the result of cvt.rna.tf32.f32, written
 // with two full-rate integer instructions (add half an ulp to the magnitude, clear the 13 dropped bits) because
@@ -52,27 +85,31 @@ __device__ __forceinline__ void split4(const float4& x, float4& hi, float4& lo) 
   lo.x = tf32_rna(x.x - hi.x); lo.y = tf32_rna(x.y - hi.y); lo.z = tf32_rna(x.z - hi.z); lo.w = tf32_rna(x.w - hi.w);
 }
 
-template <typename OutT, bool kBmn>
+template <typename OutT, bool kBmn, int kSplit>
 __global__ void __launch_bounds__(FusedCfg::THREADS, 1)
 gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const GemmParams p) {
-  using Cfg = FusedCfg;
+  using Cfg = FusedCfgT<kSplit>;
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES, CH = Cfg::CHUNK_KB;
 
   extern __shared__ uint8_t dyn_smem[];
   __shared__ uint64_t raw_full[STAGES], conv_done[STAGES], empty_bar[STAGES];
   __shared__ uint64_t main_full[2], main_empty[2], corr_full[2], corr_empty[2];
+  // Split-K hand-off, one barrier per epilogue warp (32 rows of the tile): part_full[r - 1][q] lives in the
+  // leader and is signalled by rank r; part_empty[q] lives in every rank >= 1 and is signalled by the leader.
+  __shared__ uint64_t part_full[3][4], part_empty[4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) SX_TRACE(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&conv_done[s], 4);  // one arrival per converter warp
+      mbar_init(&conv_done[s], Cfg::CONV_WARPS);  // one arrival per converter warp
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -80,6 +117,10 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       mbar_init(&main_empty[a], 4);
       mbar_init(&corr_full[a], 1);
       mbar_init(&corr_empty[a], 4);
+    }
+    for (int q = 0; q < 4; ++q) {
+      mbar_init(&part_empty[q], 1);
+      for (int r = 0; r < 3; ++r) mbar_init(&part_full[r][q], 1);
     }
     abort_flag = 0;
     fence_mbar_init();
@@ -90,12 +131,21 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kSplit > 1) cluster_sync_all();  // every CTA's barriers are initialised before a peer arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  if (threadIdx.x == 0) SX_TRACE(1);
 
   const int per = p.m_tiles * p.n_tiles;
   const int total_tiles = p.batch * per;
-  const int nkb = (p.K + BK - 1) / BK;
+  // This CTA's share of the k-blocks: the first (nkb_all mod kSplit) ranks take one more. The host only
+  // splits when every rank gets at least one.
+  const int rank = kSplit > 1 ? (int)cluster_ctarank() : 0;
+  const int first_tile = blockIdx.x / kSplit, tile_step = gridDim.x / kSplit;
+  const int nkb_all = (p.K + BK - 1) / BK;
+  const int kb_base = nkb_all / kSplit, kb_rem = nkb_all % kSplit;
+  const int kb0 = rank * kb_base + (rank < kb_rem ? rank : kb_rem);
+  const int nkb = kb_base + (rank < kb_rem ? 1 : 0);
   const int nchunks = (nkb + CH - 1) / CH;
 
   if (warp == 0) {
@@ -106,16 +156,18 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      for (int t = first_tile; ok && t < total_tiles; t += tile_step) {
         const int z = t / per, r = t - z * per;
         const int m0 = (r % p.m_tiles) * BM, n0 = (r / p.m_tiles) * BN;
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) { ok = false; break; }
           uint8_t* base = tiles + stage * Cfg::STAGE_BYTES;
           mbar_arrive_expect_tx(&raw_full[stage], Cfg::RAW_BYTES);
-          tma_load_3d(base + Cfg::A_OFF, &tmA, &raw_full[stage], kb * BK, m0, z);
-          if constexpr (kBmn) tma_load_3d(base + Cfg::BRAW_OFF, &tmB, &raw_full[stage], n0, kb * BK, z);
-          else tma_load_3d(base + Cfg::BRAW_OFF, &tmB, &raw_full[stage], kb * BK, n0, z);
+          const int k0 = (kb0 + kb) * BK;
+          if (kb == 0) SX_TRACE(2);
+          tma_load_3d(base + Cfg::A_OFF, &tmA, &raw_full[stage], k0, m0, z);
+          if constexpr (kBmn) tma_load_3d(base + Cfg::BRAW_OFF, &tmB, &raw_full[stage], n0, k0, z);
+          else tma_load_3d(base + Cfg::BRAW_OFF, &tmB, &raw_full[stage], k0, n0, z);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -130,7 +182,7 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int macc = 0, cacc = 0;
       uint32_t mphase = 0, cphase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      for (int t = first_tile; ok && t < total_tiles; t += tile_step) {
         if (!mbar_wait(&corr_empty[cacc], cphase ^ 1, &abort_flag)) break;
         const uint32_t d_corr = tmem_base + 2 * BN + cacc * BN;
         int kb = 0;
@@ -160,6 +212,7 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (++macc == 2) { macc = 0; mphase ^= 1; }
         }
         if (!ok) break;
+        SX_TRACE(6);
         umma_commit(&corr_full[cacc]);
         if (++cacc == 2) { cacc = 0; cphase ^= 1; }
       }
@@ -170,13 +223,15 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+    for (int t = first_tile; ok && t < total_tiles; t += tile_step) {
       for (int kb = 0; kb < nkb; ++kb) {
         if (!mbar_wait(&raw_full[stage], phase, &abort_flag)) { ok = false; break; }
+        if (tid == 0 && kb == 0) SX_TRACE(3);
         uint8_t* base = tiles + stage * Cfg::STAGE_BYTES;
+        constexpr int CT = 32 * Cfg::CONV_WARPS;  // converter threads
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {  // A: 1024 16-byte chunks, position-wise
-          const int off = (i * 128 + tid) * 16;
+        for (int i = 0; i < 1024 / CT; ++i) {  // A: 1024 16-byte chunks, position-wise
+          const int off = (i * CT + tid) * 16;
           float4 hi, lo;
           split4(*reinterpret_cast<const float4*>(base + Cfg::A_OFF + off), hi, lo);
           *reinterpret_cast<float4*>(base + Cfg::A_OFF + off) = hi;
@@ -184,8 +239,8 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         }
         if constexpr (!kBmn) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {  // B [64 n][32 k], position-wise
-            const int off = (i * 128 + tid) * 16;
+          for (int i = 0; i < 512 / CT; ++i) {  // B [64 n][32 k], position-wise
+            const int off = (i * CT + tid) * 16;
             float4 hi, lo;
             split4(*reinterpret_cast<const float4*>(base + Cfg::BRAW_OFF + off), hi, lo);
             *reinterpret_cast<float4*>(base + Cfg::BRAW_OFF + off) = hi;
@@ -194,8 +249,8 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         } else {
           const float* raw = reinterpret_cast<const float*>(base + Cfg::BRAW_OFF);  // [32 k][64 n]
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {  // transpose: 4 consecutive k of one column n -> one 16-byte chunk
-            const int item = i * 128 + tid;
+          for (int i = 0; i < 512 / CT; ++i) {  // transpose: 4 consecutive k of one column n -> one 16-byte chunk
+            const int item = i * CT + tid;
             const int n = item & 63, kc = item >> 6;
             float4 x;
             x.x = raw[(kc * 4 + 0) * 64 + n];
@@ -212,6 +267,8 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         fence_proxy_async_smem();  // the tensor core reads these tiles through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(&conv_done[stage]);
+        if (tid == 0 && kb == 0) SX_TRACE(4);
+        if (tid == 0 && kb == nkb - 1) SX_TRACE(5);
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
@@ -221,9 +278,9 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const EpilogueCtx<OutT> ep(p);
     const uint32_t lane_base = uint32_t(q * 32) << 16;
     int macc = 0, cacc = 0;
-    uint32_t mphase = 0, cphase = 0;
+    uint32_t mphase = 0, cphase = 0, xphase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+    for (int t = first_tile; ok && t < total_tiles; t += tile_step) {
       const int z = t / per, r = t - z * per;
       const int m0 = (r % p.m_tiles) * BM, n0 = (r / p.m_tiles) * BN;
       float sum[BN];
@@ -231,6 +288,7 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
       for (int ch = 0; ch < nchunks; ++ch) {
         if (!mbar_wait(&main_full[macc], mphase, &abort_flag)) { ok = false; break; }
+        if (q == 0 && lane == 0 && ch == 0) SX_TRACE(7);
         tc_fence_after_sync();
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
@@ -247,6 +305,7 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
       if (!ok) break;
       if (!mbar_wait(&corr_full[cacc], cphase, &abort_flag)) break;
+      if (q == 0 && lane == 0) SX_TRACE(8);
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
@@ -261,6 +320,63 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (lane == 0) mbar_arrive(&corr_empty[cacc]);
       if (++cacc == 2) { cacc = 0; cphase ^= 1; }
 
+      if constexpr (kSplit > 1) {
+        // Partial tiles are laid out [16 column groups][128 rows][4 floats]: consecutive lanes (rows) touch
+        // consecutive 16-byte chunks, for the writer and for the leader's remote reads alike.
+        float* part = reinterpret_cast<float*>(tiles + STAGES * Cfg::STAGE_BYTES);
+        const int prow = q * 32 + lane;
+        if (rank != 0) {
+          if (!mbar_wait<true>(&part_empty[q], xphase ^ 1, &abort_flag)) break;  // leader has read the previous one
+#pragma unroll
+          for (int g = 0; g < BN / 4; ++g)
+            *reinterpret_cast<float4*>(part + (g * BM + prow) * 4) =
+                make_float4(sum[g * 4 + 0], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3]);
+          __syncwarp();  // orders the other lanes' stores before lane 0's release
+          if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&part_full[rank - 1][q]), 0));
+          if (q == 0 && lane == 0) SX_TRACE(9);
+          xphase ^= 1;
+          continue;  // only the leader stores
+        }
+        bool got = true;
+        for (int r = 1; r < kSplit; ++r)
+          if (!mbar_wait<true>(&part_full[r - 1][q], xphase, &abort_flag)) { got = false; break; }
+        if (q == 0 && lane == 0) SX_TRACE(13);
+        if (got) {
+          // Remote (distributed shared memory) loads take on the order of 100 ns each: a round issues the loads
+          // of all peers for a group of columns before the first add, so 12 (8 for two CTAs) are in flight per
+          // thread. The adds run in rank order per element, whatever the arrival order: reproducible bits.
+          constexpr int G = kSplit == 2 ? 8 : 4;  // 16-byte column groups per peer and round
+          uint32_t remote[kSplit - 1];
+#pragma unroll
+          for (int r = 1; r < kSplit; ++r) remote[r - 1] = mapa_u32(smem_u32(part), (uint32_t)r);
+#pragma unroll
+          for (int h = 0; h < BN / 4 / G; ++h) {
+            float4 v[kSplit - 1][G];
+#pragma unroll
+            for (int r = 0; r < kSplit - 1; ++r)
+#pragma unroll
+              for (int g = 0; g < G; ++g)
+                v[r][g] = ld_shared_cluster_v4(remote[r] + (uint32_t)(((h * G + g) * BM + prow) * 16));
+#pragma unroll
+            for (int r = 0; r < kSplit - 1; ++r)
+#pragma unroll
+              for (int g = 0; g < G; ++g) {
+                const int j = (h * G + g) * 4;
+                sum[j + 0] += v[r][g].x; sum[j + 1] += v[r][g].y; sum[j + 2] += v[r][g].z; sum[j + 3] += v[r][g].w;
+              }
+          }
+          // The loaded values have been consumed, so the peers may overwrite their buffers: no release needed.
+          __syncwarp();
+          if (lane == 0) {
+#pragma unroll
+            for (int r = 1; r < kSplit; ++r) mbar_arrive_cluster_relaxed(mapa_u32(smem_u32(&part_empty[q]), (uint32_t)r));
+          }
+        }
+        if (!got) break;
+        xphase ^= 1;
+      }
+
+      if (q == 0 && lane == 0) SX_TRACE(9);
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
       const long long row_off = (long long)z * p.c_batch_stride + (long long)row * p.ldc;
@@ -273,14 +389,18 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         for (int j = 0; j < 32; ++j) v[j] = sum[c * 32 + j];
         ep.template strip<false>(v, row_ok, row_off, col0);
       }
+      if (q == 0 && lane == 0) SX_TRACE(10);
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
+  if (threadIdx.x == 0) SX_TRACE(11);
+  if constexpr (kSplit > 1) cluster_sync_all();  // peers are done with this CTA's shared memory and barriers
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<1>(tmem_base, Cfg::TMEM_COLS);
+    if (lane == 0) SX_TRACE(12);
   }
   if (threadIdx.x == 0 && abort_flag != 0 && p.status != nullptr) atomicExch(p.status, int(ST_WAIT_TIMEOUT));
 }
@@ -288,12 +408,34 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 // ------------------------------------------------------------------ host side
 namespace {
 
-template <typename OutT, bool kBmn>
+template <typename OutT, bool kBmn, int kSplit>
 int launch_fused(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t stream) {
-  auto kern = gemm_f32_fused_kernel<OutT, kBmn>;
-  SX_ENSURE_DYN_SMEM(kern, FusedCfg::DYN_SMEM);
-  kern<<<grid, FusedCfg::THREADS, FusedCfg::DYN_SMEM, stream>>>(tmA, tmB, p);
-  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+  using Cfg = FusedCfgT<kSplit>;
+  auto kern = gemm_f32_fused_kernel<OutT, kBmn, kSplit>;
+  SX_ENSURE_DYN_SMEM(kern, Cfg::DYN_SMEM);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::DYN_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kSplit;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = kSplit > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+}
+
+template <typename OutT, bool kBmn>
+int launch_split(int split, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
+                 cudaStream_t stream) {
+  switch (split) {
+    case 4: return launch_fused<OutT, kBmn, 4>(tmA, tmB, p, grid, stream);
+    case 2: return launch_fused<OutT, kBmn, 2>(tmA, tmB, p, grid, stream);
+    default: return launch_fused<OutT, kBmn, 1>(tmA, tmB, p, grid, stream);
+  }
 }
 
 }  // namespace
@@ -339,18 +481,42 @@ int launch_gemm_f32_fused(const TcGemmArgs& a, cudaStream_t stream) {
   p.m_tiles = (int)((a.M + 127) / 128);
   p.n_tiles = (int)((a.N + 63) / 64);
   const long long total = (long long)p.batch * p.m_tiles * p.n_tiles;
-  const int grid = (int)(total < a.num_sms ? total : a.num_sms);
+  const int split = f32_fused_split_k(total, a.K, a.num_sms);
+  const long long clusters = total < a.num_sms / split ? total : a.num_sms / split;
+  const int grid = (int)clusters * split;
   if (a.out_bf16)
-    return a.b_mn ? launch_fused<__nv_bfloat16, true>(tmA, tmB, p, grid, stream)
-                  : launch_fused<__nv_bfloat16, false>(tmA, tmB, p, grid, stream);
-  return a.b_mn ? launch_fused<float, true>(tmA, tmB, p, grid, stream)
-                : launch_fused<float, false>(tmA, tmB, p, grid, stream);
+    return a.b_mn ? launch_split<__nv_bfloat16, true>(split, tmA, tmB, p, grid, stream)
+                  : launch_split<__nv_bfloat16, false>(split, tmA, tmB, p, grid, stream);
+  return a.b_mn ? launch_split<float, true>(split, tmA, tmB, p, grid, stream)
+                : launch_split<float, false>(split, tmA, tmB, p, grid, stream);
+}
+
+#ifdef SX_FUSED_TRACE
+extern "C" __attribute__((visibility("default"))) int symplex_b200_debug_fused_trace(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_fused_trace, sizeof(unsigned long long) * 32);
+}
+#endif
+
+// How many CTAs share one output tile (split-K over a cluster): only when the tiles alone would leave most SMs
+// idle and every rank still gets at least two k-blocks of 32.
+int f32_fused_split_k(long long tiles, long long K, int num_sms) {
+  if (const char* e = getenv("SYMPLEX_B200_F32_SPLITK")) {
+    const int v = atoi(e);
+    if (v == 1 || v == 2 || v == 4) return (K + 31) / 32 >= v ? v : 1;  // forced (tests): any tile count
+  }
+  const long long nkb = (K + 31) / 32;
+  if (tiles * 4 <= num_sms && nkb >= 8) return 4;
+  if (tiles * 2 <= num_sms && nkb >= 4) return 2;
+  return 1;
 }
 
 
-KernelShape describe_gemm_f32_fused() {
-  using C = FusedCfg;
-  return KernelShape{"gemm_f32_fused_kernel", C::BM, C::BN, C::BK, C::BM, C::BN, C::UMMA_K, C::THREADS, 1, C::STAGES, C::DYN_SMEM, C::TMEM_COLS};
+KernelShape describe_gemm_f32_fused(int split) {
+  auto mk = [](auto cfg, int cluster) {
+    using C = decltype(cfg);
+    return KernelShape{"gemm_f32_fused_kernel", C::BM, C::BN, C::BK, C::BM, C::BN, C::UMMA_K, C::THREADS, cluster, C::STAGES, C::DYN_SMEM, C::TMEM_COLS};
+  };
+  return split == 4 ? mk(FusedCfgT<4>{}, 4) : split == 2 ? mk(FusedCfgT<2>{}, 2) : mk(FusedCfgT<1>{}, 1);
 }
 
 }  // namespace sx
