@@ -508,6 +508,25 @@ def main():
     launches = lib.symplex_b200_launch_count() - launches0
     sx.sync_status()
 
+    # Steps of a few tens of microseconds: the Python caller cannot issue launches that fast, so the loop above
+    # times the host. The same K steps are then captured into one CUDA graph and the replay is timed - the
+    # library's launches are capturable (no allocation or synchronisation on a warm call).
+    if not sharded and world == 1 and elapsed_ms / args.steps < 0.1:
+        config["eager_ms_per_step"] = elapsed_ms / args.steps
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(args.steps):
+                step()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        elapsed_ms = e0.elapsed_time(e1)
+        config["launch"] = f"one CUDA graph of {args.steps} steps (eager launches are host-bound at this size)"
+        sx.sync_status()
+
     # per-launch duration of the GEMM kernel alone (no collective), CUDA events on the launching stream
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if sharded:
@@ -518,7 +537,7 @@ def main():
             sx.gemm(Ak, Bm, bias=bias, activation=w["act"], out=Ck, b_layout=b_layout)
     else:
         kernel_only = step
-    if sharded and op.world == 1:
+    if (sharded and op.world == 1) or "launch" in config:
         kernel_ms = elapsed_ms / args.steps  # one step is exactly one launch of the GEMM kernel
     else:
         kernel_only()

@@ -50,7 +50,8 @@ struct FusedCfgT {
   static constexpr int STAGES = kSplit > 1 ? 3 : 4;         // split-K trades one stage for the partial-tile buffer
   static constexpr int PART_BYTES = kSplit > 1 ? BM * BN * 4 : 0;  // this CTA's fp32 partial tile (ranks 1..)
   static constexpr int TMEM_COLS = 4 * BN;  // main[2] + corr[2]
-  static constexpr int CONV_WARPS = 8;                      // converter warps (two per scheduler: latency hiding)
+  static constexpr int CONV_WARPS = 8;                      // converter warps ...
+  static constexpr int CONV_GROUPS = 2;                     // ... in groups that take alternate k-blocks
   static constexpr int THREADS = 192 + 32 * CONV_WARPS;
   static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + PART_BYTES + 1024;
 };
@@ -109,7 +110,7 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&conv_done[s], Cfg::CONV_WARPS);  // one arrival per converter warp
+      mbar_init(&conv_done[s], Cfg::CONV_WARPS / Cfg::CONV_GROUPS);  // one arrival per converter warp of a group
       mbar_init(&empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -218,17 +219,24 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
     }
   } else if (warp >= 6) {
-    // ------------------------------------------------------------ converters (128 threads)
-    const int tid = threadIdx.x - 192;
-    int stage = 0;
-    uint32_t phase = 0;
+    // ------------------------------------------------------------ converters: two groups of four warps
+    // A stage's conversion is a latency chain (wait, shared loads, split, shared stores, proxy fence, arrive), not
+    // a throughput problem: eight warps on one stage were hardly faster than four. So the groups alternate
+    // k-blocks - group g converts the k-blocks whose running index is congruent to g modulo 2 - and two stages
+    // are in conversion at any time.
+    constexpr int CT = 32 * Cfg::CONV_WARPS / Cfg::CONV_GROUPS;  // threads that share one stage
+    const int group = (warp - 6) / (Cfg::CONV_WARPS / Cfg::CONV_GROUPS);
+    const int tid = (threadIdx.x - 192) % CT;
+    int it = 0;  // k-blocks this CTA has gone through, over all its tiles
     bool ok = true;
     for (int t = first_tile; ok && t < total_tiles; t += tile_step) {
-      for (int kb = 0; kb < nkb; ++kb) {
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        if (it % Cfg::CONV_GROUPS != group) continue;
+        const int stage = it % STAGES;
+        const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
         if (!mbar_wait(&raw_full[stage], phase, &abort_flag)) { ok = false; break; }
         if (tid == 0 && kb == 0) SX_TRACE(3);
         uint8_t* base = tiles + stage * Cfg::STAGE_BYTES;
-        constexpr int CT = 32 * Cfg::CONV_WARPS;  // converter threads
 #pragma unroll
         for (int i = 0; i < 1024 / CT; ++i) {  // A: 1024 16-byte chunks, position-wise
           const int off = (i * CT + tid) * 16;
@@ -269,7 +277,6 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (lane == 0) mbar_arrive(&conv_done[stage]);
         if (tid == 0 && kb == 0) SX_TRACE(4);
         if (tid == 0 && kb == nkb - 1) SX_TRACE(5);
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else {
