@@ -55,7 +55,7 @@ def test_hardware_target(lib):
 
 CONFIGS = [
     # name, args, kwargs, kernel, tile, cluster
-    ("cfg1", (512, 512, 512), dict(dtype="fp32"), "gemm_f32_fused_kernel", (128, 64, 32), 1),
+    ("cfg1", (512, 512, 512), dict(dtype="fp32"), "gemm_f32_fused_kernel", (128, 64, 32), 4),  # split-K over a cluster
     ("cfg2_bf16", (4096, 4096, 4096), dict(dtype="bf16", out_dtype="fp32", b_layout=_capi.COL_MAJOR),
      "gemm_pair_kernel", (256, 256, 64), 2),
     ("cfg2_fp32", (4096, 4096, 4096), dict(dtype="fp32", b_layout=_capi.COL_MAJOR), "gemm_tf32x3_kernel", (128, 128, 32), 1),
@@ -75,7 +75,7 @@ def test_compile_matmul_for_the_baseline_configs(lib, name, args, kwargs, kernel
     batch = kwargs.get("batch", 1)
     assert r.tiles == -(-M // tile[0]) * -(-N // tile[1]) * batch
     assert 1 <= r.grid_dims[0] <= 148 and r.grid_dims[0] % cluster == 0 and r.grid_dims[1:] == (1, 1)
-    assert r.block_dims[0] in (192, 320) and r.shared_mem_bytes <= 227 * 1024 and r.tmem_columns <= 512
+    assert r.block_dims[0] in (192, 320, 448) and r.shared_mem_bytes <= 227 * 1024 and r.tmem_columns <= 512
     assert r.flops == 2.0 * M * N * K * batch
     # never faster than the roofline it is derived from
     peak = 1663.5e12 / (6.0 if kwargs["dtype"] == "fp32" else 1.0)
@@ -95,6 +95,11 @@ def test_plan_follows_the_dispatch_rules(lib):
     # cfg4 is HBM-bound, the big bf16 GEMMs are tensor-bound
     assert planner.compile_matmul(64, 64, 64, dtype="fp32", batch=2048).bound == "hbm"
     assert planner.compile_matmul(8192, 8192, 8192, dtype="bf16").bound == "tensor"
+    # split-K over a cluster only when the tiles alone leave most SMs idle and K is long enough
+    assert planner.compile_matmul(512, 512, 512, dtype="fp32").grid_dims[0] == 32 * 4
+    assert planner.compile_matmul(512, 1024, 512, dtype="fp32").cluster_size == 2
+    assert planner.compile_matmul(512, 512, 64, dtype="fp32").cluster_size == 1
+    assert planner.compile_matmul(1024, 1024, 512, dtype="fp32").cluster_size == 1
     # fewer SMs -> smaller grid
     assert planner.compile_matmul(8192, 8192, 8192, dtype="bf16", num_sms=64).grid_dims[0] == 64
 
@@ -112,7 +117,7 @@ def test_cuda_compile_kernel_descriptions(lib):
     from symplex_b200 import engine
     k = engine.cuda_compile_kernel("matmul", {"M": 128, "N": 128, "K": 64, "tile_m": 32, "tile_n": 32, "tile_k": 8})
     assert k.kernel_name() == "gemm_f32_fused_kernel" and k.estimated_gflops() > 0 and k.ptx_size() == len(k.ptx_source())
-    assert k.block_dims() == (320, 1, 1) and k.grid_dims()[0] == 2
+    assert k.block_dims() == (448, 1, 1) and k.grid_dims()[0] == 2
     e = engine.cuda_compile_kernel("elementwise", {"op": "add", "n": 1 << 24})
     assert e.kernel_name() == "fused_elementwise_ring_kernel" and e.block_dims() == (288, 1, 1)
     assert e.grid_dims()[0] == 148 * 2 and e.shared_mem_bytes() == 256 + 3 * 2 * 16384
