@@ -57,8 +57,10 @@ NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192 = 882.17e6 + 119.91e6
 NCU_TRAFFIC_BYTES = {
     "headline_bf16_8192_cube_bias_gelu": NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192,
     "cfg2_fp32_4096_cube_colmajor_b": 1103.19e6 + 62.13e6,
-    # fused fp32 kernel, 2048 x 64^3: 67.19 MB read + 5.14 MB written (C stays in L2 during the launch)
-    "cfg4_batched_fp32_2048x64_cube": 67.19e6 + 5.14e6,
+    # fused fp32 kernel, 2048 x 64^3: 67.20 MB read + 3.37 MB written (C stays in L2 during the launch)
+    "cfg4_batched_fp32_2048x64_cube": 67.20e6 + 3.37e6,
+    # fused fp32 kernel, 512^3 with split-K: 2.18 MB read (A and B once), C stays in L2
+    "cfg1_fp32_512_cube": 2.18e6,
     # fused elementwise ring kernel: 800.09 MB read (+ 4.09 MB of earlier dirty lines written back);
     # 805.38 MB read + 240.92 MB written (the last 27 MB of dst are still in L2 when the kernel ends)
     "f3_fused_axpb_sum_200M": 800.09e6 + 4.09e6,
