@@ -982,7 +982,7 @@ int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm
   const double t_tensor = out->flops / (peak * eff * occupancy);
   double hbm_bytes = out->bytes;
   if (kc.kind == KK_F32_SPLIT) hbm_bytes += 3.0 * ((double)p.M * p.K + (double)p.K * p.N) * 4.0 * p.batch;
-  const double t_hbm = hbm_bytes / (kc.kind == KK_F32_FUSED ? 0.4 * 6552e9 : 6552e9);
+  const double t_hbm = hbm_bytes / (kc.kind == KK_F32_FUSED ? 0.64 * 6552e9 : 6552e9);  // fused: measured streaming rate
   // The in-kernel-split fp32 kernel serves small problems, where filling and draining its pipeline (first
   // loads, conversion, MMA completion, accumulator drain, teardown: ~7 us measured) is most of the run time.
   const double t = (t_tensor > t_hbm ? t_tensor : t_hbm) + 4e-6 * (1 + out->prepass_launches) +
