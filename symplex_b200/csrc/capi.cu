@@ -946,7 +946,10 @@ int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm
   double eff;  // fraction of the tensor peak the variant sustains on large problems (measured)
   switch (kc.kind) {
     case KK_F32_FUSED:
-      ks = describe_gemm_f32_fused(f32_fused_split_k((long long)((p.M + 127) / 128) * ((p.N + 63) / 64) * p.batch, p.K, num_sms));
+      ks = f32_fused_tile_rows(p.M) == 64
+               ? describe_gemm_f32_fused(1, 64)
+               : describe_gemm_f32_fused(
+                     f32_fused_split_k((long long)((p.M + 127) / 128) * ((p.N + 63) / 64) * p.batch, p.K, num_sms), 128);
       eff = 0.45;
       break;
     case KK_F32_SPLIT: ks = describe_gemm_tf32x3(kc.bn); eff = 0.71; break;

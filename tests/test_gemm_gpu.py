@@ -525,3 +525,31 @@ def test_fp32_split_k_is_reproducible(lib, monkeypatch):
     for _ in range(5):
         assert torch.equal(sx.gemm(A, B), first)
     sx.sync_status()
+
+
+@pytest.mark.parametrize("M,N,K,batch", [(64, 64, 64, 8), (1, 64, 32, 1), (17, 100, 72, 3), (64, 320, 1000, 2), (40, 64, 4096, 1)])
+def test_fp32_64_row_mma_shape(lib, oracle, monkeypatch, M, N, K, batch):
+    """Problems with at most 64 rows run the M = 64 shape of the tensor-core instruction (accumulator rows in
+    lanes 0-15 of each tensor-memory quarter). It must give the bits the 128-row shape gives (the zero rows that
+    shape pads with contribute nothing) and meet the 1e-5 bound."""
+    rng = np.random.default_rng(11)
+    shape_a = (batch, M, K) if batch > 1 else (M, K)
+    shape_b = (batch, K, N) if batch > 1 else (K, N)
+    A = rng.uniform(-1, 1, shape_a).astype(np.float32)
+    B = rng.uniform(-1, 1, shape_b).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    tA, tB, tb = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), torch.from_numpy(bias).cuda()
+    out = {}
+    monkeypatch.setenv("SYMPLEX_B200_F32_SPLITK", "1")
+    for rows in ("64", "128"):
+        monkeypatch.setenv("SYMPLEX_B200_F32_TILE_ROWS", rows)
+        out[rows] = (sx.gemm(tA, tB, bias=tb, activation="tanh").cpu().numpy(),
+                     sx.gemm(tA, tB.transpose(-1, -2).contiguous(), b_layout=sx.COL_MAJOR,
+                             out_dtype=torch.bfloat16).float().cpu().numpy())
+    sx.sync_status()
+    assert np.array_equal(out["64"][0], out["128"][0]) and np.array_equal(out["64"][1], out["128"][1])
+    A2, B2 = (A[0], B[0]) if batch > 1 else (A, B)
+    ref = oracle.jit_parallel_matmul(A2, B2)
+    got, got_bf = (out["64"][0][0], out["64"][1][0]) if batch > 1 else out["64"]
+    assert rel_frobenius(got, np.tanh(ref + bias)) <= 1e-5
+    assert rel_frobenius(got_bf, oracle.bf16_round(ref)) <= 1e-2
