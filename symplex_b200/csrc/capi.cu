@@ -947,9 +947,9 @@ int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm
   switch (kc.kind) {
     case KK_F32_FUSED:
       ks = f32_fused_tile_rows(p.M) == 64
-               ? describe_gemm_f32_fused(1, 64)
+               ? describe_gemm_f32_small()
                : describe_gemm_f32_fused(
-                     f32_fused_split_k((long long)((p.M + 127) / 128) * ((p.N + 63) / 64) * p.batch, p.K, num_sms), 128);
+                     f32_fused_split_k((long long)((p.M + 127) / 128) * ((p.N + 63) / 64) * p.batch, p.K, num_sms));
       eff = 0.45;
       break;
     case KK_F32_SPLIT: ks = describe_gemm_tf32x3(kc.bn); eff = 0.71; break;
@@ -966,6 +966,8 @@ int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm
   out->tmem_columns = ks.tmem_cols;
   const long long mt = (p.M + ks.tile_m - 1) / ks.tile_m, nt = (p.N + ks.tile_n - 1) / ks.tile_n;
   out->tiles = mt * nt * p.batch;
+  if (kc.kind == KK_F32_FUSED && f32_fused_tile_rows(p.M) == 64)
+    out->tiles = nt * ((p.batch + 1) / 2);  // that kernel's unit of work holds two problems' 64 x 64 tiles
   const long long units = num_sms / ks.cluster;  // persistent: one CTA (or one cluster) per SM (group of SMs)
   const long long active = out->tiles < units ? out->tiles : units;
   out->grid_dims[0] = (int32_t)(active * ks.cluster); out->grid_dims[1] = 1; out->grid_dims[2] = 1;

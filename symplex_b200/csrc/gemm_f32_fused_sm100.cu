@@ -37,23 +37,17 @@
 
 namespace sx {
 
-template <int kSplit, int kBM = 128>
+template <int kSplit>
 struct FusedCfgT {
-  // kBM = 64: problems with at most 64 rows use the M = 64 shape of tcgen05.mma, so that no zero rows are
-  // loaded, converted and multiplied. The accumulator then sits in lanes 0-15 of each 32-lane quarter of
-  // tensor memory (row r in lane (r / 16) * 32 + r % 16) and an epilogue warp owns 16 rows.
-  static constexpr int BM = kBM, BN = 64, BK = 32, UMMA_K = 8, CHUNK_KB = 4;
-  static constexpr int ROWS_PER_WARP = BM / 4;
-  static constexpr int A_BYTES = BM * 128;                  // raw A, becomes A hi in place   16 KB (8 KB)
-  static constexpr int A_OFF = 0;
-  static constexpr int ALO_OFF = A_BYTES;                   // A lo                            16 KB (8 KB)
-  static constexpr int BRAW_OFF = 2 * A_BYTES;              // raw B (K-major: becomes hi)      8 KB
-  static constexpr int BHI_OFF = BRAW_OFF + 8 * 1024;       // B hi when B had to be transposed 8 KB
-  static constexpr int BLO_OFF = BHI_OFF + 8 * 1024;        // B lo                             8 KB
-  static constexpr int STAGE_BYTES = BLO_OFF + 8 * 1024;    // 56 KB (40 KB)
-  static constexpr int RAW_BYTES = BM * 128 + 8 * 1024;  // bytes the TMA delivers per stage
-  // Split-K trades one stage for the partial-tile buffer; the 64-row shape's smaller stages allow a fifth.
-  static constexpr int STAGES = kSplit > 1 ? 3 : (kBM == 64 ? 5 : 4);
+  static constexpr int BM = 128, BN = 64, BK = 32, UMMA_K = 8, CHUNK_KB = 4;
+  static constexpr int A_OFF = 0;             // raw A, becomes A hi          16 KB
+  static constexpr int ALO_OFF = 16 * 1024;   // A lo                          16 KB
+  static constexpr int BRAW_OFF = 32 * 1024;  // raw B (K-major: becomes hi)    8 KB
+  static constexpr int BHI_OFF = 40 * 1024;   // B hi when B had to be transposed 8 KB
+  static constexpr int BLO_OFF = 48 * 1024;   // B lo                           8 KB
+  static constexpr int STAGE_BYTES = 56 * 1024;
+  static constexpr int RAW_BYTES = 16 * 1024 + 8 * 1024;  // bytes the TMA delivers per stage
+  static constexpr int STAGES = kSplit > 1 ? 3 : 4;         // split-K trades one stage for the partial-tile buffer
   static constexpr int PART_BYTES = kSplit > 1 ? BM * BN * 4 : 0;  // this CTA's fp32 partial tile (ranks 1..)
   static constexpr int TMEM_COLS = 4 * BN;  // main[2] + corr[2]
   static constexpr int CONV_WARPS = 8;                      // converter warps ...
@@ -92,12 +86,11 @@ __device__ __forceinline__ void split4(const float4& x, float4& hi, float4& lo) 
   lo.x = tf32_rna(x.x - hi.x); lo.y = tf32_rna(x.y - hi.y); lo.z = tf32_rna(x.z - hi.z); lo.w = tf32_rna(x.w - hi.w);
 }
 
-template <typename OutT, bool kBmn, int kSplit, int kBM>
+template <typename OutT, bool kBmn, int kSplit>
 __global__ void __launch_bounds__(FusedCfg::THREADS, 1)
 gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const GemmParams p) {
-  using Cfg = FusedCfgT<kSplit, kBM>;
-  static_assert(kBM == 128 || (kBM == 64 && kSplit == 1), "the 64-row shape is built without split-K");
+  using Cfg = FusedCfgT<kSplit>;
   constexpr int BM = Cfg::BM, BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES, CH = Cfg::CHUNK_KB;
 
   extern __shared__ uint8_t dyn_smem[];
@@ -245,7 +238,7 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (tid == 0 && kb == 0) SX_TRACE(3);
         uint8_t* base = tiles + stage * Cfg::STAGE_BYTES;
 #pragma unroll
-        for (int i = 0; i < BM * 8 / CT; ++i) {  // A: BM x 8 16-byte chunks, position-wise
+        for (int i = 0; i < 1024 / CT; ++i) {  // A: 1024 16-byte chunks, position-wise
           const int off = (i * CT + tid) * 16;
           float4 hi, lo;
           split4(*reinterpret_cast<const float4*>(base + Cfg::A_OFF + off), hi, lo);
@@ -391,8 +384,8 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
 
       if (q == 0 && lane == 0) SX_TRACE(9);
-      const int row = m0 + q * Cfg::ROWS_PER_WARP + lane;
-      const bool row_ok = lane < Cfg::ROWS_PER_WARP && row < p.M;
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.M;
       const long long row_off = (long long)z * p.c_batch_stride + (long long)row * p.ldc;
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
@@ -422,10 +415,10 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 // ------------------------------------------------------------------ host side
 namespace {
 
-template <typename OutT, bool kBmn, int kSplit, int kBM = 128>
+template <typename OutT, bool kBmn, int kSplit>
 int launch_fused(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid, cudaStream_t stream) {
-  using Cfg = FusedCfgT<kSplit, kBM>;
-  auto kern = gemm_f32_fused_kernel<OutT, kBmn, kSplit, kBM>;
+  using Cfg = FusedCfgT<kSplit>;
+  auto kern = gemm_f32_fused_kernel<OutT, kBmn, kSplit>;
   SX_ENSURE_DYN_SMEM(kern, Cfg::DYN_SMEM);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
@@ -448,7 +441,6 @@ int launch_split(int split, const CUtensorMap& tmA, const CUtensorMap& tmB, cons
   switch (split) {
     case 4: return launch_fused<OutT, kBmn, 4>(tmA, tmB, p, grid, stream);
     case 2: return launch_fused<OutT, kBmn, 2>(tmA, tmB, p, grid, stream);
-    case 64: return launch_fused<OutT, kBmn, 1, 64>(tmA, tmB, p, grid, stream);  // 64-row shape, no split
     default: return launch_fused<OutT, kBmn, 1>(tmA, tmB, p, grid, stream);
   }
 }
@@ -465,12 +457,12 @@ bool f32_fused_operands_ok(const TcGemmArgs& a) {
 int launch_gemm_f32_fused(const TcGemmArgs& a, cudaStream_t stream) {
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return SX_ERR_INVALID;
   if (!f32_fused_operands_ok(a)) return SX_ERR_INVALID;
-  const int bm = f32_fused_tile_rows(a.M);
+  if (f32_fused_tile_rows(a.M) == 64) return launch_gemm_f32_small(a, stream);  // at most 64 rows: its own kernel
   CUtensorMap tmA, tmB;
   {
     uint64_t dims[3] = {(uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.batch};
     uint64_t strides[2] = {(uint64_t)a.lda * 4, (uint64_t)a.a_plane_stride * 4};
-    uint32_t box[3] = {32u, (uint32_t)bm, 1u};
+    uint32_t box[3] = {32u, 128u, 1u};
     int rc = encode_tensor_map_3d(&tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.A, dims, strides, box);
     if (rc != SX_OK) return rc;
   }
@@ -494,26 +486,24 @@ int launch_gemm_f32_fused(const TcGemmArgs& a, cudaStream_t stream) {
   p.bias = a.bias; p.residual = a.residual;
   p.alpha = a.alpha; p.beta = a.beta; p.act = a.act;
   p.status = a.status;
-  p.m_tiles = (int)((a.M + bm - 1) / bm);
+  p.m_tiles = (int)((a.M + 127) / 128);
   p.n_tiles = (int)((a.N + 63) / 64);
   const long long total = (long long)p.batch * p.m_tiles * p.n_tiles;
-  int split = f32_fused_split_k(total, a.K, a.num_sms);
-  if (bm == 64) split = 1;
+  const int split = f32_fused_split_k(total, a.K, a.num_sms);
   const long long clusters = total < a.num_sms / split ? total : a.num_sms / split;
   const int grid = (int)clusters * split;
-  const int variant = bm == 64 ? 64 : split;
   if (a.out_bf16)
-    return a.b_mn ? launch_split<__nv_bfloat16, true>(variant, tmA, tmB, p, grid, stream)
-                  : launch_split<__nv_bfloat16, false>(variant, tmA, tmB, p, grid, stream);
-  return a.b_mn ? launch_split<float, true>(variant, tmA, tmB, p, grid, stream)
-                : launch_split<float, false>(variant, tmA, tmB, p, grid, stream);
+    return a.b_mn ? launch_split<__nv_bfloat16, true>(split, tmA, tmB, p, grid, stream)
+                  : launch_split<__nv_bfloat16, false>(split, tmA, tmB, p, grid, stream);
+  return a.b_mn ? launch_split<float, true>(split, tmA, tmB, p, grid, stream)
+                : launch_split<float, false>(split, tmA, tmB, p, grid, stream);
 }
 
-// Rows of the output tile: 64 (the M = 64 MMA shape) when the whole problem has at most 64 rows, else 128.
+// Rows of one problem's output tile: 64 when the problem has at most 64 rows (gemm_f32_small_kernel takes it),
+// else 128 (this file's kernel). SYMPLEX_B200_F32_TILE_ROWS=128 forces this file's kernel (tests compare the two).
 int f32_fused_tile_rows(long long M) {
   if (const char* e = getenv("SYMPLEX_B200_F32_TILE_ROWS")) {
-    const int v = atoi(e);
-    if (v == 64 || v == 128) return v;
+    if (atoi(e) == 128) return 128;
   }
   return M <= 64 ? 64 : 128;
 }
@@ -538,11 +528,7 @@ int f32_fused_split_k(long long tiles, long long K, int num_sms) {
 }
 
 
-KernelShape describe_gemm_f32_fused(int split, int tile_rows) {
-  if (tile_rows == 64) {
-    using C = FusedCfgT<1, 64>;
-    return KernelShape{"gemm_f32_fused_kernel", C::BM, C::BN, C::BK, C::BM, C::BN, C::UMMA_K, C::THREADS, 1, C::STAGES, C::DYN_SMEM, C::TMEM_COLS};
-  }
+KernelShape describe_gemm_f32_fused(int split) {
   auto mk = [](auto cfg, int cluster) {
     using C = decltype(cfg);
     return KernelShape{"gemm_f32_fused_kernel", C::BM, C::BN, C::BK, C::BM, C::BN, C::UMMA_K, C::THREADS, cluster, C::STAGES, C::DYN_SMEM, C::TMEM_COLS};

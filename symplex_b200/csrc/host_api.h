@@ -83,7 +83,10 @@ int launch_gemm_f32_fused(const TcGemmArgs& a, cudaStream_t stream);
 bool f32_fused_operands_ok(const TcGemmArgs& a);
 // CTAs per output tile (1, 2 or 4; > 1 = split-K over a thread-block cluster) for `tiles` tiles of 128 x 64.
 int f32_fused_split_k(long long tiles, long long K, int num_sms);
-// Rows per output tile of that kernel: 64 for problems with at most 64 rows (no split-K then), else 128.
+// The same arithmetic for problems with at most 64 rows (batches of tiny products): 64 x 64 tiles (M = 64 MMA
+// shape) and separate rings for raw and converted tiles (gemm_f32_small_sm100.cu).
+int launch_gemm_f32_small(const TcGemmArgs& a, cudaStream_t stream);
+// Rows of one problem's output tile: 64 (problems with at most 64 rows go to launch_gemm_f32_small), else 128.
 int f32_fused_tile_rows(long long M);
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda dependency).
@@ -116,7 +119,8 @@ struct KernelShape {
 KernelShape describe_gemm_tc(int bn);      // gemm_sm100.cu: bf16, one CTA per tile
 KernelShape describe_gemm_pair(int kmb);   // gemm_pair_sm100.cu: bf16, CTA pair, kmb = 1 (256x256) or 2 (512x256)
 KernelShape describe_gemm_tf32x3(int bn);  // gemm_tf32x3_sm100.cu: fp32 from pre-split planes
-KernelShape describe_gemm_f32_fused(int split_k, int tile_rows);  // gemm_f32_fused_sm100.cu: fp32, hi/lo split in shared memory
+KernelShape describe_gemm_f32_fused(int split_k);
+KernelShape describe_gemm_f32_small();     // gemm_f32_small_sm100.cu: fp32, at most 64 rows  // gemm_f32_fused_sm100.cu: fp32, hi/lo split in shared memory
 
 // ---- fused elementwise programs (fused_elementwise.cu) -------------------------------------------------------
 // One op of a compiled program. Operand kinds: input array (value = compacted input index), immediate

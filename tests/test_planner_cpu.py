@@ -60,7 +60,7 @@ CONFIGS = [
      "gemm_pair_kernel", (256, 256, 64), 2),
     ("cfg2_fp32", (4096, 4096, 4096), dict(dtype="fp32", b_layout=_capi.COL_MAJOR), "gemm_tf32x3_kernel", (128, 128, 32), 1),
     ("cfg3", (8192, 16384, 4096), dict(dtype="bf16", activation="gelu"), "gemm_pair_kernel", (512, 256, 64), 2),
-    ("cfg4", (64, 64, 64), dict(dtype="fp32", batch=2048), "gemm_f32_fused_kernel", (128, 64, 32), 1),
+    ("cfg4", (64, 64, 64), dict(dtype="fp32", batch=2048), "gemm_f32_small_kernel", (64, 64, 32), 1),
     ("cfg5", (65536, 8192, 8192), dict(dtype="bf16"), "gemm_pair_kernel", (512, 256, 64), 2),
     ("small_bf16", (256, 192, 128), dict(dtype="bf16"), "gemm_tc_kernel", (128, 64, 64), 1),
 ]
@@ -73,7 +73,10 @@ def test_compile_matmul_for_the_baseline_configs(lib, name, args, kwargs, kernel
     assert r.kernel_name == kernel and r.optimal_tile == tile and r.cluster_size == cluster
     M, N, K = args
     batch = kwargs.get("batch", 1)
-    assert r.tiles == -(-M // tile[0]) * -(-N // tile[1]) * batch
+    if kernel == "gemm_f32_small_kernel":  # its unit of work holds two problems
+        assert r.tiles == -(-N // tile[1]) * -(-batch // 2) and r.mma_shape == (128, 128, 8)
+    else:
+        assert r.tiles == -(-M // tile[0]) * -(-N // tile[1]) * batch
     assert 1 <= r.grid_dims[0] <= 148 and r.grid_dims[0] % cluster == 0 and r.grid_dims[1:] == (1, 1)
     assert r.block_dims[0] in (192, 320, 448) and r.shared_mem_bytes <= 227 * 1024 and r.tmem_columns <= 512
     assert r.flops == 2.0 * M * N * K * batch
@@ -118,6 +121,7 @@ def test_cuda_compile_kernel_descriptions(lib):
     k = engine.cuda_compile_kernel("matmul", {"M": 128, "N": 128, "K": 64, "tile_m": 32, "tile_n": 32, "tile_k": 8})
     assert k.kernel_name() == "gemm_f32_fused_kernel" and k.estimated_gflops() > 0 and k.ptx_size() == len(k.ptx_source())
     assert k.block_dims() == (448, 1, 1) and k.grid_dims()[0] == 2
+    assert engine.cuda_compile_kernel("matmul", {"M": 64, "N": 128, "K": 64}).kernel_name() == "gemm_f32_small_kernel"
     e = engine.cuda_compile_kernel("elementwise", {"op": "add", "n": 1 << 24})
     assert e.kernel_name() == "fused_elementwise_ring_kernel" and e.block_dims() == (288, 1, 1)
     assert e.grid_dims()[0] == 148 * 2 and e.shared_mem_bytes() == 256 + 3 * 2 * 16384
