@@ -385,6 +385,31 @@ static int host_buf(int i, size_t bytes, void** out) {
   return SX_OK;
 }
 
+// The calling thread's streams: the compute stream always, the two copy streams and the per-chunk events of the
+// chunked pipelines on request. A thread that moved to another device starts over with fresh buffers.
+static int host_ctx(bool pipeline, HostCtx** out) {
+  HostCtx& h = t_host;
+  int dev = 0;
+  SX_CUDA(cudaGetDevice(&dev));
+  if (h.stream == nullptr || h.dev != dev) {
+    SX_CUDA(cudaStreamCreateWithFlags(&h.stream, cudaStreamNonBlocking));
+    h.dev = dev;
+    h.pipeline_ready = false;
+    for (int i = 0; i < 6; ++i) { h.buf[i] = nullptr; h.cap[i] = 0; }
+  }
+  if (pipeline && !h.pipeline_ready) {
+    SX_CUDA(cudaStreamCreateWithFlags(&h.h2d, cudaStreamNonBlocking));
+    SX_CUDA(cudaStreamCreateWithFlags(&h.d2h, cudaStreamNonBlocking));
+    for (int i = 0; i < 64; ++i) {
+      SX_CUDA(cudaEventCreateWithFlags(&h.ev_in[i], cudaEventDisableTiming));
+      SX_CUDA(cudaEventCreateWithFlags(&h.ev_out[i], cudaEventDisableTiming));
+    }
+    h.pipeline_ready = true;
+  }
+  *out = &h;
+  return SX_OK;
+}
+
 static int gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
                      const void* residual) {
   Plan p;
@@ -395,14 +420,9 @@ static int gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, v
   DeviceState* st = nullptr;
   rc = device_state(&st);
   if (rc != SX_OK) return rc;
-  HostCtx& h = t_host;
-  int dev = 0;
-  SX_CUDA(cudaGetDevice(&dev));
-  if (h.stream == nullptr || h.dev != dev) {
-    SX_CUDA(cudaStreamCreateWithFlags(&h.stream, cudaStreamNonBlocking));
-    h.dev = dev;
-    for (int i = 0; i < 6; ++i) { h.buf[i] = nullptr; h.cap[i] = 0; }
-  }
+  HostCtx* hp = nullptr;
+  if ((rc = host_ctx(false, &hp)) != SX_OK) return rc;
+  HostCtx& h = *hp;
   const size_t in_elt = p.f32_in ? 4 : 2, out_elt = p.bf16_out ? 2 : 4;
   // Extent of each host operand including batch strides.
   const size_t a_bytes = ((size_t)(p.batch - 1) * p.a_bs + (size_t)(p.M - 1) * p.lda + p.K) * in_elt;
@@ -428,15 +448,7 @@ static int gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, v
     const long long nchunks = (p.M + chunk_rows - 1) / chunk_rows;
     const bool dense = p.lda == p.K && p.ldc == p.N;
     if (p.batch == 1 && dense && !residual && nchunks >= 3 && nchunks <= 64 && getenv("SYMPLEX_B200_NO_PIPELINE") == nullptr) {
-      if (!h.pipeline_ready) {
-        SX_CUDA(cudaStreamCreateWithFlags(&h.h2d, cudaStreamNonBlocking));
-        SX_CUDA(cudaStreamCreateWithFlags(&h.d2h, cudaStreamNonBlocking));
-        for (int i = 0; i < 64; ++i) {
-          SX_CUDA(cudaEventCreateWithFlags(&h.ev_in[i], cudaEventDisableTiming));
-          SX_CUDA(cudaEventCreateWithFlags(&h.ev_out[i], cudaEventDisableTiming));
-        }
-        h.pipeline_ready = true;
-      }
+      if ((rc = host_ctx(true, &hp)) != SX_OK) return rc;
       void* ws = nullptr;
       if (p.total && (rc = pool_scratch(st, p.total, &ws)) != SX_OK) return rc;
       SX_CUDA(cudaMemcpyAsync(dB, B, b_bytes, cudaMemcpyHostToDevice, h.h2d));
@@ -567,23 +579,9 @@ static int fe_host(const symplex_fused_op* ops, size_t n_ops, const void* const*
     if (inputs == nullptr || inputs[prog->input_map[i]] == nullptr) return fail(SX_ERR_INVALID, "null input array");
   DeviceState* st = nullptr;
   if ((rc = device_state(&st)) != SX_OK) return rc;
-  HostCtx& h = t_host;
-  int dev = 0;
-  SX_CUDA(cudaGetDevice(&dev));
-  if (h.stream == nullptr || h.dev != dev) {
-    SX_CUDA(cudaStreamCreateWithFlags(&h.stream, cudaStreamNonBlocking));
-    h.dev = dev;
-    for (int i = 0; i < 6; ++i) { h.buf[i] = nullptr; h.cap[i] = 0; }
-  }
-  if (!h.pipeline_ready) {
-    SX_CUDA(cudaStreamCreateWithFlags(&h.h2d, cudaStreamNonBlocking));
-    SX_CUDA(cudaStreamCreateWithFlags(&h.d2h, cudaStreamNonBlocking));
-    for (int i = 0; i < 64; ++i) {
-      SX_CUDA(cudaEventCreateWithFlags(&h.ev_in[i], cudaEventDisableTiming));
-      SX_CUDA(cudaEventCreateWithFlags(&h.ev_out[i], cudaEventDisableTiming));
-    }
-    h.pipeline_ready = true;
-  }
+  HostCtx* hp = nullptr;
+  if ((rc = host_ctx(true, &hp)) != SX_OK) return rc;
+  HostCtx& h = *hp;
   // Arena: one device array per used input, the output array, one double per chunk.
   const int ni = prog->n_inputs;
   const size_t eb = (size_t)elem_bytes;

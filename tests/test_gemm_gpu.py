@@ -553,3 +553,47 @@ def test_fp32_64_row_mma_shape(lib, oracle, monkeypatch, M, N, K, batch):
     got, got_bf = (out["64"][0][0], out["64"][1][0]) if batch > 1 else out["64"]
     assert rel_frobenius(got, np.tanh(ref + bias)) <= 1e-5
     assert rel_frobenius(got_bf, oracle.bf16_round(ref)) <= 1e-2
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_configurations_against_oracle(lib, oracle, seed):
+    """Seeded random sweep over everything the descriptor can say: dtype, ragged M / N / K, batch, B layout, bias,
+    scale, activation, output dtype. Which kernel serves a case is the dispatcher's business; the oracle bound is
+    the same for all of them."""
+    rng = np.random.default_rng(1000 + seed)
+    f32 = bool(rng.integers(0, 2))
+    M, N, K = (int(rng.integers(1, 400)), int(rng.integers(1, 400)), int(rng.integers(1, 700)))
+    if seed % 6 == 0:
+        M = int(rng.integers(1, 65))  # the small-row kernel
+    batch = int(rng.choice([1, 1, 2, 3, 5]))
+    col_major = bool(rng.integers(0, 2))
+    act = [None, "relu", "gelu", "sigmoid", "tanh", "silu"][int(rng.integers(0, 6))]
+    use_bias = bool(rng.integers(0, 2))
+    alpha = float(rng.choice([1.0, 0.5, -2.0]))
+    out_bf16 = (not f32) and bool(rng.integers(0, 2))
+    A = rng.uniform(-1, 1, (batch, M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (batch, K, N)).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32) if use_bias else None
+    if not f32:
+        A, B = oracle.bf16_round(A), oracle.bf16_round(B)
+    tdt = torch.float32 if f32 else torch.bfloat16
+    tA = torch.from_numpy(A).to(DEV).to(tdt)
+    tB = torch.from_numpy(B).to(DEV).to(tdt)
+    if col_major:
+        tB = tB.transpose(-1, -2).contiguous()
+    if batch == 1:
+        tA, tB = tA[0], tB[0]
+    got = sx.gemm(tA, tB, bias=torch.from_numpy(bias).to(DEV) if use_bias else None, activation=act, alpha=alpha,
+                  b_layout=sx.COL_MAJOR if col_major else sx.ROW_MAJOR,
+                  out_dtype=torch.bfloat16 if out_bf16 else torch.float32)
+    sx.sync_status()
+    got = got.float().cpu().numpy().reshape(batch, M, N)
+    for z in range(batch):
+        ref = oracle.epilogue(oracle.jit_parallel_matmul(A[z], B[z]), alpha=alpha, bias=bias,
+                              act=_capi.ACTIVATIONS[act])
+        if out_bf16:
+            ref = oracle.bf16_round(ref)
+        tol = TOL_F32 if f32 else TOL_BF16
+        err = rel_frobenius(got[z], ref)
+        assert err <= tol, dict(seed=seed, f32=f32, shape=(batch, M, N, K), col_major=col_major, act=act, bias=use_bias,
+                                alpha=alpha, out_bf16=out_bf16, err=err)
