@@ -597,3 +597,22 @@ def test_random_configurations_against_oracle(lib, oracle, seed):
         err = rel_frobenius(got[z], ref)
         assert err <= tol, dict(seed=seed, f32=f32, shape=(batch, M, N, K), col_major=col_major, act=act, bias=use_bias,
                                 alpha=alpha, out_bf16=out_bf16, err=err)
+
+
+def test_small_row_kernel_unaligned_output_and_odd_batch(lib, oracle):
+    """N = 101 makes the rows of C 404 bytes long, so the TMA-store epilogue is not available and the kernel stores
+    directly; an odd batch leaves the last pair half empty; M = 30 leaves two epilogue warps without rows."""
+    rng = np.random.default_rng(5)
+    batch, M, N, K = 3, 30, 101, 72
+    A = rng.uniform(-1, 1, (batch, M, K)).astype(np.float32)
+    Bt = rng.uniform(-1, 1, (batch, N, K)).astype(np.float32)  # column-major B: [N, K]
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    from symplex_b200 import planner
+    assert planner.compile_matmul(M, N, K, dtype="fp32", batch=batch, b_layout=sx.COL_MAJOR).kernel_name == \
+        "gemm_f32_small_kernel"
+    got = sx.gemm(torch.from_numpy(A).cuda(), torch.from_numpy(Bt).cuda(), bias=torch.from_numpy(bias).cuda(),
+                  activation="relu", b_layout=sx.COL_MAJOR).cpu().numpy()
+    sx.sync_status()
+    for z in range(batch):
+        ref = np.maximum(oracle.jit_parallel_matmul(A[z], np.ascontiguousarray(Bt[z].T)) + bias, 0)
+        assert rel_frobenius(got[z], ref) <= TOL_F32
