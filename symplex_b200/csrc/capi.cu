@@ -224,7 +224,8 @@ static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_
   if (const char* e = getenv("SYMPLEX_B200_TILE")) forced = atoi(e);
   if (p.f32_in) {
     // Small and batched problems (each operand element feeds only a few tiles): split inside the GEMM kernel.
-    bool fused = (p.M + 127) / 128 <= 8 && (p.N + 63) / 64 <= 16 && f32_fused_ok;
+    // With at most 64 rows there is a single row of tiles: no B element is converted twice, whatever N is.
+    bool fused = (p.M <= 64 || ((p.M + 127) / 128 <= 8 && (p.N + 63) / 64 <= 16)) && f32_fused_ok;
     if (const char* e = getenv("SYMPLEX_B200_F32_FUSED")) fused = atoi(e) != 0 && f32_fused_ok;
     if (fused) return {KK_F32_FUSED, 64};
     if (forced == 64 || forced == 128) return {KK_F32_SPLIT, forced};

@@ -527,7 +527,8 @@ def test_fp32_split_k_is_reproducible(lib, monkeypatch):
     sx.sync_status()
 
 
-@pytest.mark.parametrize("M,N,K,batch", [(64, 64, 64, 8), (1, 64, 32, 1), (17, 100, 72, 3), (64, 320, 1000, 2), (40, 64, 4096, 1)])
+@pytest.mark.parametrize("M,N,K,batch", [(64, 64, 64, 8), (1, 64, 32, 1), (17, 100, 72, 3), (64, 320, 1000, 2), (40, 64, 4096, 1),
+                                         (48, 2048, 256, 1)])
 def test_fp32_64_row_mma_shape(lib, oracle, monkeypatch, M, N, K, batch):
     """Problems with at most 64 rows run the M = 64 shape of the tensor-core instruction (accumulator rows in
     lanes 0-15 of each tensor-memory quarter). It must give the bits the 128-row shape gives (the zero rows that
