@@ -185,6 +185,11 @@ typedef struct symplex_device_info {
 } symplex_device_info;
 int symplex_cuda_device_info(symplex_device_info* out);
 
+/* sizeof() of the structs of this header as the library was compiled: {symplex_gemm_desc, symplex_device_info,
+ * symplex_fused_op, symplex_b200_target, symplex_gemm_plan}. Lets a binding written in another language check
+ * its own struct definitions at load time. */
+void symplex_b200_abi_sizes(int32_t out[5]);
+
 /* Kernels launched by this library on the calling process since load (all threads). */
 uint64_t symplex_b200_launch_count(void);
 

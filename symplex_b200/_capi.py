@@ -118,6 +118,7 @@ SIGNATURES = {
     "symplex_cuda_available": (c_int, []),
     "symplex_cuda_device_info": (c_int, [ctypes.POINTER(DeviceInfo)]),
     "symplex_b200_launch_count": (c_uint64, []),
+    "symplex_b200_abi_sizes": (None, [ctypes.POINTER(c_int32 * 5)]),
     "symplex_simd_fused_elementwise_f32": (c_double, [ctypes.POINTER(FusedOp), c_size_t, ctypes.POINTER(c_void_p), c_size_t,
                                                       ctypes.POINTER(c_float), c_size_t, c_size_t, c_uint8, _F32P]),
     "symplex_simd_fused_elementwise_f64": (c_double, [ctypes.POINTER(FusedOp), c_size_t, ctypes.POINTER(c_void_p), c_size_t,
@@ -171,6 +172,11 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)  # AttributeError here = header and library out of sync
         fn.restype = restype
         fn.argtypes = argtypes
+    sizes = (c_int32 * 5)()
+    lib.symplex_b200_abi_sizes(ctypes.byref(sizes))
+    mine = [ctypes.sizeof(t) for t in (GemmDesc, DeviceInfo, FusedOp, Target, GemmPlan)]
+    if list(sizes) != mine:
+        raise ImportError(f"struct layouts of {LIB_PATH} {list(sizes)} differ from this binding's {mine}: rebuild")
     _lib = lib
     return lib
 

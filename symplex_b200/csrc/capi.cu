@@ -841,6 +841,15 @@ int symplex_cuda_device_info(symplex_device_info* out) {
 
 uint64_t symplex_b200_launch_count(void) { return g_launches.load(); }
 
+void symplex_b200_abi_sizes(int32_t out[5]) {
+  if (!out) return;
+  out[0] = (int32_t)sizeof(symplex_gemm_desc);
+  out[1] = (int32_t)sizeof(symplex_device_info);
+  out[2] = (int32_t)sizeof(symplex_fused_op);
+  out[3] = (int32_t)sizeof(symplex_b200_target);
+  out[4] = (int32_t)sizeof(symplex_gemm_plan);
+}
+
 int symplex_b200_fused_elementwise_plan(int n_inputs, int64_t n, int element_bytes, int num_sms,
                                         int32_t grid_dims[3], int32_t block_dims[3], int32_t* shared_mem_bytes) {
   if (n_inputs < 0 || n_inputs > FE_MAX_INPUTS || n <= 0 || (element_bytes != 4 && element_bytes != 8) || !grid_dims ||

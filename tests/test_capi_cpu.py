@@ -140,3 +140,11 @@ def test_missing_library_raises(monkeypatch, tmp_path):
     monkeypatch.setattr(_capi, "LIB_PATH", str(tmp_path / "libsymplex_b200.so"))
     with pytest.raises(ImportError, match="no CPU fallback"):
         _capi.load()
+
+
+def test_struct_sizes_match_the_compiled_library(lib):
+    sizes = (ctypes.c_int32 * 5)()
+    lib.symplex_b200_abi_sizes(ctypes.byref(sizes))
+    assert list(sizes) == [ctypes.sizeof(t) for t in (_capi.GemmDesc, _capi.DeviceInfo, _capi.FusedOp, _capi.Target,
+                                                      _capi.GemmPlan)]
+    assert sizes[0] == 104 and sizes[2] == 8
