@@ -70,8 +70,16 @@ __device__ unsigned long long g_fused_trace[32];
 #else
 #define SX_TRACE(i) do { } while (0)
 #endif
-__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed_after(uint32_t cluster_addr, uint32_t dep) {
+  asm volatile(
+      "{\n"
+      ".reg .pred q;\n"
+      "setp.eq.u32 q, %1, 0xffffffff;\n"
+      "@q mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n"
+      "@!q mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n"
+      "}\n" ::"r"(cluster_addr),
+      "r"(dep)
+      : "memory");
 }
 
 // Round to tf32 (10 mantissa bits), nearest with ties away from zero - the result of cvt.rna.tf32.f32, written
@@ -372,11 +380,16 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 sum[j + 0] += v[r][g].x; sum[j + 1] += v[r][g].y; sum[j + 2] += v[r][g].z; sum[j + 3] += v[r][g].w;
               }
           }
-          // The loaded values have been consumed, so the peers may overwrite their buffers: no release needed.
-          __syncwarp();
+          // Hand the buffers back only when the loads have returned: the sums they feed are folded into a vote
+          // that the (relaxed: nothing to publish) remote arrives depend on - see mbar_arrive_after.
+          uint32_t seen = 0;
+#pragma unroll
+          for (int j = 0; j < BN; ++j) seen |= __float_as_uint(sum[j]);
+          const uint32_t vote = __ballot_sync(__activemask(), seen == 0x7fc0dead);
           if (lane == 0) {
 #pragma unroll
-            for (int r = 1; r < kSplit; ++r) mbar_arrive_cluster_relaxed(mapa_u32(smem_u32(&part_empty[q]), (uint32_t)r));
+            for (int r = 1; r < kSplit; ++r)
+              mbar_arrive_cluster_relaxed_after(mapa_u32(smem_u32(&part_empty[q]), (uint32_t)r), vote);
           }
         }
         if (!got) break;

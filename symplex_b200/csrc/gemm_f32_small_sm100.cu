@@ -75,6 +75,21 @@ extern "C" __attribute__((visibility("default"))) int symplex_b200_debug_small_t
 #define SM_TRACE(tile, i) do { } while (0)
 #endif
 
+// Loads of a raw stage, volatile so that they stay where they are written (before the stage is handed back).
+__device__ __forceinline__ float4 ld_raw_v4(const uint8_t* p) {
+  float4 v;
+  asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(smem_u32(p))
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_raw_f32(const float* p) {
+  float v;
+  asm volatile("ld.volatile.shared.f32 %0, [%1];" : "=f"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+
 template <typename OutT, bool kBmn>
 __global__ void __launch_bounds__(SmallCfg::THREADS, 1)
 gemm_f32_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -232,11 +247,11 @@ gemm_f32_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         float4 xa[NA], xb[NB];
 #pragma unroll
         for (int i = 0; i < NA; ++i)  // A: 128 x 8 16-byte chunks, position-wise (the swizzle carries over)
-          xa[i] = *reinterpret_cast<const float4*>(raw + Cfg::RAW_A + (i * CT + tid) * 16);
+          xa[i] = ld_raw_v4(raw + Cfg::RAW_A + (i * CT + tid) * 16);
         if constexpr (!kBmn) {
 #pragma unroll
           for (int i = 0; i < NB; ++i)  // B [2 x 64 n][32 k], position-wise
-            xb[i] = *reinterpret_cast<const float4*>(raw + Cfg::RAW_B + (i * CT + tid) * 16);
+            xb[i] = ld_raw_v4(raw + Cfg::RAW_B + (i * CT + tid) * 16);
         } else {
           const float* rb = reinterpret_cast<const float*>(raw + Cfg::RAW_B);  // [2][32 k][64 n], unswizzled
 #pragma unroll
@@ -244,11 +259,19 @@ gemm_f32_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const int item = i * CT + tid;
             const int n = item & 63, kc = (item >> 6) & 7, b = item >> 9;
             const float* src = rb + b * (32 * 64) + kc * 4 * 64 + n;
-            xb[i] = make_float4(src[0], src[64], src[128], src[192]);
+            xb[i] = make_float4(ld_raw_f32(src), ld_raw_f32(src + 64), ld_raw_f32(src + 128), ld_raw_f32(src + 192));
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&raw_empty[rs]);  // this warp has read the raw stage: the producer may refill it
+        // The stage may be overwritten as soon as the producer sees the arrivals, but loads that are still in
+        // flight are not waited for (see mbar_arrive_after): fold every load's result into one word, vote on it,
+        // and make the arrive depend on the vote.
+        uint32_t seen = 0;
+#pragma unroll
+        for (int i = 0; i < NA; ++i) seen |= __float_as_uint(xa[i].x) | __float_as_uint(xa[i].w);
+#pragma unroll
+        for (int i = 0; i < NB; ++i) seen |= __float_as_uint(xb[i].x) | __float_as_uint(xb[i].y) | __float_as_uint(xb[i].z) | __float_as_uint(xb[i].w);
+        const uint32_t vote = __ballot_sync(__activemask(), seen == 0x7fc0dead);
+        if (lane == 0) mbar_arrive_after(&raw_empty[rs], vote);  // the producer may refill the raw stage
 #pragma unroll
         for (int i = 0; i < NA; ++i) {
           const int off = (i * CT + tid) * 16;

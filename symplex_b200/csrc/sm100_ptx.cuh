@@ -71,6 +71,24 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrive that carries a data dependency on `dep` (a value the compiler cannot fold), so it cannot be issued before
+// the instructions that produce `dep`. Used to hand a shared-memory buffer back to an asynchronous producer:
+// neither program order nor the arrive's release semantics make the hardware wait for shared-memory LOADS that are
+// still in flight, so a buffer released right after loading from it can be overwritten under those loads
+// (observed: two of the four wavefronts of one 16-byte load returned the next tile's data). Fold the loaded values
+// into one word, let a warp vote consume it (it cannot issue before every lane's loads have returned), and pass
+// the vote here.
+__device__ __forceinline__ void mbar_arrive_after(uint64_t* bar, uint32_t dep) {
+  asm volatile(
+      "{\n"
+      ".reg .pred q;\n"
+      "setp.eq.u32 q, %1, 0xffffffff;\n"
+      "@q mbarrier.arrive.shared::cta.b64 _, [%0];\n"
+      "@!q mbarrier.arrive.shared::cta.b64 _, [%0];\n"
+      "}\n" ::"r"(smem_u32(bar)),
+      "r"(dep)
+      : "memory");
+}
 // Arrive on a barrier that lives in another CTA of the cluster (address from mapa_u32).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
