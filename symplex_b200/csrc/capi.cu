@@ -233,15 +233,20 @@ static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_
     return {KK_F32_SPLIT, wide ? 128 : 64};
   }
   const int bn = pick_bn(p.M, p.N, p.batch, num_sms, forced);
-  // Tile shape by how much work there is: 512x256 per CTA pair when that still fills the machine at least
-  // twice over (least L2 -> SM traffic per flop), 256x256 pairs for mid-size problems, single-CTA tiles
-  // (down to 128x64) when only those give every SM something to do.
+  // Tile shape by how much work there is: CTA pairs once 256x256 pair tiles give every pair of SMs something to
+  // do, single-CTA tiles (down to 128x64) otherwise. Between the two pair shapes the cheaper one by a wave count:
+  // waves x tile area / measured tensor-pipe utilisation (512x256: 0.875, least L2 -> SM traffic per flop;
+  // 256x256: 0.80). 4096^3: 2 waves of 512x256 beat 4 waves of 256x256 by 6 % (measured).
   int mode = 0;  // 0 single CTA, 1 pair 256x256, 2 pair 512x256
   if (forced == 0 && bn == 256 && p.M > 128) {
     const long long pairs = num_sms / 2;
     const long long nt = (p.N + 255) / 256;
-    if (((p.M + 511) / 512) * nt * p.batch >= 2 * pairs) mode = 2;
-    else if (((p.M + 255) / 256) * nt * p.batch >= pairs) mode = 1;
+    const long long t256 = ((p.M + 255) / 256) * nt * p.batch, t512 = ((p.M + 511) / 512) * nt * p.batch;
+    if (t256 >= pairs) {
+      const double cost256 = (double)((t256 + pairs - 1) / pairs) * 1.0 / 0.80;
+      const double cost512 = (double)((t512 + pairs - 1) / pairs) * 2.0 / 0.875;
+      mode = cost512 <= cost256 ? 2 : 1;
+    }
   }
   if (const char* e = getenv("SYMPLEX_B200_PAIR")) mode = atoi(e);
   if (n_peers > 0 && mode == 0) mode = 1;  // only the pair kernels carry the peer-store epilogue

@@ -57,7 +57,7 @@ CONFIGS = [
     # name, args, kwargs, kernel, tile, cluster
     ("cfg1", (512, 512, 512), dict(dtype="fp32"), "gemm_f32_fused_kernel", (128, 64, 32), 4),  # split-K over a cluster
     ("cfg2_bf16", (4096, 4096, 4096), dict(dtype="bf16", out_dtype="fp32", b_layout=_capi.COL_MAJOR),
-     "gemm_pair_kernel", (256, 256, 64), 2),
+     "gemm_pair_kernel", (512, 256, 64), 2),  # 2 waves of 512x256 beat 4 waves of 256x256
     ("cfg2_fp32", (4096, 4096, 4096), dict(dtype="fp32", b_layout=_capi.COL_MAJOR), "gemm_tf32x3_kernel", (128, 128, 32), 1),
     ("cfg3", (8192, 16384, 4096), dict(dtype="bf16", activation="gelu"), "gemm_pair_kernel", (512, 256, 64), 2),
     ("cfg4", (64, 64, 64), dict(dtype="fp32", batch=2048), "gemm_f32_small_kernel", (64, 64, 32), 1),
@@ -103,6 +103,9 @@ def test_plan_follows_the_dispatch_rules(lib):
     assert planner.compile_matmul(512, 1024, 512, dtype="fp32").cluster_size == 2
     assert planner.compile_matmul(512, 512, 64, dtype="fp32").cluster_size == 1
     assert planner.compile_matmul(1024, 1024, 512, dtype="fp32").cluster_size == 1
+    # mid-size bf16: pair tiles of 256x256 when the taller tile would only add padding or a wave
+    assert planner.compile_matmul(256, 32768, 512, dtype="bf16").optimal_tile == (256, 256, 64)
+    assert planner.compile_matmul(1024, 4096, 512, dtype="bf16").kernel_name == "gemm_tc_kernel"
     # fewer SMs -> smaller grid
     assert planner.compile_matmul(8192, 8192, 8192, dtype="bf16", num_sms=64).grid_dims[0] == 64
 
