@@ -75,6 +75,9 @@ ELEMENTWISE_WORKLOADS = {
                                    consts=[2.0, 1.0], reduce_op=0, desc="sum(x * 2.0 + 1.0)"),
     "f3_fused_mul_add_relu_64M": dict(n=64 << 20, n_inputs=3, ops=[(2, 0, 0, 0, 1), (0, 2, 0, 0, 2), (15, 2, 1, 0, 0)],
                                       consts=[], reduce_op=255, desc="dst = relu(a * b + c)"),
+    # the f64 twin (what the reference's Python layer calls for float64 NumPy arrays)
+    "f3_fused_axpb_f64_64M": dict(n=64 << 20, n_inputs=1, ops=[(2, 0, 0, 1, 0), (0, 2, 0, 1, 1)], consts=[2.0, 1.0],
+                                  reduce_op=255, desc="dst = x * 2.0 + 1.0 (float64)", f64=True),
 }
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -212,17 +215,18 @@ def _elementwise_cpu(w, n_sample, steps, warmup):
     from oracle_loader import load_oracle
     orc = load_oracle()
     rng = np.random.default_rng(0)
-    arrays = [rng.uniform(-1, 1, n_sample).astype(np.float32) for _ in range(w["n_inputs"])]
+    ndt = np.float64 if w.get("f64") else np.float32
+    arrays = [rng.uniform(-1, 1, n_sample).astype(ndt) for _ in range(w["n_inputs"])]
     for _ in range(max(1, warmup)):
-        orc.fused_elementwise(w["ops"], arrays, w["consts"], reduce_op=w["reduce_op"])
+        orc.fused_elementwise(w["ops"], arrays, w["consts"], reduce_op=w["reduce_op"], dtype=ndt)
     t0 = time.perf_counter()
     for _ in range(steps):
-        orc.fused_elementwise(w["ops"], arrays, w["consts"], reduce_op=w["reduce_op"])
+        orc.fused_elementwise(w["ops"], arrays, w["consts"], reduce_op=w["reduce_op"], dtype=ndt)
     dt = (time.perf_counter() - t0) / steps
     streams = w["n_inputs"] + (0 if w["reduce_op"] != 255 else 1)
     sample = (f"{n_sample} of {w['n']} elements, C restatement of the reference's fused_elem_f32_avx2_core "
               "(scalar code, 1 thread; the reference runs the same chain 8 lanes wide on 1 thread)")
-    return 4.0 * streams * n_sample / dt / 1e9, dt, sample
+    return (8.0 if w.get("f64") else 4.0) * streams * n_sample / dt / 1e9, dt, sample
 
 
 def main_elementwise(args):
@@ -231,18 +235,21 @@ def main_elementwise(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     n, reduce = w["n"], w["reduce_op"] != 255
+    f64 = bool(w.get("f64"))
+    eb = 8 if f64 else 4
     streams = w["n_inputs"] + (0 if reduce else 1)
-    algo_bytes = 4.0 * streams * n
+    algo_bytes = float(eb) * streams * n
     config = {"workload": args.workload, "chain": w["desc"], "elements": n, "inputs": w["n_inputs"],
-              "output": "scalar (f64)" if reduce else "f32 array", "partition": "replicas only",
-              "l2": f"arrays of {4 * n / 1e6:.0f} MB each, larger than L2"}
+              "output": "scalar (f64)" if reduce else ("f64 array" if f64 else "f32 array"), "partition": "replicas only",
+              "l2": f"arrays of {eb * n / 1e6:.0f} MB each, larger than L2"}
     if args.impl == "reference":
         if rank != 0:
             return 0
         gbs, dt, sample = _elementwise_cpu(w, 16 << 20, args.steps, args.warmup)
         line = {"impl": "reference", "metric": "fused_elementwise_gbps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f64" if f64 else "f32", "data": "synthetic",
+                "config": config,
                 "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample},
                 "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
@@ -263,22 +270,23 @@ def main_elementwise(args):
         dist.init_process_group("nccl", device_id=dev)
     peaks, peak_note = load_peaks()
     g = torch.Generator(device=dev).manual_seed(99 + rank)
-    arrays = [torch.rand(n, device=dev, generator=g) * 2 - 1 for _ in range(w["n_inputs"])]
-    out = None if reduce else torch.empty(n, device=dev)
+    tdt = torch.float64 if f64 else torch.float32
+    arrays = [torch.rand(n, device=dev, generator=g, dtype=tdt) * 2 - 1 for _ in range(w["n_inputs"])]
+    out = None if reduce else torch.empty(n, device=dev, dtype=tdt)
 
     # Arguments of the C-ABI call are packed once: a step is then one library call = one kernel launch, with
     # a few microseconds of host work (the kernels run 0.1-0.2 ms, so per-step Python work would show).
     lib = _capi.load()
     c_ops = _capi.pack_fused_ops(w["ops"])
     c_ptrs = (ctypes.c_void_p * len(arrays))(*[a.data_ptr() for a in arrays])
-    c_consts = (ctypes.c_float * max(len(w["consts"]), 1))(*w["consts"])
+    c_consts = ((ctypes.c_double if f64 else ctypes.c_float) * max(len(w["consts"]), 1))(*w["consts"])
+    c_fn = lib.symplex_b200_fused_elementwise_f64 if f64 else lib.symplex_b200_fused_elementwise_f32
     res = torch.zeros((), device=dev, dtype=torch.float64) if reduce else out
     stream = torch.cuda.current_stream(dev).cuda_stream
 
     def step():
-        rc = lib.symplex_b200_fused_elementwise_f32(c_ops, len(w["ops"]), c_ptrs, len(arrays), c_consts, len(w["consts"]),
-                                                    n, w["reduce_op"], None if reduce else out.data_ptr(),
-                                                    res.data_ptr() if reduce else None, stream)
+        rc = c_fn(c_ops, len(w["ops"]), c_ptrs, len(arrays), c_consts, len(w["consts"]), n, w["reduce_op"],
+                  None if reduce else out.data_ptr(), res.data_ptr() if reduce else None, stream)
         if rc != 0:
             raise SystemExit(f"fused elementwise failed: {_capi.last_error()}")
         return res
@@ -322,15 +330,15 @@ def main_elementwise(args):
     # End to end through the reference-shaped host entry point: pinned host arrays in, host array / scalar out.
     e2e = None
     if not args.no_e2e:
-        host = [torch.empty(n, dtype=torch.float32).pin_memory() for _ in range(w["n_inputs"])]
+        host = [torch.empty(n, dtype=tdt).pin_memory() for _ in range(w["n_inputs"])]
         for h, a in zip(host, arrays):
             h.copy_(a)
-        hout = None if reduce else torch.empty(n, dtype=torch.float32).pin_memory()
+        hout = None if reduce else torch.empty(n, dtype=tdt).pin_memory()
         ptrs = [h.data_ptr() for h in host]
+        host_fn = _symplex_core.simd_fused_elementwise_f64 if f64 else _symplex_core.simd_fused_elementwise_f32
 
         def host_step():
-            return _symplex_core.simd_fused_elementwise_f32(w["ops"], ptrs, w["consts"], n, w["reduce_op"],
-                                                            0 if reduce else hout.data_ptr())
+            return host_fn(w["ops"], ptrs, w["consts"], n, w["reduce_op"], 0 if reduce else hout.data_ptr())
         host_step()
         reps = max(2, min(args.steps, 5))
         if world > 1:
@@ -344,8 +352,9 @@ def main_elementwise(args):
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         dt = tt.item()
         e2e = {"value": algo_bytes * world / dt / 1e9, "unit": "GB/s", "ms_per_step": dt * 1e3,
-               "h2d_bytes_per_step": 4 * n * w["n_inputs"], "d2h_bytes_per_step": 8 if reduce else 4 * n,
-               "api": "symplex_simd_fused_elementwise_f32 (pinned host arrays, chunked copy/compute/copy pipeline)"}
+               "h2d_bytes_per_step": eb * n * w["n_inputs"], "d2h_bytes_per_step": 8 if reduce else eb * n,
+               "api": f"symplex_simd_fused_elementwise_{'f64' if f64 else 'f32'} (pinned host arrays, chunked "
+                      "copy/compute/copy pipeline)"}
         if reduce:
             e2e["result"] = hv
     if rank != 0:
@@ -363,7 +372,8 @@ def main_elementwise(args):
         cpu_baseline = {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample}
     line = {"metric": "fused_elementwise_gbps", "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "roofline": roofline,
+            "vs_baseline": None, "dtype": "f64" if f64 else "f32", "data": "synthetic", "config": config,
+            "roofline": roofline,
             "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks}
     if reduce:
         line["result"] = float(res.item())
