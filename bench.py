@@ -75,6 +75,8 @@ ELEMENTWISE_WORKLOADS = {
                                    consts=[2.0, 1.0], reduce_op=0, desc="sum(x * 2.0 + 1.0)"),
     "f3_fused_mul_add_relu_64M": dict(n=64 << 20, n_inputs=3, ops=[(2, 0, 0, 0, 1), (0, 2, 0, 0, 2), (15, 2, 1, 0, 0)],
                                       consts=[], reduce_op=255, desc="dst = relu(a * b + c)"),
+    "f3_fused_axpb_store_128M": dict(n=128 << 20, n_inputs=1, ops=[(2, 0, 0, 1, 0), (0, 2, 0, 1, 1)], consts=[2.0, 1.0],
+                                     reduce_op=255, desc="dst = x * 2.0 + 1.0"),
     # the f64 twin (what the reference's Python layer calls for float64 NumPy arrays)
     "f3_fused_axpb_f64_64M": dict(n=64 << 20, n_inputs=1, ops=[(2, 0, 0, 1, 0), (0, 2, 0, 1, 1)], consts=[2.0, 1.0],
                                   reduce_op=255, desc="dst = x * 2.0 + 1.0 (float64)", f64=True),
