@@ -165,6 +165,27 @@ void cache_tiled_sgemm_thin(const float* a, const float* b, float* c, size_t m, 
  * lhs must be RowMajor. Returns 0 or a negative SYMPLEX_ERR_* code. */
 int64_t symplex_b200_exec_tensor_matmul(const uint8_t* record, size_t record_len, void* const* slots, size_t nslots);
 
+/* ---- jit::ORCJIT::execute(name, KernelArgs&) ------------------------------------------------ */
+
+/* Same members, order and types as jit::KernelArgs (include/symplex/jit/orc_jit.h:103-114), so a C++ caller
+ * passes its KernelArgs object as is. */
+typedef struct symplex_kernel_args {
+  void* data;           /* output tensor (host) */
+  int64_t data_size;    /* bytes */
+  void** input_ptrs;    /* input tensors (host) */
+  int64_t num_inputs;
+  int64_t* input_sizes; /* bytes each; may be NULL (then sizes are not checked) */
+  int64_t M, N, K;
+  int64_t batch;
+} symplex_kernel_args;
+
+/* ORCJIT::execute(kernel_name, args) (include/symplex/jit/orc_jit.h:179) for the kernels of this path, fp32,
+ * row-major, host pointers: "matmul" (inputs A [batch][M][K], B [batch][K][N] -> data [batch][M][N]) and
+ * "fused_matmul_bias_relu" (third input bias[N]). Names are matched on these substrings, so the reference's
+ * generated names ("symplex_matmul_128x128x64", ...) work. Returns 0, or a negative SYMPLEX_ERR_* code: unknown
+ * kernel, too few inputs, or a buffer smaller than the dimensions require are SYMPLEX_ERR_INVALID. */
+int symplex_b200_execute(const char* kernel_name, const symplex_kernel_args* args);
+
 /* ---- device queries -------------------------------------------------------------------------- */
 
 /* CudaRuntime::is_available / _symplex_core.cuda_available (rust-engine/src/cuda_backend.rs:1078-1100,

@@ -53,6 +53,13 @@ class FusedOp(ctypes.Structure):
                 ("reserved", c_uint8), ("rhs_idx", c_uint16)]
 
 
+class KernelArgs(ctypes.Structure):
+    """``symplex_kernel_args`` (the reference's ``jit::KernelArgs``)."""
+    _fields_ = [("data", c_void_p), ("data_size", c_int64), ("input_ptrs", ctypes.POINTER(c_void_p)),
+                ("num_inputs", c_int64), ("input_sizes", ctypes.POINTER(c_int64)),
+                ("M", c_int64), ("N", c_int64), ("K", c_int64), ("batch", c_int64)]
+
+
 class Target(ctypes.Structure):
     """``symplex_b200_target``."""
     _fields_ = [
@@ -115,6 +122,7 @@ SIGNATURES = {
     "blas_sgemm": (None, [_F32P, _F32P, _F32P, c_size_t, c_size_t, c_size_t]),
     "cache_tiled_sgemm_thin": (None, [_F32P, _F32P, _F32P, c_size_t, c_size_t, c_size_t]),
     "symplex_b200_exec_tensor_matmul": (c_int64, [c_char_p, c_size_t, ctypes.POINTER(c_void_p), c_size_t]),
+    "symplex_b200_execute": (c_int, [c_char_p, ctypes.POINTER(KernelArgs)]),
     "symplex_cuda_available": (c_int, []),
     "symplex_cuda_device_info": (c_int, [ctypes.POINTER(DeviceInfo)]),
     "symplex_b200_launch_count": (c_uint64, []),

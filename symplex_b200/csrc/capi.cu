@@ -807,6 +807,38 @@ int64_t symplex_b200_exec_tensor_matmul(const uint8_t* rec, size_t len, void* co
   return gemm_host(&d, slots[lhs], slots[rhs], slots[dst], nullptr, nullptr);
 }
 
+int symplex_b200_execute(const char* kernel_name, const symplex_kernel_args* a) {
+  if (kernel_name == nullptr || a == nullptr) return fail(SX_ERR_INVALID, "null kernel name or arguments");
+  const bool fused = strstr(kernel_name, "fused_matmul_bias_relu") != nullptr;
+  if (!fused && strstr(kernel_name, "matmul") == nullptr)
+    return fail(SX_ERR_INVALID, "kernel '%s' is not on this path (matmul, fused_matmul_bias_relu)", kernel_name);
+  const int64_t need = fused ? 3 : 2;
+  if (a->num_inputs < need || a->input_ptrs == nullptr)
+    return fail(SX_ERR_INVALID, "kernel '%s' takes %lld inputs, got %lld", kernel_name, (long long)need,
+                (long long)a->num_inputs);
+  if (a->M < 0 || a->N < 0 || a->K < 0 || a->batch < 0) return fail(SX_ERR_INVALID, "negative dimension");
+  if (a->M > 0x7fffffffLL || a->N > 0x7fffffffLL || a->K > 0x7fffffffLL || a->batch > 0x7fffffffLL)
+    return fail(SX_ERR_INVALID, "dimension exceeds 2^31-1");
+  if (a->M == 0 || a->N == 0 || a->K == 0 || a->batch == 0) return SX_OK;
+  const int64_t want_in[3] = {a->batch * a->M * a->K * 4, a->batch * a->K * a->N * 4, a->N * 4};
+  if (a->input_sizes != nullptr)
+    for (int i = 0; i < need; ++i)
+      if (a->input_sizes[i] < want_in[i])
+        return fail(SX_ERR_INVALID, "input %d holds %lld bytes, the dimensions need %lld", i,
+                    (long long)a->input_sizes[i], (long long)want_in[i]);
+  if (a->data == nullptr || a->data_size < a->batch * a->M * a->N * 4)
+    return fail(SX_ERR_INVALID, "output holds %lld bytes, the dimensions need %lld", (long long)a->data_size,
+                (long long)(a->batch * a->M * a->N * 4));
+  for (int i = 0; i < need; ++i)
+    if (a->input_ptrs[i] == nullptr) return fail(SX_ERR_INVALID, "input %d is null", i);
+  symplex_gemm_desc d;
+  symplex_b200_gemm_desc_init(&d, a->M, a->N, a->K, SYMPLEX_DT_F32, SYMPLEX_DT_F32);
+  d.batch = (int32_t)a->batch;
+  if (fused) d.activation = SYMPLEX_ACT_RELU;
+  return gemm_host(&d, a->input_ptrs[0], a->input_ptrs[1], a->data,
+                   fused ? static_cast<const float*>(a->input_ptrs[2]) : nullptr, nullptr);
+}
+
 int symplex_cuda_available(void) {
   int n = 0;
   if (cudaGetDeviceCount(&n) != cudaSuccess || n < 1) {

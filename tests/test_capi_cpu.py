@@ -148,3 +148,36 @@ def test_struct_sizes_match_the_compiled_library(lib):
     assert list(sizes) == [ctypes.sizeof(t) for t in (_capi.GemmDesc, _capi.DeviceInfo, _capi.FusedOp, _capi.Target,
                                                       _capi.GemmPlan)]
     assert sizes[0] == 104 and sizes[2] == 8
+
+
+def _kernel_args(arrays, out, M, N, K, batch=1, sizes=True):
+    ka = _capi.KernelArgs()
+    ptrs = (ctypes.c_void_p * max(len(arrays), 1))(*[a.ctypes.data for a in arrays])
+    szs = (ctypes.c_int64 * max(len(arrays), 1))(*[a.nbytes for a in arrays])
+    ka.data, ka.data_size = out.ctypes.data, out.nbytes
+    ka.input_ptrs, ka.num_inputs = ptrs, len(arrays)
+    ka.input_sizes = szs if sizes else None
+    ka.M, ka.N, ka.K, ka.batch = M, N, K, batch
+    ka._keep = (ptrs, szs)
+    return ka
+
+
+def test_execute_kernel_args_validation(lib):
+    """ORCJIT::execute-shaped entry point: struct layout of jit::KernelArgs and argument checks (no GPU needed)."""
+    assert ctypes.sizeof(_capi.KernelArgs) == 9 * 8
+    A, B, C = np.zeros((4, 6), np.float32), np.zeros((6, 5), np.float32), np.zeros((4, 5), np.float32)
+    ok = _kernel_args([A, B], C, 4, 5, 6)
+    assert lib.symplex_b200_execute(b"conv2d_3x3", ctypes.byref(ok)) == _capi.ERR_INVALID
+    assert "not on this path" in _capi.last_error()
+    assert lib.symplex_b200_execute(b"symplex_fused_matmul_bias_relu_4x5x6", ctypes.byref(ok)) == _capi.ERR_INVALID
+    assert "takes 3 inputs" in _capi.last_error()
+    small_out = _kernel_args([A, B], np.zeros(3, np.float32), 4, 5, 6)
+    assert lib.symplex_b200_execute(b"matmul", ctypes.byref(small_out)) == _capi.ERR_INVALID
+    assert "output holds 12 bytes" in _capi.last_error()
+    small_in = _kernel_args([A[:2], B], C, 4, 5, 6)
+    assert lib.symplex_b200_execute(b"matmul", ctypes.byref(small_in)) == _capi.ERR_INVALID
+    assert "input 0 holds" in _capi.last_error()
+    assert lib.symplex_b200_execute(b"matmul", ctypes.byref(_kernel_args([A, B], C, 0, 5, 6))) == 0   # nothing to do
+    assert lib.symplex_b200_execute(b"matmul", None) == _capi.ERR_INVALID
+    if not lib.symplex_cuda_available():
+        assert lib.symplex_b200_execute(b"symplex_matmul_4x5x6", ctypes.byref(ok)) == _capi.ERR_DRIVER

@@ -617,3 +617,21 @@ def test_small_row_kernel_unaligned_output_and_odd_batch(lib, oracle):
     for z in range(batch):
         ref = np.maximum(oracle.jit_parallel_matmul(A[z], np.ascontiguousarray(Bt[z].T)) + bias, 0)
         assert rel_frobenius(got[z], ref) <= TOL_F32
+
+
+def test_execute_with_kernel_args(lib, oracle):
+    """The ORCJIT::execute-shaped entry point (jit::KernelArgs bundle, host pointers, fp32), plain and fused."""
+    from test_capi_cpu import _kernel_args
+    rng = np.random.default_rng(3)
+    batch, M, N, K = 3, 70, 96, 130
+    A = rng.uniform(-1, 1, (batch, M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (batch, K, N)).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    C = np.full((batch, M, N), np.nan, np.float32)
+    assert lib.symplex_b200_execute(b"symplex_matmul_70x96x130", ctypes.byref(_kernel_args([A, B], C, M, N, K, batch))) == 0
+    for z in range(batch):
+        assert rel_frobenius(C[z], oracle.jit_parallel_matmul(A[z], B[z])) <= TOL_F32
+    C1 = np.full((M, N), np.nan, np.float32)
+    ka = _kernel_args([A[0], B[0], bias], C1, M, N, K, 1, sizes=False)
+    assert lib.symplex_b200_execute(b"fused_matmul_bias_relu", ctypes.byref(ka)) == 0
+    assert rel_frobenius(C1, oracle.fused_matmul_bias_relu(A[0], B[0], bias)) <= TOL_F32
