@@ -181,3 +181,62 @@ def test_f64_reduction_lane_structure(oracle):
         z[:64].max() + z[64:].max()
     assert oracle.fused_elementwise([(ADD, IN, 0, CONST, 0)], [z], [0.0], reduce_op=RMIN, exact=True,
                                     dtype=np.float64) == z.min()
+
+
+def _expected_slots_and_inputs(ops, n_inputs):
+    """Independent restatement of the host compiler's bookkeeping: a value needs a slot iff it is used by an op
+    other than its immediate successor; a slot is released at the value's last use, before the using op's own
+    result is placed; slots are taken lowest-free-first is not required - only the high-water mark is compared."""
+    n = len(ops)
+    refs = []
+    used_inputs = set()
+    for i, (op, ls, li, rs, ri) in enumerate(ops):
+        r = []
+        sides = [(ls, li)] if op >= 6 else [(ls, li), (rs, ri)]
+        for src, idx in sides:
+            if src == 0 and idx < n_inputs:
+                used_inputs.add(idx)
+            elif src == 2 and idx < i:
+                r.append(idx)
+        refs.append(r)
+    last_use = [-1] * n
+    for i, r in enumerate(refs):
+        for j in r:
+            last_use[j] = i
+    live, high = set(), 0
+    for i in range(n):
+        for j in set(refs[i]):
+            if last_use[j] == i:
+                live.discard(j)
+        if last_use[i] > i + 1:
+            live.add(i)
+            high = max(high, len(live))
+    return high, len(used_inputs)
+
+
+def test_program_compiler_against_an_independent_liveness_count(lib):
+    rng = np.random.default_rng(123)
+    checked = 0
+    for trial in range(300):
+        n_ops = int(rng.integers(1, 40))
+        n_inputs = int(rng.integers(1, 6))
+        ops = []
+        for i in range(n_ops):
+            op = int(rng.integers(0, 17))
+            def operand():
+                src = int(rng.choice([0, 1, 2, 2]))
+                if src == 0:
+                    return 0, int(rng.integers(0, n_inputs + 1))          # sometimes out of range: reads 0
+                if src == 1:
+                    return 1, int(rng.integers(0, 3))
+                return 2, int(rng.integers(0, max(1, i + 1)))             # sometimes a self / forward reference
+            (ls, li), (rs, ri) = operand(), operand()
+            ops.append((op, ls, li, rs, ri))
+        want_slots, want_inputs = _expected_slots_and_inputs(ops, n_inputs)
+        rc, slots, used = _info(lib, ops, n_inputs)
+        if want_slots > 16:
+            assert rc == _capi.ERR_INVALID
+            continue
+        assert (rc, slots, used) == (0, want_slots, want_inputs), (trial, ops)
+        checked += 1
+    assert checked > 250

@@ -230,3 +230,41 @@ def test_f64_host_entry_point(torch_cuda, oracle):
     assert np.array_equal(dst, a / b - 0.5)
     s = _symplex_core.simd_fused_elementwise_f64(ops, [a.ctypes.data, b.ctypes.data], [0.5], n, SUM, 0)
     assert abs(s - np.sum(dst)) <= 1e-13 * np.abs(dst).sum()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_random_programs_bitwise(torch_cuda, oracle, dtype):
+    """Seeded random chains over the exactly rounded, overflow-safe ops (add sub mul min max neg abs relu), random
+    operand sources including long-lived intermediates, 1-6 inputs, ragged lengths: bit for bit against the oracle."""
+    import symplex_b200 as sx
+    torch = torch_cuda
+    rng = np.random.default_rng(77)
+    safe = [ADD, SUB, MUL, MIN, MAX, NEG, ABS, RELU]
+    for trial in range(40):
+        n_inputs = int(rng.integers(1, 7))
+        n_ops = int(rng.integers(1, 14))
+        n = int(rng.choice([37, 1000, 4096, 5000, 12289, 40000]))
+        consts = [float(c) for c in rng.uniform(-1.5, 1.5, 3)]
+        ops = []
+        for i in range(n_ops):
+            def operand():
+                src = int(rng.choice([0, 0, 1, 2, 2]))
+                if src == 0:
+                    return 0, int(rng.integers(0, n_inputs))
+                if src == 1:
+                    return 1, int(rng.integers(0, 3))
+                return (2, int(rng.integers(0, i))) if i > 0 else (0, 0)
+            (ls, li), (rs, ri) = operand(), operand()
+            ops.append((int(rng.choice(safe)), ls, li, rs, ri))
+        arrays = [rng.uniform(-1.2, 1.2, n).astype(dtype) for _ in range(n_inputs)]
+        want = oracle.fused_elementwise(ops, arrays, consts, dtype=dtype)
+        got = sx.fused_elementwise(ops, [torch.from_numpy(a).cuda() for a in arrays], consts).cpu().numpy()
+        bits = np.uint32 if dtype == np.float32 else np.uint64
+        assert np.array_equal(got.view(bits), want.view(bits)), (trial, ops)
+        ref_sum = oracle.fused_elementwise(ops, arrays, consts, reduce_op=SUM, dtype=dtype)
+        got_sum = float(sx.fused_elementwise(ops, [torch.from_numpy(a).cuda() for a in arrays], consts,
+                                             reduce_op=SUM).item())
+        scale = float(np.abs(want.astype(np.float64)).sum()) + 1e-30
+        assert abs(got_sum - float(want.astype(np.float64).sum())) <= (1e-6 if dtype == np.float32 else 1e-13) * scale
+        assert abs(got_sum - ref_sum) <= 2e-5 * scale
+    sx.sync_status()
