@@ -233,20 +233,23 @@ static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_
     return {KK_F32_SPLIT, wide ? 128 : 64};
   }
   const int bn = pick_bn(p.M, p.N, p.batch, num_sms, forced);
-  // Tile shape by how much work there is: CTA pairs once 256x256 pair tiles give every pair of SMs something to
-  // do, single-CTA tiles (down to 128x64) otherwise. Between the two pair shapes the cheaper one by a wave count:
-  // waves x tile area / measured tensor-pipe utilisation (512x256: 0.875, least L2 -> SM traffic per flop;
-  // 256x256: 0.80). 4096^3: 2 waves of 512x256 beat 4 waves of 256x256 by 6 % (measured).
+  // Tile shape by estimated cost = waves x (output area one SM computes per tile) / tensor-pipe utilisation of the
+  // shape, measured on large problems: single-CTA tiles 128 x 256 / 128 / 64 reach 0.70 / 0.56 / 0.40, 256x256 pair
+  // tiles 0.80, 512x256 pair tiles 0.875 (least L2 -> SM traffic per flop). Examples (measured): 4096^3 runs 2 waves
+  // of 512x256 (108 us) rather than 4 of 256x256 (116 us); 2048^3 one wave of 256x256 pairs (19.6 us) rather than
+  // two of 128x128 (28.4 us).
   int mode = 0;  // 0 single CTA, 1 pair 256x256, 2 pair 512x256
-  if (forced == 0 && bn == 256 && p.M > 128) {
+  if (forced == 0 && p.M > 128 && p.N >= 256) {
     const long long pairs = num_sms / 2;
     const long long nt = (p.N + 255) / 256;
+    const long long t0 = ((p.M + 127) / 128) * ((p.N + bn - 1) / bn) * p.batch;
     const long long t256 = ((p.M + 255) / 256) * nt * p.batch, t512 = ((p.M + 511) / 512) * nt * p.batch;
-    if (t256 >= pairs) {
-      const double cost256 = (double)((t256 + pairs - 1) / pairs) * 1.0 / 0.80;
-      const double cost512 = (double)((t512 + pairs - 1) / pairs) * 2.0 / 0.875;
-      mode = cost512 <= cost256 ? 2 : 1;
-    }
+    const double eff0 = bn == 256 ? 0.70 : bn == 128 ? 0.56 : 0.40;
+    const double cost0 = (double)((t0 + num_sms - 1) / num_sms) * (128.0 * bn) / eff0;
+    const double cost256 = (double)((t256 + pairs - 1) / pairs) * (128.0 * 256.0) / 0.80;
+    const double cost512 = p.M > 256 ? (double)((t512 + pairs - 1) / pairs) * (256.0 * 256.0) / 0.875 : 1e300;
+    if (cost512 <= cost256 && cost512 <= cost0) mode = 2;
+    else if (cost256 <= cost0) mode = 1;
   }
   if (const char* e = getenv("SYMPLEX_B200_PAIR")) mode = atoi(e);
   if (n_peers > 0 && mode == 0) mode = 1;  // only the pair kernels carry the peer-store epilogue

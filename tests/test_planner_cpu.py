@@ -105,7 +105,8 @@ def test_plan_follows_the_dispatch_rules(lib):
     assert planner.compile_matmul(1024, 1024, 512, dtype="fp32").cluster_size == 1
     # mid-size bf16: pair tiles of 256x256 when the taller tile would only add padding or a wave
     assert planner.compile_matmul(256, 32768, 512, dtype="bf16").optimal_tile == (256, 256, 64)
-    assert planner.compile_matmul(1024, 4096, 512, dtype="bf16").kernel_name == "gemm_tc_kernel"
+    assert planner.compile_matmul(2048, 2048, 2048, dtype="bf16").optimal_tile == (256, 256, 64)   # 1 wave, not 2 of 128x128
+    assert planner.compile_matmul(512, 512, 512, dtype="bf16").kernel_name == "gemm_tc_kernel"      # 32 small tiles > 4 pairs
     # fewer SMs -> smaller grid
     assert planner.compile_matmul(8192, 8192, 8192, dtype="bf16", num_sms=64).grid_dims[0] == 64
 
