@@ -183,17 +183,25 @@ def gemm(A, B, *, bias=None, residual=None, activation=None, alpha=1.0, beta=0.0
     if K == 0:
         raise ValueError("K == 0 is not supported")
     s = stream if stream is not None else torch.cuda.current_stream(A.device).cuda_stream
-    with torch.cuda.device(A.device):
+
+    def launch():
         if peer_outputs:
             arr = (ctypes.c_void_p * len(peer_outputs))(*[int(x) for x in peer_outputs])
-            rc = _capi.load().symplex_b200_gemm_peers(ctypes.byref(d), A.data_ptr(), B.data_ptr(), out.data_ptr(),
-                                                      bias.data_ptr() if bias is not None else None,
-                                                      residual.data_ptr() if residual is not None else None,
-                                                      arr, len(peer_outputs), s)
-        else:
-            rc = _capi.load().symplex_b200_gemm(ctypes.byref(d), A.data_ptr(), B.data_ptr(), out.data_ptr(),
-                                                bias.data_ptr() if bias is not None else None,
-                                                residual.data_ptr() if residual is not None else None, s)
+            return _capi.load().symplex_b200_gemm_peers(ctypes.byref(d), A.data_ptr(), B.data_ptr(), out.data_ptr(),
+                                                        bias.data_ptr() if bias is not None else None,
+                                                        residual.data_ptr() if residual is not None else None,
+                                                        arr, len(peer_outputs), s)
+        return _capi.load().symplex_b200_gemm(ctypes.byref(d), A.data_ptr(), B.data_ptr(), out.data_ptr(),
+                                              bias.data_ptr() if bias is not None else None,
+                                              residual.data_ptr() if residual is not None else None, s)
+
+    # Switching the current device costs several microseconds per call - as much as a small kernel - so it is
+    # only done when the operands live on another device than the current one.
+    if A.device.index is None or A.device.index == torch.cuda.current_device():
+        rc = launch()
+    else:
+        with torch.cuda.device(A.device):
+            rc = launch()
     _capi.check(rc)
     return out
 
