@@ -126,6 +126,9 @@ def gemm_host(desc: GemmDesc, A_ptr: int, B_ptr: int, C_ptr: int, bias_ptr: int 
     _capi.check(_capi.load().symplex_b200_gemm_host(ctypes.byref(desc), A_ptr, B_ptr, C_ptr, bias_ptr, residual_ptr))
 
 
+_gemm_descs: dict = {}
+
+
 def gemm(A, B, *, bias=None, residual=None, activation=None, alpha=1.0, beta=0.0, out=None, out_dtype=None,
          b_layout=ROW_MAJOR, tile_n=0, stream=None, peer_outputs=None):
     """Fused GEMM on CUDA tensors: ``act(alpha * A @ B + beta * residual + bias)``.
@@ -176,8 +179,15 @@ def gemm(A, B, *, bias=None, residual=None, activation=None, alpha=1.0, beta=0.0
         if residual.dtype != out_t or tuple(residual.shape) != shape:
             raise ValueError("residual must match the output's dtype and shape")
         residual = residual.contiguous()
-    d = make_desc(M, N, K, in_dt, DT_F32 if out_t == torch.float32 else DT_BF16, batch=batch, b_layout=b_layout,
-                  alpha=alpha, beta=beta, activation=activation, tile_n=tile_n)
+    # Descriptors are only read by the library, so one per distinct problem is built and kept.
+    key = (M, N, K, in_dt, out_t, batch, b_layout, alpha, beta, activation, tile_n)
+    d = _gemm_descs.get(key)
+    if d is None:
+        if len(_gemm_descs) >= 512:
+            _gemm_descs.clear()
+        d = _gemm_descs[key] = make_desc(M, N, K, in_dt, DT_F32 if out_t == torch.float32 else DT_BF16, batch=batch,
+                                         b_layout=b_layout, alpha=alpha, beta=beta, activation=activation,
+                                         tile_n=tile_n)
     if M == 0 or N == 0 or batch == 0:
         return out
     if K == 0:

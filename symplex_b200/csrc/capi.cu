@@ -62,6 +62,25 @@ static EncodeTiledFn encode_fn() {
 
 int encode_tensor_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, const uint64_t dims[3],
                          const uint64_t strides_bytes[2], const uint32_t box[3], bool swizzle128) {
+  // A tensor map is a pure function of the address and geometry it is encoded from, and callers in a loop pass
+  // the same few operands again and again, so the last encodes of this thread are kept (direct-mapped, no lock).
+  struct Cached {
+    uint64_t key[9];
+    CUtensorMap map;
+    bool valid;
+  };
+  constexpr int CACHE_SLOTS = 32;
+  static thread_local Cached cache[CACHE_SLOTS] = {};
+  const uint64_t key[9] = {reinterpret_cast<uint64_t>(base), dims[0], dims[1], dims[2], strides_bytes[0],
+                           strides_bytes[1], (uint64_t(box[0]) << 32) | box[1],
+                           (uint64_t(box[2]) << 32) | (uint64_t(dt) << 1) | (swizzle128 ? 1u : 0u), 0};
+  uint64_t h = 0x9e3779b97f4a7c15ull;
+  for (int i = 0; i < 8; ++i) h = (h ^ key[i]) * 0xff51afd7ed558ccdull;
+  Cached& slot = cache[(h >> 40) % CACHE_SLOTS];
+  if (slot.valid && memcmp(slot.key, key, sizeof(key)) == 0) {
+    *out = slot.map;
+    return SX_OK;
+  }
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(SX_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t d[3] = {dims[0], dims[1], dims[2]};
@@ -74,6 +93,9 @@ int encode_tensor_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* b
     return fail(SX_ERR_INVALID, "cuTensorMapEncodeTiled failed (%d): dims %llu,%llu,%llu strides %llu,%llu box %u,%u,%u",
                 (int)r, (unsigned long long)d[0], (unsigned long long)d[1], (unsigned long long)d[2],
                 (unsigned long long)s[0], (unsigned long long)s[1], b[0], b[1], b[2]);
+  memcpy(slot.key, key, sizeof(key));
+  slot.map = *out;
+  slot.valid = true;
   return SX_OK;
 }
 
