@@ -157,20 +157,46 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU reference timing
+def _host_threads():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def _load_cpu_reference():
-    """(callable(A, B, C, M, N, K), kind, cores, name): the reference's CPU matmul for this path."""
+    """(callable(A, B, C, M, N, K), kind, cores, name): the reference's CPU matmul for this path.
+
+    Rows of A are split into one contiguous block per host thread and every block runs the reference's kernel
+    on its own rows of C, which is how the reference's rayon entry points spread a matmul over the cores
+    (rust-engine/src/x86_emitter.rs:1877-1897 `parallel_matmul`, :1845-1875 `parallel_cache_blocked_matmul`);
+    the per-element arithmetic of a row does not depend on the split.
+    """
+    from concurrent.futures import ThreadPoolExecutor
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     from oracle_loader import load_oracle, load_ref_kernels
+    cores = _host_threads()
     ref = load_ref_kernels()
     if ref is not None:
+        pool = ThreadPoolExecutor(max_workers=cores) if cores > 1 else None
+
+        def rows(A, B, C, r0, r1, N, K):
+            ref.symplex_matmul_f32(A.ctypes.data + r0 * K * 4, B.ctypes.data, C.ctypes.data + r0 * N * 4, r1 - r0, N, K)
+
         def run(A, B, C, M, N, K):
-            ref.symplex_matmul_f32(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K)
-        return run, "reference", 1, "kernels/matmul.c:symplex_matmul_f32 compiled unchanged (single-threaded code)"
+            parts = min(cores, M)
+            if pool is None or parts <= 1:
+                return rows(A, B, C, 0, M, N, K)
+            cuts = [M * i // parts for i in range(parts + 1)]
+            for f in [pool.submit(rows, A, B, C, cuts[i], cuts[i + 1], N, K) for i in range(parts)]:
+                f.result()
+        return run, "reference", cores, (f"kernels/matmul.c:symplex_matmul_f32 compiled unchanged, one row block per "
+                                         f"thread on {cores} threads (the reference's rayon row split)")
     orc = load_oracle()
 
     def run(A, B, C, M, N, K):
-        orc.lib.oracle_jit_parallel_matmul(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K, 1)
-    return run, "port", 1, "oracle port of jit_parallel_matmul (the reference's AVX-512 JIT path is single-threaded)"
+        orc.lib.oracle_jit_parallel_matmul(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K, cores)
+    return run, "port", cores, f"oracle port of jit_parallel_matmul, row blocks on {cores} threads"
 
 
 def cpu_sample(w, rows):
@@ -204,7 +230,7 @@ def time_cpu_reference(w, rows, steps, warmup):
 
 def cpu_rows_for(w, seconds=3.0, gflops_guess=5.0):
     per_row = 2.0 * w["N"] * w["K"]
-    rows = int(seconds * gflops_guess * 1e9 / per_row)
+    rows = int(seconds * gflops_guess * 1e9 / per_row) * _host_threads()  # every thread gets the same share
     return max(1, min(w["M"], rows))
 
 
@@ -416,7 +442,8 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
-        rows = cpu_rows_for(w)
+        # a step is a row sample worth up to ~3 s per thread, shrunk so that all steps end within about a minute
+        rows = cpu_rows_for(w, seconds=max(0.25, min(3.0, 60.0 / (args.steps + max(1, args.warmup)))))
         tflops, dt, kind, cores, sample = time_cpu_reference(w, rows, args.steps, max(1, args.warmup))
         line = {"impl": "reference", "metric": "gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
