@@ -164,6 +164,12 @@ def _host_threads():
         return max(1, os.cpu_count() or 1)
 
 
+def _parts(cores, M, N, K):
+    """Row blocks a CPU matmul is split into: one per thread, but none smaller than ~20 MFLOP (a hand-off to a
+    thread costs more than a 64^3 product)."""
+    return int(max(1, min(cores, M, 2.0 * M * N * K // 2e7)))
+
+
 def _load_cpu_reference():
     """(callable(A, B, C, M, N, K), kind, cores, name): the reference's CPU matmul for this path.
 
@@ -184,19 +190,20 @@ def _load_cpu_reference():
             ref.symplex_matmul_f32(A.ctypes.data + r0 * K * 4, B.ctypes.data, C.ctypes.data + r0 * N * 4, r1 - r0, N, K)
 
         def run(A, B, C, M, N, K):
-            parts = min(cores, M)
+            parts = _parts(cores, M, N, K)
             if pool is None or parts <= 1:
                 return rows(A, B, C, 0, M, N, K)
             cuts = [M * i // parts for i in range(parts + 1)]
             for f in [pool.submit(rows, A, B, C, cuts[i], cuts[i + 1], N, K) for i in range(parts)]:
                 f.result()
         return run, "reference", cores, (f"kernels/matmul.c:symplex_matmul_f32 compiled unchanged, one row block per "
-                                         f"thread on {cores} threads (the reference's rayon row split)")
+                                         f"thread on up to {cores} threads (the reference's rayon row split)")
     orc = load_oracle()
 
     def run(A, B, C, M, N, K):
-        orc.lib.oracle_jit_parallel_matmul(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K, cores)
-    return run, "port", cores, f"oracle port of jit_parallel_matmul, row blocks on {cores} threads"
+        orc.lib.oracle_jit_parallel_matmul(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K,
+                                           _parts(cores, M, N, K))
+    return run, "port", cores, f"oracle port of jit_parallel_matmul, row blocks on up to {cores} threads"
 
 
 def cpu_sample(w, rows):
@@ -213,25 +220,35 @@ def cpu_sample(w, rows):
     return A, B, np.zeros((M, w["N"]), np.float32)
 
 
-def time_cpu_reference(w, rows, steps, warmup):
+def time_cpu_reference(w, seconds, steps, warmup):
+    """Time the reference's CPU matmul on a row sample of workload `w` sized so that one step takes about `seconds`.
+
+    The sample is sized from a calibration pass (two rows per thread) run on this host: the kernel streams all of B
+    for every row of A, so its rate with every core busy depends on the box's memory system, not on a per-core guess.
+    """
+    import numpy as np
     run, kind, cores, name = _load_cpu_reference()
-    A, B, C = cpu_sample(w, rows)
-    M = A.shape[0]
+    N, K = w["N"], w["K"]
+    rows0 = min(w["M"], max(2 * cores, 8))
+    A, B, C = cpu_sample(w, w["M"] if w["M"] * K <= (1 << 24) else max(rows0, min(w["M"], 64 * cores)))
+    run(A, B, C, rows0, N, K)  # pages in B and the code
+    t0 = time.perf_counter()
+    run(A, B, C, rows0, N, K)
+    rate = rows0 / max(time.perf_counter() - t0, 1e-6)  # rows per second
+    M = int(max(min(cores, w["M"]), min(w["M"], rate * seconds)))
+    if M > A.shape[0]:  # more rows than were drawn: repeat them (the kernel's speed does not depend on the values)
+        reps = (M + A.shape[0] - 1) // A.shape[0]
+        A = np.ascontiguousarray(np.tile(A, (reps, 1))[:M])
+        C = np.zeros((M, N), np.float32)
     for _ in range(warmup):
-        run(A, B, C, M, w["N"], w["K"])
+        run(A, B, C, M, N, K)
     t0 = time.perf_counter()
     for _ in range(steps):
-        run(A, B, C, M, w["N"], w["K"])
+        run(A, B, C, M, N, K)
     dt = (time.perf_counter() - t0) / max(1, steps)
-    tflops = 2.0 * M * w["N"] * w["K"] / dt / 1e12
+    tflops = 2.0 * M * N * K / dt / 1e12
     sample = f"{M} of {w['M']} rows of A (all of B), one problem of {w['batch']}; {name}"
-    return tflops, dt, kind, cores, sample
-
-
-def cpu_rows_for(w, seconds=3.0, gflops_guess=5.0):
-    per_row = 2.0 * w["N"] * w["K"]
-    rows = int(seconds * gflops_guess * 1e9 / per_row) * _host_threads()  # every thread gets the same share
-    return max(1, min(w["M"], rows))
+    return tflops, dt, kind, _parts(cores, M, N, K), sample
 
 
 # ----------------------------------------------------------------------------- main
@@ -442,9 +459,9 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
-        # a step is a row sample worth up to ~3 s per thread, shrunk so that all steps end within about a minute
-        rows = cpu_rows_for(w, seconds=max(0.25, min(3.0, 60.0 / (args.steps + max(1, args.warmup)))))
-        tflops, dt, kind, cores, sample = time_cpu_reference(w, rows, args.steps, max(1, args.warmup))
+        # a step is a row sample of up to ~3 s (sized by a calibration pass), shrunk so that all steps end within about a minute
+        seconds = max(0.25, min(3.0, 60.0 / (args.steps + max(1, args.warmup))))
+        tflops, dt, kind, cores, sample = time_cpu_reference(w, seconds, args.steps, max(1, args.warmup))
         line = {"impl": "reference", "metric": "gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
                 "scaling": "strong" if w["sharded"] else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -639,7 +656,7 @@ def main():
 
     cpu_baseline = None
     if not args.no_cpu_baseline and world == 1:
-        tfl, dt, kind, cores, sample = time_cpu_reference(w, cpu_rows_for(w, seconds=4.0), steps=3, warmup=1)
+        tfl, dt, kind, cores, sample = time_cpu_reference(w, 4.0, steps=3, warmup=1)
         cpu_baseline = {"value": tfl, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample}
 
     line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
