@@ -1,6 +1,5 @@
 """Test configuration: the ``gpu`` marker, and loaders for the CPU oracle (the checker, never the product)."""
 import os
-import subprocess
 import sys
 
 import pytest

@@ -4,7 +4,6 @@ import ctypes
 import json
 import struct
 
-import numpy as np
 import pytest
 
 from symplex_b200 import _capi, fusion

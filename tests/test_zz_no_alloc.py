@@ -8,7 +8,6 @@ the first would show - and compares each result with the regular pooled entry po
 """
 import ctypes
 
-import numpy as np
 import pytest
 import torch
 
