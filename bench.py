@@ -585,6 +585,27 @@ def main():
         config["launch"] = f"one CUDA graph of {args.steps} steps (eager launches are host-bound at this size)"
         sx.sync_status()
 
+    # Spread of single steps (outside the timed region above, which stays K back-to-back steps): one event between
+    # consecutive steps; for graph-launched workloads one event between consecutive replays of the K-step graph.
+    # One GPU only: these steps directly follow the timed ones, so on a power-capped board they show the sustained
+    # rate (the clock has settled by then) next to the burst the first K steps may have run at.
+    step_spread = None
+    if world == 1:
+        nspread = max(3, min(args.steps, 20))
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(nspread + 1)]
+        marks[0].record()
+        for i in range(nspread):
+            if "launch" in config:
+                graph.replay()
+            else:
+                step()
+            marks[i + 1].record()
+        torch.cuda.synchronize()
+        per = [marks[i].elapsed_time(marks[i + 1]) / (args.steps if "launch" in config else 1)
+               for i in range(nspread)]
+        step_spread = {"min": min(per), "median": statistics.median(per), "max": max(per), "n": nspread}
+        sx.sync_status()
+
     # per-launch duration of the GEMM kernel alone (no collective), CUDA events on the launching stream
     k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if sharded:
@@ -665,7 +686,7 @@ def main():
             "dtype": "bf16" if w["dt"] == "bf16" else "f32 (3xTF32 on tensor cores)", "data": "synthetic",
             "config": config, "frac_of_bf16_peak": value / (args.gpus * float(peaks["bf16_tflops"])),
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
-            "clocks": clocks}
+            "clocks": clocks, "step_ms": step_spread}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
