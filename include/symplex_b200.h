@@ -32,6 +32,7 @@ extern "C" {
 
 /* Element types: values of the reference's ScalarType (rust-engine/src/types.rs:110-116). */
 #define SYMPLEX_DT_F32 9
+#define SYMPLEX_DT_F64 10 /* TensorMatMul records and the f64 thin ABI only; not an in_dtype of symplex_gemm_desc */
 #define SYMPLEX_DT_BF16 11
 
 /* Matrix layouts: values of the reference's MatrixLayout (rust-engine/src/types.rs:177-181). */
@@ -95,6 +96,71 @@ int symplex_b200_gemm(const symplex_gemm_desc* d, const void* A, const void* B, 
 int symplex_b200_gemm_peers(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
                             const void* residual, const void* const* peer_C, int32_t n_peers, void* stream);
 
+/* ---- row-sharded GEMM across the GPUs of one box --------------------------------------------- */
+
+/* What one rank knows about the group. The reference only plans this computation
+ * (ShardingAnalyzer::analyze_matmul, include/symplex/distributed/sharding.h:107-112; CollectiveOp::ALL_GATHER and
+ * NCCLBridge::emit_nccl_ops, include/symplex/distributed/nccl_bridge.h:19-26,91-98, emit the collective as text);
+ * this is the handle of the executed counterpart. The host creates, once, on every rank: a full [M, N] C buffer and
+ * a flag block of SYMPLEX_B200_COMM_FLAG_WORDS zeroed int32, both in memory that the other ranks can map (CUDA IPC,
+ * cuMemExportToShareableHandle, or torch symmetric memory), and fills in the addresses at which THIS process sees
+ * every rank's buffers (index = rank; its own entry is its local memory). c_multicast is the address of a multicast
+ * mapping of the C buffers (cuMulticastCreate / cuMulticastBindMem), or NULL. Zero the flags and epoch before the
+ * first call and let every rank finish that (a host barrier) before any rank calls symplex_b200_sharded_gemm. */
+#define SYMPLEX_B200_MAX_RANKS 8
+#define SYMPLEX_B200_COMM_FLAG_WORDS 16
+typedef struct symplex_b200_comm {
+  int32_t rank, world;
+  void* c_base[SYMPLEX_B200_MAX_RANKS];
+  void* c_multicast;
+  int32_t* flags[SYMPLEX_B200_MAX_RANKS];
+  int64_t epoch;         /* collective calls made so far; maintained by the library */
+  int32_t wait_limit_ms; /* bound of every device-side wait for a peer; 0 = 2000 */
+  int32_t reserved;
+} symplex_b200_comm;
+
+/* How C travels. UNICAST: forwarder warps of the GEMM kernel copy each finished tile from the local C to every
+ * peer's C with 16-byte stores over NVLink. MULTICAST: the same warps store each tile once to c_multicast and the
+ * NVSwitch delivers it to every GPU (multimem.st). EPILOGUE_TMA: the epilogue warps forward their own blocks by TMA
+ * (the first design; kept for comparison) - this mode does NOT order the ranks, the caller must (all ranks idle
+ * before the call, all ranks done before C is read). AUTO picks UNICAST. */
+#define SYMPLEX_XCHG_AUTO 0
+#define SYMPLEX_XCHG_UNICAST 1
+#define SYMPLEX_XCHG_MULTICAST 2
+#define SYMPLEX_XCHG_EPILOGUE_TMA 3
+
+/* C = act(alpha * A.B + bias) with the rows of A and C split evenly over comm->world ranks (rank r owns rows
+ * [r * M / world, (r + 1) * M / world)), B replicated, and C all-gathered: when the kernel this call enqueues on
+ * `stream` has finished, comm->c_base[rank] holds the whole [M, N] product. One kernel per rank does the GEMM and
+ * the exchange; the ranks order themselves with flags in each other's memory (UNICAST / MULTICAST): a rank's C is
+ * not overwritten before it has entered the call, and the kernel does not end before every peer's tiles have
+ * landed. d describes the GLOBAL problem (d->M = all rows; bf16 inputs for world > 1; batch 1; dense C). Collective:
+ * every rank calls it, the same number of times, in the same order. A peer that does not show up within the wait
+ * limit makes the kernel give up: symplex_b200_sync_status then returns SYMPLEX_ERR_TIMEOUT on the ranks that
+ * waited, and C is not valid. */
+int symplex_b200_sharded_gemm(const symplex_gemm_desc* d, const void* A_local, const void* B, const float* bias,
+                              symplex_b200_comm* comm, int32_t exchange, void* stream);
+
+/* ShardingAnalyzer::analyze_matmul -> ShardPlan (include/symplex/distributed/sharding.h:65-112) as plain data, for
+ * the row split this library executes: A SHARD_DIM_0, B REPLICATE, C SHARD_DIM_0 followed by an all-gather.
+ * Strategy codes are the reference's ShardingStrategy values (sharding.h:18-24). Returns SYMPLEX_ERR_INVALID if M
+ * does not split evenly. Host only. */
+typedef struct symplex_shard_spec {
+  int32_t strategy;         /* 0 REPLICATE, 1 SHARD_DIM_0, ... */
+  int32_t shard_dim;        /* -1 if replicated */
+  int64_t original_shape[2], local_shape[2];
+} symplex_shard_spec;
+typedef struct symplex_shard_plan {
+  symplex_shard_spec a, b, c;
+  int32_t n_all_gather_ops; /* 1 if world > 1: all_gather(C, dim 0) */
+  int32_t n_all_reduce_ops, n_all_to_all_ops; /* 0 */
+  int32_t world;
+  int64_t total_communication_bytes; /* received by all devices together: world * (world - 1) * M/world * N * bytes */
+  int64_t peak_memory_per_device;    /* local A + B + full C */
+} symplex_shard_plan;
+int symplex_b200_analyze_matmul(int64_t M, int64_t N, int64_t K, int32_t world, int32_t bytes_per_element,
+                                symplex_shard_plan* out);
+
 /* Same, with caller-provided scratch of at least symplex_b200_gemm_workspace_bytes(d) bytes
  * (256-byte aligned device memory); never allocates. */
 int symplex_b200_gemm_ws(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
@@ -110,14 +176,44 @@ int symplex_b200_gemm_ws(const symplex_gemm_desc* d, const void* A, const void* 
  * 1024 x 1024 x 1020 fits), else SYMPLEX_ERR_INVALID.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that call
  * before starting any stream capture. All calls share the one array: calls whose GPU work may overlap race
- * on it and must be serialised by the caller. Nothing needs clearing between calls. */
+ * on it and must be serialised by the caller. Nothing needs clearing between calls. "No allocating routine" is
+ * about this library's code: the first CUDA call of a process on a device creates its context and loads the
+ * library's kernels, and that is also when the array becomes resident. A device-side failure (a bounded wait
+ * that ran out) is reported by symplex_b200_noalloc_status, below - not by symplex_b200_sync_status. */
 #define SYMPLEX_B200_NOALLOC_SCRATCH_BYTES (16 * 1024 * 1024)
 int symplex_b200_sgemm_noalloc(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                                void* stream);
 
+/* Status of the symplex_b200_sgemm_noalloc calls since the last call of this function on the current device:
+ * synchronises `stream`, returns 0 or SYMPLEX_ERR_TIMEOUT (a bounded device-side wait ran out; C of those calls
+ * is not valid) and clears the word. No counterpart in the reference. Like the entry point it serves, it calls no
+ * allocating routine: the status word is a second small variable inside the library image, read with a plain
+ * device-to-host copy into a stack variable. (symplex_b200_sync_status reports the other entry points' status word
+ * and may allocate on its first call; it does not see a no-alloc failure.) */
+int symplex_b200_noalloc_status(void* stream);
+
 /* Synchronise `stream` and return the device-side status of the launches since the last call:
  * 0, SYMPLEX_ERR_TIMEOUT or SYMPLEX_ERR_EXEC. */
 int symplex_b200_sync_status(void* stream);
+
+/* Self-test of the kernels' unwinding: runs one 128 x 64 x 128 bf16 product (A [128,128], B [128,64] row-major,
+ * C [128,64] bf16, device pointers) in which the TMA producer deliberately leaves out the last k-block and every
+ * wait is bounded by limit_ms (1..1000). The MMA thread's wait for that block runs out, every role of the CTA
+ * unwinds (copies drained, tensor memory freed) and the kernel returns normally with its status word set.
+ * Synchronises, clears the status word and returns what it found: SYMPLEX_ERR_TIMEOUT is the expected result,
+ * 0 means the wait did not run out. Nothing traps and nothing spins without a bound; the next call on the device
+ * works as usual. No counterpart in the reference. */
+int symplex_b200_selftest_wait_timeout(const void* A, const void* B, void* C, int32_t limit_ms, void* stream);
+
+/* Process-wide tuning overrides, for tests and experiments: "tile_n" (0 auto, 64/128/256), "pair_mode" (-1 auto,
+ * 0 single-CTA tiles, 1 256x256 CTA pairs, 2 512x256 CTA pairs), "f32_fused" (-1 auto, 0, 1), "f32_split_k" (0 auto,
+ * 1, 2, 4), "f32_tile_rows" (0 auto, 128), "group_m" (0 auto), "tma_store" (1, 0), "pipeline_mb" (96),
+ * "pipeline" (1, 0), "wait_limit_ms" (2000), "trace" (0, 1: one line per GEMM dispatch on stderr). Only "tile_n"
+ * and "trace" can also be preset from the environment (SYMPLEX_B200_TILE, SYMPLEX_B200_TRACE, read once at load);
+ * the pipeline depth is a compile-time constant of each kernel. set returns SYMPLEX_ERR_INVALID for an unknown
+ * name; get returns INT64_MIN for one. */
+int symplex_b200_set_option(const char* name, int64_t value);
+int64_t symplex_b200_get_option(const char* name);
 
 /* Message for the most recent failure on the calling thread (static storage; never NULL). */
 const char* symplex_b200_last_error(void);
@@ -156,13 +252,24 @@ void symplex_matmul_tiled_f32(const float* A, const float* B, float* C, int64_t 
  * (rust-engine/src/phase3_jit.rs:431-445,660-669): alpha 1, beta 0, natural leading dimensions. */
 void blas_sgemm(const float* a, const float* b, float* c, size_t m, size_t n, size_t k);
 void cache_tiled_sgemm_thin(const float* a, const float* b, float* c, size_t m, size_t n, size_t k);
+/* Their f64 twins (rust-engine/src/phase3_jit.rs:449-461,676-685), which TensorMatMul traces with element type F64
+ * call (:13024-13118): C = A.B in double precision, host pointers, row-major. Computed by a CUDA-core kernel in
+ * the summation order of the reference's cache_tiled_dgemm (:578-650: per block of 128 consecutive k a chain of
+ * separately rounded multiply and add from 0, blocks added to C in increasing k), so the results are bit-identical
+ * to that function's (a CBLAS build of the reference, which rounds differently, agrees to ~1e-15). */
+void blas_dgemm(const double* a, const double* b, double* c, size_t m, size_t n, size_t k);
+void cache_tiled_dgemm_thin(const double* a, const double* b, double* c, size_t m, size_t n, size_t k);
+/* The same product on device pointers, asynchronous on `stream`; lda / ldb / ldc in elements (0 = packed). */
+int symplex_b200_dgemm(const double* A, const double* B, double* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                       int64_t ldb, int64_t ldc, void* stream);
 
 /* Execute one serialized Instr::TensorMatMul record (rust-engine/src/types.rs:407-417,646-657,884-904: opcode
  * 0xA2, dst/lhs/rhs slot u16, m/n/k u64, element_ty, lhs_layout, rhs_layout; 34 bytes little endian) against an
  * array of host pointers indexed by slot - what the reference's JIT lowers to a blas_sgemm call
  * (rust-engine/src/phase3_jit.rs:13024-13118). Unlike the reference, which parses the layout bytes and then
- * ignores them, rhs_layout is honoured (RowMajor: [K,N]; ColMajor: stored [N,K]); F32 and BF16 element types;
- * lhs must be RowMajor. Returns 0 or a negative SYMPLEX_ERR_* code. */
+ * ignores them, rhs_layout is honoured (RowMajor: [K,N]; ColMajor: stored [N,K]); F32 and BF16 element types, and
+ * F64 (row-major rhs only; the product blas_dgemm computes); lhs must be RowMajor. Returns 0 or a negative
+ * SYMPLEX_ERR_* code. */
 int64_t symplex_b200_exec_tensor_matmul(const uint8_t* record, size_t record_len, void* const* slots, size_t nslots);
 
 /* ---- jit::ORCJIT::execute(name, KernelArgs&) ------------------------------------------------ */
@@ -210,6 +317,9 @@ int symplex_cuda_device_info(symplex_device_info* out);
  * symplex_fused_op, symplex_b200_target, symplex_gemm_plan}. Lets a binding written in another language check
  * its own struct definitions at load time. */
 void symplex_b200_abi_sizes(int32_t out[5]);
+/* The same list continued: ..., symplex_b200_comm, symplex_shard_plan, symplex_generated_kernel, symplex_fusion_op,
+ * symplex_kernel_args. Writes the first n entries to out (may be NULL) and returns how many there are. */
+int32_t symplex_b200_abi_sizes_ext(int32_t* out, int32_t n);
 
 /* Kernels launched by this library on the calling process since load (all threads). */
 uint64_t symplex_b200_launch_count(void);
@@ -312,6 +422,56 @@ int symplex_b200_hardware_target(symplex_b200_target* out);
  * prefetch distance. Null output pointers are skipped. */
 void symplex_b200_micro_kernel_config(uint8_t target, size_t element_bytes, size_t* out_tile_m, size_t* out_tile_n,
                                       size_t* out_tile_k, size_t* out_acc_regs, size_t* out_prefetch_dist);
+/* The same function under the reference's own symbol name and argument list
+ * (include/symplex/polyhedral/rust_bridge.h:221-229, rust-engine/src/ffi.rs:695-717), so C++ code that declares
+ * it extern "C" links against this library unchanged. */
+void poly_get_micro_kernel_config(uint8_t target, size_t element_bytes, size_t* out_tile_m, size_t* out_tile_n,
+                                  size_t* out_tile_k, size_t* out_acc_regs, size_t* out_prefetch_dist);
+
+/* codegen::CodeGenerator::generate_matmul(M, N, K, TileConfig, depth) -> GeneratedKernel
+ * (include/symplex/codegen/code_generator.h:19-45) for a library of precompiled kernels: the kernel a bf16 (element
+ * bytes 2) or fp32 (4) product of that shape dispatches to, its launch geometry and resource use. The TileConfig's
+ * tile_n is taken as the advisory hint of symplex_gemm_desc (0 / 64 / 128 / 256; other values are ignored, as the
+ * reference's generator repairs infeasible tiles). There is no ptx_source. register_count is the per-thread
+ * register budget the kernel is compiled for (64K registers / threads per CTA). valid = 0 and error_message set for
+ * an empty problem. Host only. */
+typedef struct symplex_generated_kernel {
+  char kernel_name[64];
+  int64_t shared_mem_bytes, register_count;
+  int64_t grid_dims[3], block_dims[3];
+  int32_t valid;
+  char error_message[128];
+} symplex_generated_kernel;
+int symplex_b200_generate_matmul(int64_t M, int64_t N, int64_t K, int32_t element_bytes, int64_t tile_m, int64_t tile_n,
+                                 int64_t tile_k, symplex_generated_kernel* out);
+
+/* ---- fusion discovery for the matmul path (host only) -------------------------------------------- */
+
+/* One op as the reference's discover_fusions takes it (rust-engine/src/lib.rs:344-348): name ("matmul",
+ * "batch_matmul", "add", "mul", "relu", "gelu", "sigmoid", "tanh", "silu", ...; others never fuse into a matmul),
+ * output shape, dtype name ("fp32", "fp16", "bf16", "fp8", "int8", "int4"; unknown = fp32). */
+typedef struct symplex_fusion_op {
+  const char* op;
+  const int64_t* shape;
+  int32_t rank;
+  const char* dtype;
+} symplex_fusion_op;
+
+/* symplex_engine.discover_fusions (rust-engine/src/lib.rs:344-413) restricted to the one pattern of this path:
+ * every maximal chain [matmul, (mul,) (add,) (activation)] of at least two ops that
+ * matches_matmul_bias_activation accepts (rust-engine/src/fusion_engine.rs:1587-1623) becomes one
+ * "MatMulBiasReLU" boundary with estimate_memory_savings' traffic figure (:1209-1225: 2 x bytes(op 0) +
+ * 2 x bytes(op 1)), compute_savings_factor 1.1 and the pattern's base confidence 0.9. Writes the JSON document of
+ * the reference's schema into json_out (NUL terminated) and returns its length, or the negated length needed if
+ * cap is too small (nothing is written then), or SYMPLEX_ERR_INVALID for null arguments. */
+int64_t symplex_b200_discover_fusions(const symplex_fusion_op* ops, size_t n_ops, char* json_out, size_t cap);
+
+/* The longest prefix of ops[first..] that one GEMM launch executes, written into the epilogue fields of *d:
+ * [matmul, (mul,) (add,) (activation)] -> act(alpha * A.B + bias). Sets d->activation; *consumed = ops used
+ * (1 = a bare matmul), *has_bias / *has_scale say whether the caller must pass a bias vector / set d->alpha to the
+ * multiplier. Returns SYMPLEX_ERR_INVALID if ops[first] is not a matmul. */
+int symplex_b200_compile_epilogue(const symplex_fusion_op* ops, size_t n_ops, size_t first, symplex_gemm_desc* d,
+                                  int32_t* consumed, int32_t* has_bias, int32_t* has_scale);
 
 /* training::CompilerPipeline::compile_matmul -> PipelineResult (include/symplex/training/compiler_pipeline.h:18-33,70)
  * and cuda_backend::LaunchConfig::matmul (rust-engine/src/cuda_backend.rs:144-154) for this library: which

@@ -47,7 +47,27 @@ class Oracle:
         lib.oracle_fused_elementwise_f32.restype = ctypes.c_double
         lib.oracle_fused_elementwise_f64.argtypes = [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _int, _vp, _int]
         lib.oracle_fused_elementwise_f64.restype = ctypes.c_double
+        lib.oracle_matmul_jit_avx512.argtypes = [_vp, _vp, _vp, _i64, _i64, _i64]
+        lib.oracle_matmul_jit_avx512.restype = _int
+        lib.oracle_cache_tiled_dgemm.argtypes = [_vp, _vp, _vp, _i64, _i64, _i64]
+        lib.oracle_cache_tiled_dgemm.restype = None
         self.threads = max(1, int(lib.oracle_max_threads()))
+
+    def matmul_jit_avx512(self, A, B):
+        """The AVX-512 intrinsics twin of ``matmul_jit_order`` (one thread); None on a CPU without AVX-512F."""
+        A, B = self._prep(A, B)
+        C = np.full((A.shape[0], B.shape[1]), np.nan, np.float32)
+        rc = self.lib.oracle_matmul_jit_avx512(_ptr(A), _ptr(B), _ptr(C), A.shape[0], B.shape[1], A.shape[1])
+        return C if rc == 0 else None
+
+    def cache_tiled_dgemm(self, A, B):
+        """The reference's f64 tiled GEMM order (``rust-engine/src/phase3_jit.rs:578-650``)."""
+        A = np.ascontiguousarray(A, dtype=np.float64)
+        B = np.ascontiguousarray(B, dtype=np.float64)
+        assert A.ndim == 2 and B.ndim == 2 and A.shape[1] == B.shape[0]
+        C = np.full((A.shape[0], B.shape[1]), np.nan, np.float64)
+        self.lib.oracle_cache_tiled_dgemm(_ptr(A), _ptr(B), _ptr(C), A.shape[0], B.shape[1], A.shape[1])
+        return C
 
     def fused_elementwise(self, ops, inputs, constants, reduce_op=255, exact=False, dtype=np.float32):
         """The reference's fused op chain on host arrays: returns the result array (reduce_op 255) or the reduced
@@ -152,8 +172,8 @@ class Oracle:
 
 
 def load_oracle() -> Oracle:
-    src = os.path.join(ORACLE_DIR, "symplex_oracle.c")
-    if not os.path.exists(ORACLE_SO) or os.path.getmtime(ORACLE_SO) < os.path.getmtime(src):
+    newest = max(os.path.getmtime(os.path.join(ORACLE_DIR, f)) for f in ("symplex_oracle.c", "symplex_oracle_avx512.c"))
+    if not os.path.exists(ORACLE_SO) or os.path.getmtime(ORACLE_SO) < newest:
         subprocess.run(["make", "-C", ORACLE_DIR, ORACLE_SO], check=True, capture_output=True)
     return Oracle(ctypes.CDLL(ORACLE_SO))
 

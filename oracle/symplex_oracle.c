@@ -540,6 +540,29 @@ double oracle_fused_elementwise_f64(const oracle_fused_op* ops, int64_t n_ops, c
   return r + scalar_acc;
 }
 
+/* ---- the f64 tiled GEMM behind blas_dgemm / cache_tiled_dgemm_thin ------------------------------
+ * rust-engine/src/phase3_jit.rs:578-650 (cache_tiled_dgemm): C = 0; for each block of KC = 128 consecutive k
+ * (ascending): acc = 0; for k in the block: acc = acc + a*b - Rust rounds the product and the sum separately
+ * (no contraction; this file is compiled with -ffp-contract=off) - then C = C + acc. The MC / NC / MR / NR
+ * tiling and the packing only reorder which elements are worked on, never an element's own arithmetic.
+ * Unpinned by the reference's tests (none calls it); pinned here only through the structure above. */
+void oracle_cache_tiled_dgemm(const double* A, const double* B, double* C, int64_t M, int64_t N, int64_t K) {
+  for (int64_t i = 0; i < M; ++i)
+    for (int64_t j = 0; j < N; ++j) {
+      double c = 0.0;
+      for (int64_t k0 = 0; k0 < K; k0 += 128) {
+        const int64_t k1 = k0 + 128 < K ? k0 + 128 : K;
+        double acc = 0.0;
+        for (int64_t k = k0; k < k1; ++k) {
+          double t = A[i * K + k] * B[k * N + j];
+          acc = acc + t;
+        }
+        c = c + acc;
+      }
+      C[i * N + j] = c;
+    }
+}
+
 int oracle_max_threads(void) {
   long n = sysconf(_SC_NPROCESSORS_ONLN);
   return n > 0 ? (int)n : 1;

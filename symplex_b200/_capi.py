@@ -95,6 +95,41 @@ class GemmPlan(ctypes.Structure):
     ]
 
 
+class Comm(ctypes.Structure):
+    """``symplex_b200_comm``."""
+    _fields_ = [("rank", c_int32), ("world", c_int32), ("c_base", c_void_p * 8), ("c_multicast", c_void_p),
+                ("flags", c_void_p * 8), ("epoch", c_int64), ("wait_limit_ms", c_int32), ("reserved", c_int32)]
+
+
+class ShardSpec(ctypes.Structure):
+    """``symplex_shard_spec``."""
+    _fields_ = [("strategy", c_int32), ("shard_dim", c_int32), ("original_shape", c_int64 * 2),
+                ("local_shape", c_int64 * 2)]
+
+
+class ShardPlanPOD(ctypes.Structure):
+    """``symplex_shard_plan``."""
+    _fields_ = [("a", ShardSpec), ("b", ShardSpec), ("c", ShardSpec),
+                ("n_all_gather_ops", c_int32), ("n_all_reduce_ops", c_int32), ("n_all_to_all_ops", c_int32),
+                ("world", c_int32), ("total_communication_bytes", c_int64), ("peak_memory_per_device", c_int64)]
+
+
+class GeneratedKernel(ctypes.Structure):
+    """``symplex_generated_kernel``."""
+    _fields_ = [("kernel_name", c_char * 64), ("shared_mem_bytes", c_int64), ("register_count", c_int64),
+                ("grid_dims", c_int64 * 3), ("block_dims", c_int64 * 3), ("valid", c_int32),
+                ("error_message", c_char * 128)]
+
+
+class FusionOp(ctypes.Structure):
+    """``symplex_fusion_op``."""
+    _fields_ = [("op", c_char_p), ("shape", ctypes.POINTER(c_int64)), ("rank", c_int32), ("dtype", c_char_p)]
+
+
+XCHG_AUTO, XCHG_UNICAST, XCHG_MULTICAST, XCHG_EPILOGUE_TMA = 0, 1, 2, 3
+COMM_FLAG_WORDS = 16
+DT_F64 = 10
+
 REDUCE_SUM, REDUCE_MAX, REDUCE_MIN, REDUCE_NONE = 0, 1, 2, 255
 
 _F32P = c_void_p  # raw addresses; callers pass ints (numpy ``.ctypes.data`` / torch ``.data_ptr()``)
@@ -109,6 +144,25 @@ SIGNATURES = {
     "symplex_b200_gemm_ws": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_size_t, c_void_p]),
     "symplex_b200_sgemm_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "symplex_b200_sharded_gemm": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, ctypes.POINTER(Comm),
+                                          c_int32, c_void_p]),
+    "symplex_b200_analyze_matmul": (c_int, [c_int64, c_int64, c_int64, c_int32, c_int32, ctypes.POINTER(ShardPlanPOD)]),
+    "symplex_b200_noalloc_status": (c_int, [c_void_p]),
+    "symplex_b200_selftest_wait_timeout": (c_int, [c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
+    "symplex_b200_set_option": (c_int, [c_char_p, c_int64]),
+    "symplex_b200_get_option": (c_int64, [c_char_p]),
+    "blas_dgemm": (None, [_F32P, _F32P, _F32P, c_size_t, c_size_t, c_size_t]),
+    "cache_tiled_dgemm_thin": (None, [_F32P, _F32P, _F32P, c_size_t, c_size_t, c_size_t]),
+    "symplex_b200_dgemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                   c_void_p]),
+    "poly_get_micro_kernel_config": (None, [c_uint8, c_size_t] + [ctypes.POINTER(c_size_t)] * 5),
+    "symplex_b200_generate_matmul": (c_int, [c_int64, c_int64, c_int64, c_int32, c_int64, c_int64, c_int64,
+                                             ctypes.POINTER(GeneratedKernel)]),
+    "symplex_b200_discover_fusions": (c_int64, [ctypes.POINTER(FusionOp), c_size_t, c_char_p, c_size_t]),
+    "symplex_b200_compile_epilogue": (c_int, [ctypes.POINTER(FusionOp), c_size_t, c_size_t, ctypes.POINTER(GemmDesc),
+                                              ctypes.POINTER(c_int32), ctypes.POINTER(c_int32),
+                                              ctypes.POINTER(c_int32)]),
+    "symplex_b200_abi_sizes_ext": (c_int32, [ctypes.POINTER(c_int32), c_int32]),
     "symplex_b200_sync_status": (c_int, [c_void_p]),
     "symplex_b200_last_error": (c_char_p, []),
     "symplex_b200_gemm_host": (c_int, [ctypes.POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
@@ -180,13 +234,42 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)  # AttributeError here = header and library out of sync
         fn.restype = restype
         fn.argtypes = argtypes
-    sizes = (c_int32 * 5)()
-    lib.symplex_b200_abi_sizes(ctypes.byref(sizes))
-    mine = [ctypes.sizeof(t) for t in (GemmDesc, DeviceInfo, FusedOp, Target, GemmPlan)]
+    sizes = (c_int32 * 10)()
+    lib.symplex_b200_abi_sizes_ext(sizes, 10)
+    mine = [ctypes.sizeof(t) for t in (GemmDesc, DeviceInfo, FusedOp, Target, GemmPlan, Comm, ShardPlanPOD,
+                                       GeneratedKernel, FusionOp, KernelArgs)]
     if list(sizes) != mine:
         raise ImportError(f"struct layouts of {LIB_PATH} {list(sizes)} differ from this binding's {mine}: rebuild")
     _lib = lib
     return lib
+
+
+def pack_fusion_ops(ops):
+    """``[(name, shape, dtype), ...]`` -> (ctypes array of ``FusionOp``, keep-alive list)."""
+    arr = (FusionOp * max(len(ops), 1))()
+    keep = []
+    for i, (name, shape, dtype) in enumerate(ops):
+        sh = (c_int64 * max(len(shape), 1))(*[int(x) for x in shape])
+        keep.append(sh)
+        arr[i] = FusionOp(str(name).encode(), ctypes.cast(sh, ctypes.POINTER(c_int64)), len(shape), str(dtype).encode())
+    return arr, keep
+
+
+class option:
+    """``with option("pair_mode", 1): ...`` - set a tuning override of the library, restore it afterwards."""
+
+    def __init__(self, name: str, value: int):
+        self.name, self.value = name.encode(), int(value)
+
+    def __enter__(self):
+        lib = load()
+        self.old = lib.symplex_b200_get_option(self.name)
+        check(lib.symplex_b200_set_option(self.name, self.value))
+        return self
+
+    def __exit__(self, *exc):
+        load().symplex_b200_set_option(self.name, self.old)
+        return False
 
 
 def last_error() -> str:

@@ -10,9 +10,38 @@
 #include <mutex>
 
 #include "../../include/symplex_b200.h"
+#include "gemm_params.h"
 #include "host_api.h"
+#include "options.h"
 
 namespace sx {
+
+// ------------------------------------------------------------------ options
+Options& options() {
+  static Options o;
+  static const bool init = [] {
+    if (const char* e = getenv("SYMPLEX_B200_TILE")) o.tile_n = atoi(e);
+    if (const char* e = getenv("SYMPLEX_B200_TRACE")) o.trace = atoi(e);
+    return true;
+  }();
+  (void)init;
+  return o;
+}
+
+static std::atomic<int64_t>* option_by_name(const char* name) {
+  if (name == nullptr) return nullptr;
+  Options& o = options();
+  struct Entry { const char* name; std::atomic<int64_t>* v; };
+  const Entry table[] = {
+      {"tile_n", &o.tile_n}, {"pair_mode", &o.pair_mode}, {"f32_fused", &o.f32_fused},
+      {"f32_split_k", &o.f32_split_k}, {"f32_tile_rows", &o.f32_tile_rows}, {"group_m", &o.group_m},
+      {"tma_store", &o.tma_store}, {"pipeline_mb", &o.pipeline_mb}, {"pipeline", &o.pipeline},
+      {"wait_limit_ms", &o.wait_limit_ms}, {"trace", &o.trace},
+  };
+  for (const Entry& e : table)
+    if (strcmp(e.name, name) == 0) return e.v;
+  return nullptr;
+}
 
 // ------------------------------------------------------------------ errors / counters
 static thread_local char g_err[512] = "no error";
@@ -105,8 +134,12 @@ struct DeviceState {
   bool ready = false;
   int num_sms = 0;
   int* status = nullptr;  // device word written by kernels that unwind
+  unsigned* xchg_counter = nullptr;  // device word of the sharded GEMM's forwarder warps (zero between launches)
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  cudaEvent_t scratch_free = nullptr;  // recorded after the last launch that reads the pooled scratch
+  cudaStream_t scratch_stream = nullptr;  // the stream that launch went to
+  bool scratch_used = false;
   char* fe_scratch = nullptr;  // FE_SCRATCH_SETS reduction scratch areas of the fused elementwise kernels
   std::atomic<unsigned> fe_next{0};
 };
@@ -124,8 +157,10 @@ static int device_state(DeviceState** out) {
     SX_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
     if (major != 10) return fail(SX_ERR_DRIVER, "device %d is sm_%d0, this library needs sm_100", dev, major);
     SX_CUDA(cudaDeviceGetAttribute(&st.num_sms, cudaDevAttrMultiProcessorCount, dev));
-    SX_CUDA(cudaMalloc(&st.status, sizeof(int)));
-    SX_CUDA(cudaMemset(st.status, 0, sizeof(int)));
+    SX_CUDA(cudaMalloc(&st.status, 64));
+    SX_CUDA(cudaMemset(st.status, 0, 64));
+    st.xchg_counter = reinterpret_cast<unsigned*>(st.status) + 8;
+    SX_CUDA(cudaEventCreateWithFlags(&st.scratch_free, cudaEventDisableTiming));
     SX_CUDA(cudaMalloc(&st.fe_scratch, FE_SCRATCH_SETS * FE_REDUCE_SCRATCH_BYTES));
     SX_CUDA(cudaMemset(st.fe_scratch, 0, FE_SCRATCH_SETS * FE_REDUCE_SCRATCH_BYTES));
     st.ready = true;
@@ -134,22 +169,93 @@ static int device_state(DeviceState** out) {
   return SX_OK;
 }
 
-static int pool_scratch(DeviceState* st, size_t bytes, void** out) {
-  std::lock_guard<std::mutex> lk(st->mu);
-  if (bytes > st->scratch_bytes) {
-    if (st->scratch) {
-      SX_CUDA(cudaDeviceSynchronize());
-      SX_CUDA(cudaFree(st->scratch));
-      st->scratch = nullptr;
-      st->scratch_bytes = 0;
-    }
-    const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
-    SX_CUDA(cudaMalloc(&st->scratch, want));
-    st->scratch_bytes = want;
+// Where a launch gets its scratch from. Three sources: a pointer the caller owns (symplex_b200_gemm_ws, the
+// host-pointer paths' per-thread buffer), nothing, or the grow-only pool of the device. The pool is one block
+// shared by every caller of symplex_b200_gemm on that device, so its users are serialised: the pool's mutex is
+// held from the moment the pointer is handed out until the launches that use it have been enqueued (no other
+// thread can grow - and free - the block in between), and an event recorded after those launches makes a later
+// user on ANOTHER stream wait for them on the GPU. Growing synchronises the device before it frees the old
+// block. While `stream` is being captured into a CUDA graph no event is recorded or awaited (the capture's own
+// dependencies order the nodes; a graph that is replayed next to other pooled-scratch users is the caller's to
+// order).
+static int host_buf(int i, size_t bytes, void** out);
+
+struct Scratch {
+  void* fixed = nullptr;
+  DeviceState* pool = nullptr;
+  cudaStream_t stream = nullptr;
+  bool locked = false, capturing = false, host_thread = false;
+
+  static Scratch from_pointer(void* p) {
+    Scratch s;
+    s.fixed = p;
+    return s;
   }
-  *out = st->scratch;
-  return SX_OK;
-}
+  // the calling thread's own grow-only buffer (host-pointer paths), allocated when a kernel first needs it
+  static Scratch from_host_thread() {
+    Scratch s;
+    s.host_thread = true;
+    return s;
+  }
+  static Scratch from_pool(DeviceState* st, cudaStream_t stream) {
+    Scratch s;
+    s.pool = st;
+    s.stream = stream;
+    return s;
+  }
+  Scratch() = default;
+  Scratch(const Scratch&) = delete;
+  Scratch& operator=(const Scratch&) = delete;
+  Scratch(Scratch&& o) noexcept
+      : fixed(o.fixed), pool(o.pool), stream(o.stream), locked(o.locked), capturing(o.capturing), host_thread(o.host_thread) {
+    o.locked = false;
+  }
+
+  int get(size_t bytes, void** out) {
+    if (host_thread) return host_buf(6, bytes, out);
+    if (pool == nullptr) {
+      *out = fixed;
+      return SX_OK;
+    }
+    DeviceState* st = pool;
+    if (!locked) {
+      st->mu.lock();
+      locked = true;
+      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess) cudaGetLastError();
+      capturing = cs != cudaStreamCaptureStatusNone;
+    }
+    if (bytes > st->scratch_bytes) {
+      if (st->scratch) {
+        SX_CUDA(cudaDeviceSynchronize());
+        SX_CUDA(cudaFree(st->scratch));
+        st->scratch = nullptr;
+        st->scratch_bytes = 0;
+        st->scratch_used = false;
+      }
+      const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+      SX_CUDA(cudaMalloc(&st->scratch, want));
+      st->scratch_bytes = want;
+    }
+    if (!capturing && st->scratch_used && st->scratch_stream != stream)
+      SX_CUDA(cudaStreamWaitEvent(stream, st->scratch_free, 0));
+    *out = st->scratch;
+    return SX_OK;
+  }
+
+  ~Scratch() {
+    if (!locked) return;
+    if (!capturing) {
+      if (cudaEventRecord(pool->scratch_free, stream) == cudaSuccess) {
+        pool->scratch_used = true;
+        pool->scratch_stream = stream;
+      } else {
+        cudaGetLastError();
+      }
+    }
+    pool->mu.unlock();
+  }
+};
 
 // ------------------------------------------------------------------ planning
 static inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
@@ -223,17 +329,6 @@ static int make_plan(const symplex_gemm_desc* d, const void* A, const void* B, P
   return SX_OK;
 }
 
-static void debug_desc_override(TcGemmArgs* g) {
-  const char* e = getenv("SYMPLEX_B200_DESC_B");
-  if (e == nullptr) return;
-  unsigned lbo = 0, sbo = 0, ks = 0;
-  if (sscanf(e, "%u,%u,%u", &lbo, &sbo, &ks) == 3) {
-    g->dbg_lbo = lbo;
-    g->dbg_sbo = sbo;
-    g->dbg_kstep = ks;
-  }
-}
-
 // Which kernel serves a problem. One place decides, for the launch path and for the planning query alike.
 enum KernelKind { KK_F32_FUSED, KK_F32_SPLIT, KK_BF16_TC, KK_BF16_PAIR256, KK_BF16_PAIR512 };
 struct KernelChoice {
@@ -242,13 +337,14 @@ struct KernelChoice {
 };
 
 static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_peers, bool f32_fused_ok) {
+  const Options& opt = options();
   int forced = tile_n;
-  if (const char* e = getenv("SYMPLEX_B200_TILE")) forced = atoi(e);
+  if (opt.tile_n.load(std::memory_order_relaxed) != 0) forced = (int)opt.tile_n.load(std::memory_order_relaxed);
   if (p.f32_in) {
     // Small and batched problems (each operand element feeds only a few tiles): split inside the GEMM kernel.
     // With at most 64 rows there is a single row of tiles: no B element is converted twice, whatever N is.
     bool fused = (p.M <= 64 || ((p.M + 127) / 128 <= 8 && (p.N + 63) / 64 <= 16)) && f32_fused_ok;
-    if (const char* e = getenv("SYMPLEX_B200_F32_FUSED")) fused = atoi(e) != 0 && f32_fused_ok;
+    if (opt.f32_fused.load(std::memory_order_relaxed) >= 0) fused = opt.f32_fused.load(std::memory_order_relaxed) != 0 && f32_fused_ok;
     if (fused) return {KK_F32_FUSED, 64};
     if (forced == 64 || forced == 128) return {KK_F32_SPLIT, forced};
     const bool wide = p.N > 64 && ((p.M + 127) / 128) * ((p.N + 127) / 128) * p.batch >= num_sms;
@@ -273,17 +369,41 @@ static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_
     if (cost512 <= cost256 && cost512 <= cost0) mode = 2;
     else if (cost256 <= cost0) mode = 1;
   }
-  if (const char* e = getenv("SYMPLEX_B200_PAIR")) mode = atoi(e);
+  if (opt.pair_mode.load(std::memory_order_relaxed) >= 0) mode = (int)opt.pair_mode.load(std::memory_order_relaxed);
   if (n_peers > 0 && mode == 0) mode = 1;  // only the pair kernels carry the peer-store epilogue
   return {mode == 2 ? KK_BF16_PAIR512 : mode == 1 ? KK_BF16_PAIR256 : KK_BF16_TC, bn};
 }
 
+// Peer destinations of a launch (row-sharded products); see Exchange in gemm_params.h.
+struct PeerArgs {
+  int n_peers = 0;
+  int xchg = 0;  // 0: XCHG_EPILOGUE_TMA when n_peers > 0
+  const void* peer_C[7] = {};
+  int my_rank = 0, peer_rank[7] = {};
+  void* mc_C = nullptr;
+  int* flags = nullptr;
+  int* peer_flags[7] = {};
+  int epoch = 0;
+  unsigned long long wait_limit_ns = 0;
+};
+
 static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, const void* B, void* C,
-                    const float* bias, const void* residual, void* ws, DeviceState* st, cudaStream_t stream,
-                    const void* const* peer_C = nullptr, int n_peers = 0) {
+                    const float* bias, const void* residual, Scratch& scratch, DeviceState* st, cudaStream_t stream,
+                    const PeerArgs* peers = nullptr) {
   if (p.M == 0 || p.N == 0 || p.batch == 0) return SX_OK;  // nothing to write
   if (p.K == 0) return fail(SX_ERR_INVALID, "K == 0 is not supported by the device entry points");
-  uint8_t* w = static_cast<uint8_t*>(ws);
+  const Options& opt = options();
+  const int n_peers = peers ? peers->n_peers : 0;
+  uint8_t* w = nullptr;
+  auto need_scratch = [&]() -> int {
+    if (w != nullptr || p.total == 0) return SX_OK;
+    void* ws = nullptr;
+    int rc = scratch.get(p.total, &ws);
+    if (rc != SX_OK) return rc;
+    if (ws == nullptr) return fail(SX_ERR_INVALID, "this problem needs %zu bytes of scratch", p.total);
+    w = static_cast<uint8_t*>(ws);
+    return SX_OK;
+  };
   TcGemmArgs g{};
   g.M = p.M; g.N = p.N; g.batch = p.batch;
   g.out_bf16 = p.bf16_out;
@@ -294,8 +414,11 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
   g.status = st->status;
   g.num_sms = st->num_sms;
   g.K = p.K;
+  g.wait_limit_ns = (unsigned long long)opt.wait_limit_ms.load(std::memory_order_relaxed) * 1000000ull;
+  if (peers && peers->wait_limit_ns) g.wait_limit_ns = peers->wait_limit_ns;
   if (n_peers > 0 && p.f32_in)
     return fail(SX_ERR_INVALID, "peer destinations are supported for bf16 inputs only");
+  int rc;
   if (p.f32_in) {
     // Small and batched problems (each operand element feeds only a few tiles): split inside the GEMM kernel.
     {
@@ -304,7 +427,9 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
       f.A = A; f.lda = p.lda; f.a_plane_stride = p.a_bs;
       f.B = B; f.ldb = p.ldb; f.b_plane_stride = p.b_bs;
       if (choose_kernel(p, d->tile_n, st->num_sms, 0, f32_fused_operands_ok(f)).kind == KK_F32_FUSED) {
-        int rc = launch_gemm_f32_fused(f, stream);
+        if (opt.trace.load(std::memory_order_relaxed))
+          fprintf(stderr, "[symplex_b200] gemm %lldx%lldx%lld batch %d f32 -> in-kernel-split kernel\n", p.M, p.N, p.K, p.batch);
+        rc = launch_gemm_f32_fused(f, stream);
         if (rc == SX_ERR_EXEC) return fail(rc, "GEMM kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         if (rc != SX_OK) return rc;
         ++g_launches;
@@ -312,10 +437,11 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
       }
     }
     // Otherwise both operands are rewritten as {hi, lo} tf32 planes with K contiguous.
+    if ((rc = need_scratch()) != SX_OK) return rc;
     float* Ap = reinterpret_cast<float*>(w + p.a_off);
     float* Bp = reinterpret_cast<float*>(w + p.b_off);
-    int rc = launch_split_tf32(static_cast<const float*>(A), p.lda, p.a_bs, Ap, (int)p.M, (int)p.K, (int)p.a_ldp,
-                               p.batch, stream);
+    rc = launch_split_tf32(static_cast<const float*>(A), p.lda, p.a_bs, Ap, (int)p.M, (int)p.K, (int)p.a_ldp,
+                           p.batch, stream);
     if (rc != SX_OK) return fail(rc, "split_tf32(A) launch failed");
     ++g_launches;
     if (!p.b_ready) {
@@ -331,6 +457,9 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
     g.A = Ap; g.lda = p.a_ldp; g.a_plane_stride = p.M * p.a_ldp;
     g.B = Bp; g.ldb = p.b_ldp; g.b_plane_stride = p.N * p.b_ldp;
     g.bn = choose_kernel(p, d->tile_n, st->num_sms, 0, false).bn;
+    if (opt.trace.load(std::memory_order_relaxed))
+      fprintf(stderr, "[symplex_b200] gemm %lldx%lldx%lld batch %d f32 -> pre-split kernel, tile 128x%d\n", p.M, p.N, p.K,
+              p.batch, g.bn);
     rc = launch_gemm_tf32x3(g, stream);
     if (rc == SX_ERR_EXEC) return fail(rc, "GEMM kernel launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     if (rc != SX_OK) return rc;
@@ -341,15 +470,16 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
     const void* Buse = B;
     long long lda = p.lda, ldb = p.ldb, a_bs = p.a_bs, b_bs = p.b_bs;
     if (p.a_prep) {
-      int rc = launch_repack_16(A, p.lda, p.a_bs, w + p.a_off, p.a_ldp, (int)p.M, (int)p.K, p.batch, stream);
+      if ((rc = need_scratch()) != SX_OK) return rc;
+      rc = launch_repack_16(A, p.lda, p.a_bs, w + p.a_off, p.a_ldp, (int)p.M, (int)p.K, p.batch, stream);
       if (rc != SX_OK) return fail(rc, "repack(A) launch failed");
       ++g_launches;
       Ause = w + p.a_off; lda = p.a_ldp; a_bs = p.M * p.a_ldp;
     }
     if (p.b_prep) {
+      if ((rc = need_scratch()) != SX_OK) return rc;
       if (!p.b_ready) {
-        int rc = launch_repack_16(B, p.ldb, p.b_bs, w + p.b_off, p.b_ldp, (int)p.b_rows, (int)p.b_cols, p.batch,
-                                  stream);
+        rc = launch_repack_16(B, p.ldb, p.b_bs, w + p.b_off, p.b_ldp, (int)p.b_rows, (int)p.b_cols, p.batch, stream);
         if (rc != SX_OK) return fail(rc, "repack(B) launch failed");
         ++g_launches;
       }
@@ -366,16 +496,28 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
   const KernelChoice kc = choose_kernel(p, d->tile_n, st->num_sms, n_peers, false);
   g.bn = kc.bn;
   const int mode = kc.kind == KK_BF16_PAIR512 ? 2 : kc.kind == KK_BF16_PAIR256 ? 1 : 0;
-  debug_desc_override(&g);
-  if (const char* e = getenv("SYMPLEX_B200_GROUP_M")) g.group_m = atoi(e);
-  g.tma_store = 1;
-  if (const char* e = getenv("SYMPLEX_B200_TMA_STORE")) g.tma_store = atoi(e);
+  g.group_m = (int)opt.group_m.load(std::memory_order_relaxed);
+  g.tma_store = opt.tma_store.load(std::memory_order_relaxed) != 0;
   if (n_peers > 0) {
     g.n_peers = n_peers;
-    for (int i = 0; i < n_peers; ++i) g.peer_C[i] = peer_C[i];
+    g.xchg = peers->xchg;
+    g.my_rank = peers->my_rank;
+    g.mc_C = peers->mc_C;
+    g.flags = peers->flags;
+    g.epoch = peers->epoch;
+    g.xchg_counter = st->xchg_counter;
+    for (int i = 0; i < n_peers; ++i) {
+      g.peer_C[i] = peers->peer_C[i];
+      g.peer_rank[i] = peers->peer_rank[i];
+      g.peer_flags[i] = peers->peer_flags[i];
+    }
   }
   if (mode == 2) g.bn = 512;
-  int rc = mode != 0 ? launch_gemm_pair(g, stream) : launch_gemm_tc(g, stream);
+  if (opt.trace.load(std::memory_order_relaxed))
+    fprintf(stderr, "[symplex_b200] gemm %lldx%lldx%lld batch %d bf16 -> %s, tile width %d, %d peer(s), exchange %d\n", p.M,
+            p.N, p.K, p.batch, mode == 2 ? "512x256 CTA pairs" : mode == 1 ? "256x256 CTA pairs" : "single-CTA tiles", g.bn,
+            n_peers, g.xchg);
+  rc = mode != 0 ? launch_gemm_pair(g, stream) : launch_gemm_tc(g, stream);
   if (rc != SX_OK) {
     if (rc == SX_ERR_INVALID && strncmp(g_err, "cuTensorMap", 11) != 0)
       return fail(rc, "operands%s are not TMA compatible (16-byte alignment) or tile %d invalid",
@@ -393,8 +535,8 @@ struct HostCtx {
   cudaStream_t h2d = nullptr, d2h = nullptr;      // copy streams of the row-chunked pipeline
   cudaEvent_t ev_in[64] = {}, ev_out[64] = {};    // chunk c: inputs landed / result ready
   bool pipeline_ready = false;
-  void* buf[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // A, B, C, bias, residual, elementwise arena
-  size_t cap[6] = {0, 0, 0, 0, 0, 0};
+  void* buf[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // A, B, C, bias, residual, elementwise arena, GEMM scratch
+  size_t cap[7] = {0, 0, 0, 0, 0, 0, 0};
   int dev = -1;
 };
 static thread_local HostCtx t_host;
@@ -426,7 +568,7 @@ static int host_ctx(bool pipeline, HostCtx** out) {
     SX_CUDA(cudaStreamCreateWithFlags(&h.stream, cudaStreamNonBlocking));
     h.dev = dev;
     h.pipeline_ready = false;
-    for (int i = 0; i < 6; ++i) { h.buf[i] = nullptr; h.cap[i] = 0; }
+    for (int i = 0; i < 7; ++i) { h.buf[i] = nullptr; h.cap[i] = 0; }
   }
   if (pipeline && !h.pipeline_ready) {
     SX_CUDA(cudaStreamCreateWithFlags(&h.h2d, cudaStreamNonBlocking));
@@ -471,17 +613,18 @@ static int gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, v
   // Rows of C are independent, so the result is the one the single-shot path produces.
   {
     const size_t row_bytes = (size_t)p.K * in_elt + (size_t)p.N * out_elt;
-    size_t chunk_mb = 96;  // bytes of A + C moved per chunk: ~2 ms of PCIe time, several waves of GEMM tiles
-    if (const char* e = getenv("SYMPLEX_B200_PIPELINE_MB")) chunk_mb = (size_t)atoi(e) > 0 ? (size_t)atoi(e) : 1;
+    // bytes of A + C moved per chunk: 96 MB = ~2 ms of PCIe time, several waves of GEMM tiles
+    const int64_t opt_mb = options().pipeline_mb.load(std::memory_order_relaxed);
+    const size_t chunk_mb = opt_mb > 0 ? (size_t)opt_mb : 1;
     long long chunk_rows = (long long)((chunk_mb << 20) / row_bytes) / 512 * 512;
     if (chunk_rows < 2048) chunk_rows = 2048;
     if (chunk_rows * 64 < p.M) chunk_rows = ((p.M + 63) / 64 + 511) / 512 * 512;  // at most 64 chunks
     const long long nchunks = (p.M + chunk_rows - 1) / chunk_rows;
     const bool dense = p.lda == p.K && p.ldc == p.N;
-    if (p.batch == 1 && dense && !residual && nchunks >= 3 && nchunks <= 64 && getenv("SYMPLEX_B200_NO_PIPELINE") == nullptr) {
+    if (p.batch == 1 && dense && !residual && nchunks >= 3 && nchunks <= 64 &&
+        options().pipeline.load(std::memory_order_relaxed) != 0) {
       if ((rc = host_ctx(true, &hp)) != SX_OK) return rc;
-      void* ws = nullptr;
-      if (p.total && (rc = pool_scratch(st, p.total, &ws)) != SX_OK) return rc;
+      Scratch scratch = Scratch::from_host_thread();  // the calling thread's own, never the shared pool
       SX_CUDA(cudaMemcpyAsync(dB, B, b_bytes, cudaMemcpyHostToDevice, h.h2d));
       if (bias) {
         if ((rc = host_buf(3, (size_t)p.N * 4, &dbias)) != SX_OK) return rc;
@@ -503,7 +646,7 @@ static int gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, v
         pc.b_ready = c > 0;
         // this chunk's slice of the A scratch region (fp32 planes: 2 x rows x a_ldp floats; padded bf16: rows x a_ldp)
         pc.a_off = p.a_off + (size_t)r0 * p.a_ldp * (p.f32_in ? 8 : 2);
-        rc = run_gemm(d, pc, dAc, dB, dCc, static_cast<const float*>(dbias), nullptr, ws, st, h.stream);
+        rc = run_gemm(d, pc, dAc, dB, dCc, static_cast<const float*>(dbias), nullptr, scratch, st, h.stream);
         if (rc != SX_OK) {
           cudaStreamSynchronize(h.h2d);
           cudaStreamSynchronize(h.stream);
@@ -541,11 +684,8 @@ static int gemm_host(const symplex_gemm_desc* d, const void* A, const void* B, v
     // Strided C: keep the bytes between rows that the kernel does not write.
     SX_CUDA(cudaMemcpyAsync(dC, C, c_bytes, cudaMemcpyHostToDevice, h.stream));
   }
-  void* ws = nullptr;
-  if (p.total) {
-    if ((rc = pool_scratch(st, p.total, &ws)) != SX_OK) return rc;
-  }
-  rc = run_gemm(d, p, dA, dB, dC, static_cast<const float*>(dbias), dR, ws, st, h.stream);
+  Scratch scratch = Scratch::from_host_thread();
+  rc = run_gemm(d, p, dA, dB, dC, static_cast<const float*>(dbias), dR, scratch, st, h.stream);
   if (rc != SX_OK) return rc;
   SX_CUDA(cudaMemcpyAsync(C, dC, c_bytes, cudaMemcpyDeviceToHost, h.stream));
   int status = 0;
@@ -706,9 +846,8 @@ int symplex_b200_gemm(const symplex_gemm_desc* d, const void* A, const void* B, 
   if (!A || !B || !C) return fail(SX_ERR_INVALID, "null matrix pointer");
   DeviceState* st = nullptr;
   if ((rc = device_state(&st)) != SX_OK) return rc;
-  void* ws = nullptr;
-  if (p.total && (rc = pool_scratch(st, p.total, &ws)) != SX_OK) return rc;
-  return run_gemm(d, p, A, B, C, bias, residual, ws, st, static_cast<cudaStream_t>(stream));
+  Scratch scratch = Scratch::from_pool(st, static_cast<cudaStream_t>(stream));
+  return run_gemm(d, p, A, B, C, bias, residual, scratch, st, static_cast<cudaStream_t>(stream));
 }
 
 int symplex_b200_gemm_peers(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
@@ -721,9 +860,67 @@ int symplex_b200_gemm_peers(const symplex_gemm_desc* d, const void* A, const voi
   if (!A || !B || !C) return fail(SX_ERR_INVALID, "null matrix pointer");
   DeviceState* st = nullptr;
   if ((rc = device_state(&st)) != SX_OK) return rc;
-  void* ws = nullptr;
-  if (p.total && (rc = pool_scratch(st, p.total, &ws)) != SX_OK) return rc;
-  return run_gemm(d, p, A, B, C, bias, residual, ws, st, static_cast<cudaStream_t>(stream), peer_C, n_peers);
+  if (n_peers > 7) return fail(SX_ERR_INVALID, "at most 7 peer destinations");
+  PeerArgs pa;
+  pa.n_peers = n_peers;
+  for (int i = 0; i < n_peers; ++i) pa.peer_C[i] = peer_C[i];
+  Scratch scratch = Scratch::from_pool(st, static_cast<cudaStream_t>(stream));
+  return run_gemm(d, p, A, B, C, bias, residual, scratch, st, static_cast<cudaStream_t>(stream), &pa);
+}
+
+int symplex_b200_sharded_gemm(const symplex_gemm_desc* d, const void* A_local, const void* B, const float* bias,
+                              symplex_b200_comm* comm, int32_t exchange, void* stream) {
+  if (d == nullptr || comm == nullptr) return fail(SX_ERR_INVALID, "null descriptor or communicator");
+  const int world = comm->world, rank = comm->rank;
+  if (world < 1 || world > SYMPLEX_B200_MAX_RANKS || rank < 0 || rank >= world)
+    return fail(SX_ERR_INVALID, "bad communicator: rank %d of %d (at most %d ranks)", rank, world, SYMPLEX_B200_MAX_RANKS);
+  if (d->batch != 1) return fail(SX_ERR_INVALID, "the sharded GEMM takes one problem (batch 1)");
+  if (d->M % world != 0) return fail(SX_ERR_INVALID, "M = %lld rows do not split evenly over %d ranks", (long long)d->M, world);
+  if (d->ldc != 0 && d->ldc != d->N) return fail(SX_ERR_INVALID, "the gathered C is dense: ldc must be N (or 0)");
+  if (exchange < SYMPLEX_XCHG_AUTO || exchange > SYMPLEX_XCHG_EPILOGUE_TMA) return fail(SX_ERR_INVALID, "unknown exchange mode %d", exchange);
+  if (comm->c_base[rank] == nullptr) return fail(SX_ERR_INVALID, "communicator has no local C buffer");
+  symplex_gemm_desc dl = *d;  // this rank's share: rows [rank * M / world, (rank + 1) * M / world)
+  dl.M = d->M / world;
+  Plan p;
+  int rc = make_plan(&dl, A_local, B, &p);
+  if (rc != SX_OK) return rc;
+  const size_t out_elt = p.bf16_out ? 2 : 4;
+  const size_t row_off = (size_t)rank * (size_t)dl.M * (size_t)d->N * out_elt;
+  uint8_t* C_local = static_cast<uint8_t*>(comm->c_base[rank]) + row_off;
+  if (p.M == 0 || p.N == 0) return SX_OK;
+  if (!A_local || !B) return fail(SX_ERR_INVALID, "null matrix pointer");
+  DeviceState* st = nullptr;
+  if ((rc = device_state(&st)) != SX_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Scratch scratch = Scratch::from_pool(st, s);
+  if (world == 1) return run_gemm(&dl, p, A_local, B, C_local, bias, nullptr, scratch, st, s);
+  if (p.f32_in) return fail(SX_ERR_INVALID, "the sharded GEMM takes bf16 inputs");
+  PeerArgs pa;
+  int mode = exchange;
+  if (mode == SYMPLEX_XCHG_AUTO) mode = SYMPLEX_XCHG_UNICAST;
+  if (mode == SYMPLEX_XCHG_MULTICAST && comm->c_multicast == nullptr)
+    return fail(SX_ERR_INVALID, "exchange mode multicast needs comm->c_multicast (a multicast mapping of C)");
+  pa.xchg = mode == SYMPLEX_XCHG_UNICAST ? XCHG_FORWARD : mode == SYMPLEX_XCHG_MULTICAST ? XCHG_MULTICAST : XCHG_EPILOGUE_TMA;
+  pa.my_rank = rank;
+  for (int r = 0; r < world; ++r) {
+    if (r == rank) continue;
+    if (comm->c_base[r] == nullptr) return fail(SX_ERR_INVALID, "communicator has no mapping of rank %d's C", r);
+    pa.peer_C[pa.n_peers] = static_cast<uint8_t*>(comm->c_base[r]) + row_off;
+    pa.peer_rank[pa.n_peers] = r;
+    pa.peer_flags[pa.n_peers] = comm->flags[r];
+    ++pa.n_peers;
+  }
+  if (pa.xchg != XCHG_EPILOGUE_TMA) {
+    for (int r = 0; r < world; ++r)
+      if (comm->flags[r] == nullptr) return fail(SX_ERR_INVALID, "communicator has no flag block for rank %d", r);
+    pa.flags = comm->flags[rank];
+    if (comm->c_multicast) pa.mc_C = static_cast<uint8_t*>(comm->c_multicast) + row_off;
+    comm->epoch += 1;  // collective call number: every rank makes the same calls in the same order
+    if ((uint32_t)comm->epoch == 0) comm->epoch += 1;  // flags start at 0: that value never names a call
+    pa.epoch = (int)(uint32_t)comm->epoch;  // compared modulo 2^32 on the device
+    if (comm->wait_limit_ms > 0) pa.wait_limit_ns = (unsigned long long)comm->wait_limit_ms * 1000000ull;
+  }
+  return run_gemm(&dl, p, A_local, B, C_local, bias, nullptr, scratch, st, s, &pa);
 }
 
 int symplex_b200_gemm_ws(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,
@@ -738,7 +935,8 @@ int symplex_b200_gemm_ws(const symplex_gemm_desc* d, const void* A, const void* 
   if (reinterpret_cast<uintptr_t>(workspace) % 256) return fail(SX_ERR_INVALID, "workspace must be 256-byte aligned");
   DeviceState* st = nullptr;
   if ((rc = device_state(&st)) != SX_OK) return rc;
-  return run_gemm(d, p, A, B, C, bias, residual, workspace, st, static_cast<cudaStream_t>(stream));
+  Scratch scratch = Scratch::from_pointer(workspace);
+  return run_gemm(d, p, A, B, C, bias, residual, scratch, st, static_cast<cudaStream_t>(stream));
 }
 
 int symplex_b200_sync_status(void* stream) {
@@ -755,6 +953,44 @@ int symplex_b200_sync_status(void* stream) {
     return fail(SX_ERR_TIMEOUT, "device-side wait timed out (status %d)", status);
   }
   return SX_OK;
+}
+
+int symplex_b200_selftest_wait_timeout(const void* A, const void* B, void* C, int32_t limit_ms, void* stream) {
+  if (!A || !B || !C) return fail(SX_ERR_INVALID, "null matrix pointer");
+  if (limit_ms < 1 || limit_ms > 1000) return fail(SX_ERR_INVALID, "limit_ms must be in 1..1000");
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc != SX_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TcGemmArgs g{};
+  g.kind = 0; g.out_bf16 = 1; g.b_mn = 1; g.bn = 64;
+  g.M = 128; g.N = 64; g.K = 128;
+  g.batch = 1; g.nseg = 1;
+  g.a_planes = 1; g.b_planes = 1; g.za = 1; g.zb = 1;
+  g.A = A; g.lda = 128; g.a_plane_stride = 128 * 128;
+  g.B = B; g.ldb = 64; g.b_plane_stride = 128 * 64;
+  g.C = C; g.ldc = 64; g.c_batch_stride = 128 * 64;
+  g.alpha = 1.0f; g.beta = 0.0f; g.act = 0;
+  g.status = st->status;
+  g.num_sms = st->num_sms;
+  g.wait_limit_ns = (unsigned long long)limit_ms * 1000000ull;
+  g.fault_stop_early = 1;
+  rc = launch_gemm_tc(g, s);
+  if (rc != SX_OK) return fail(rc, "self-test launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+  ++g_launches;
+  return symplex_b200_sync_status(stream);
+}
+
+int symplex_b200_set_option(const char* name, int64_t value) {
+  std::atomic<int64_t>* v = option_by_name(name);
+  if (v == nullptr) return fail(SX_ERR_INVALID, "unknown option '%s'", name ? name : "(null)");
+  v->store(value);
+  return SX_OK;
+}
+
+int64_t symplex_b200_get_option(const char* name) {
+  std::atomic<int64_t>* v = option_by_name(name);
+  return v ? v->load() : INT64_MIN;
 }
 
 const char* symplex_b200_last_error(void) { return g_err; }
@@ -803,6 +1039,60 @@ void cache_tiled_sgemm_thin(const float* a, const float* b, float* c, size_t m, 
   symplex_matmul_f32(a, b, c, (int64_t)m, (int64_t)n, (int64_t)k);
 }
 
+int symplex_b200_dgemm(const double* A, const double* B, double* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                       int64_t ldb, int64_t ldc, void* stream) {
+  if (M < 0 || N < 0 || K < 0) return fail(SX_ERR_INVALID, "negative dimension");
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return fail(SX_ERR_INVALID, "dimension exceeds 2^31-1");
+  if (M == 0 || N == 0) return SX_OK;
+  if (K == 0) return fail(SX_ERR_INVALID, "K == 0 is not supported by the device entry points");
+  if (!A || !B || !C) return fail(SX_ERR_INVALID, "null matrix pointer");
+  if (lda == 0) lda = K;
+  if (ldb == 0) ldb = N;
+  if (ldc == 0) ldc = N;
+  if (lda < K || ldb < N || ldc < N) return fail(SX_ERR_INVALID, "leading dimension too small");
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc != SX_OK) return rc;
+  rc = launch_dgemm(A, lda, B, ldb, C, ldc, (int)M, (int)N, (int)K, static_cast<cudaStream_t>(stream));
+  if (rc == SX_ERR_EXEC) return fail(rc, "dgemm launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+  if (rc != SX_OK) return fail(rc, "dgemm: problem too large for one launch (more than 65535 x 64 rows)");
+  ++g_launches;
+  return SX_OK;
+}
+
+static int dgemm_host(const double* a, const double* b, double* c, size_t m, size_t n, size_t k) {
+  if (m == 0 || n == 0) return SX_OK;
+  if (k == 0) {  // the reference's loop nest leaves C = 0
+    memset(c, 0, m * n * sizeof(double));
+    return SX_OK;
+  }
+  if (!a || !b || !c) return fail(SX_ERR_INVALID, "null matrix pointer");
+  DeviceState* st = nullptr;
+  int rc = device_state(&st);
+  if (rc != SX_OK) return rc;
+  HostCtx* hp = nullptr;
+  if ((rc = host_ctx(false, &hp)) != SX_OK) return rc;
+  void *dA, *dB, *dC;
+  if ((rc = host_buf(0, m * k * 8, &dA)) != SX_OK) return rc;
+  if ((rc = host_buf(1, k * n * 8, &dB)) != SX_OK) return rc;
+  if ((rc = host_buf(2, m * n * 8, &dC)) != SX_OK) return rc;
+  SX_CUDA(cudaMemcpyAsync(dA, a, m * k * 8, cudaMemcpyHostToDevice, hp->stream));
+  SX_CUDA(cudaMemcpyAsync(dB, b, k * n * 8, cudaMemcpyHostToDevice, hp->stream));
+  rc = symplex_b200_dgemm(static_cast<double*>(dA), static_cast<double*>(dB), static_cast<double*>(dC), (int64_t)m,
+                          (int64_t)n, (int64_t)k, 0, 0, 0, hp->stream);
+  if (rc != SX_OK) return rc;
+  SX_CUDA(cudaMemcpyAsync(c, dC, m * n * 8, cudaMemcpyDeviceToHost, hp->stream));
+  SX_CUDA(cudaStreamSynchronize(hp->stream));
+  return SX_OK;
+}
+
+void blas_dgemm(const double* a, const double* b, double* c, size_t m, size_t n, size_t k) {
+  (void)dgemm_host(a, b, c, m, n, k);
+}
+void cache_tiled_dgemm_thin(const double* a, const double* b, double* c, size_t m, size_t n, size_t k) {
+  (void)dgemm_host(a, b, c, m, n, k);
+}
+
 int64_t symplex_b200_exec_tensor_matmul(const uint8_t* rec, size_t len, void* const* slots, size_t nslots) {
   // Wire format of Instr::TensorMatMul (rust-engine/src/types.rs:884-904): 0xA2, dst u16, lhs u16, rhs u16,
   // m u64, n u64, k u64, element_ty u8, lhs_layout u8, rhs_layout u8 - little endian, 34 bytes.
@@ -819,13 +1109,18 @@ int64_t symplex_b200_exec_tensor_matmul(const uint8_t* rec, size_t len, void* co
   const int ety = rec[31], lhs_layout = rec[32], rhs_layout = rec[33];
   if (dst >= nslots || lhs >= nslots || rhs >= nslots || slots == nullptr)
     return fail(SX_ERR_INVALID, "slot index out of range (%u, %u, %u of %zu)", dst, lhs, rhs, nslots);
-  if (ety != SYMPLEX_DT_F32 && ety != SYMPLEX_DT_BF16)
-    return fail(SX_ERR_INVALID, "element type %d not supported on this path (F32 = 9, BF16 = 11)", ety);
+  if (ety != SYMPLEX_DT_F32 && ety != SYMPLEX_DT_BF16 && ety != SYMPLEX_DT_F64)
+    return fail(SX_ERR_INVALID, "element type %d not supported on this path (F32 = 9, F64 = 10, BF16 = 11)", ety);
   if (lhs_layout != SYMPLEX_ROW_MAJOR) return fail(SX_ERR_INVALID, "lhs must be row-major");
   if (rhs_layout != SYMPLEX_ROW_MAJOR && rhs_layout != SYMPLEX_COL_MAJOR)
     return fail(SX_ERR_INVALID, "rhs layout byte %d is not a MatrixLayout", rhs_layout);
   if (m > 0x7fffffffULL || n > 0x7fffffffULL || k > 0x7fffffffULL) return fail(SX_ERR_INVALID, "dimension too large");
   if (m == 0 || n == 0 || k == 0) return 0;
+  if (ety == SYMPLEX_DT_F64) {  // what the reference lowers to blas_dgemm / cache_tiled_dgemm_thin
+    if (rhs_layout != SYMPLEX_ROW_MAJOR) return fail(SX_ERR_INVALID, "F64 records take a row-major rhs");
+    return dgemm_host(static_cast<const double*>(slots[lhs]), static_cast<const double*>(slots[rhs]),
+                      static_cast<double*>(slots[dst]), (size_t)m, (size_t)n, (size_t)k);
+  }
   symplex_gemm_desc d;
   symplex_b200_gemm_desc_init(&d, (int64_t)m, (int64_t)n, (int64_t)k, ety, ety);
   d.b_layout = rhs_layout;
@@ -902,6 +1197,17 @@ int symplex_cuda_device_info(symplex_device_info* out) {
 }
 
 uint64_t symplex_b200_launch_count(void) { return g_launches.load(); }
+
+int32_t symplex_b200_abi_sizes_ext(int32_t* out, int32_t n) {
+  const int32_t sizes[] = {(int32_t)sizeof(symplex_gemm_desc),     (int32_t)sizeof(symplex_device_info),
+                           (int32_t)sizeof(symplex_fused_op),      (int32_t)sizeof(symplex_b200_target),
+                           (int32_t)sizeof(symplex_gemm_plan),     (int32_t)sizeof(symplex_b200_comm),
+                           (int32_t)sizeof(symplex_shard_plan),    (int32_t)sizeof(symplex_generated_kernel),
+                           (int32_t)sizeof(symplex_fusion_op),     (int32_t)sizeof(symplex_kernel_args)};
+  const int32_t have = (int32_t)(sizeof(sizes) / sizeof(sizes[0]));
+  for (int32_t i = 0; out != nullptr && i < n && i < have; ++i) out[i] = sizes[i];
+  return have;
+}
 
 void symplex_b200_abi_sizes(int32_t out[5]) {
   if (!out) return;

@@ -33,6 +33,7 @@
 #include "epilogue.cuh"
 #include "gemm_params.h"
 #include "host_api.h"
+#include "options.h"
 #include "sm100_ptx.cuh"
 
 namespace sx {
@@ -64,12 +65,6 @@ __device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t cluster_addr) {
                : "r"(cluster_addr));  // volatile keeps it after the (volatile) barrier wait that precedes it
   return v;
 }
-#ifdef SX_FUSED_TRACE
-__device__ unsigned long long g_fused_trace[32];
-#define SX_TRACE(i) do { if (blockIdx.x == 0) g_fused_trace[i] = globaltimer_ns(); else if (blockIdx.x == 1 && (i) < 16) g_fused_trace[16 + (i)] = globaltimer_ns(); } while (0)
-#else
-#define SX_TRACE(i) do { } while (0)
-#endif
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed_after(uint32_t cluster_addr, uint32_t dep) {
   asm volatile(
       "{\n"
@@ -113,7 +108,6 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) SX_TRACE(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -143,7 +137,6 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if constexpr (kSplit > 1) cluster_sync_all();  // every CTA's barriers are initialised before a peer arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
-  if (threadIdx.x == 0) SX_TRACE(1);
 
   const int per = p.m_tiles * p.n_tiles;
   const int total_tiles = p.batch * per;
@@ -173,7 +166,6 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           uint8_t* base = tiles + stage * Cfg::STAGE_BYTES;
           mbar_arrive_expect_tx(&raw_full[stage], Cfg::RAW_BYTES);
           const int k0 = (kb0 + kb) * BK;
-          if (kb == 0) SX_TRACE(2);
           tma_load_3d(base + Cfg::A_OFF, &tmA, &raw_full[stage], k0, m0, z);
           if constexpr (kBmn) tma_load_3d(base + Cfg::BRAW_OFF, &tmB, &raw_full[stage], n0, k0, z);
           else tma_load_3d(base + Cfg::BRAW_OFF, &tmB, &raw_full[stage], k0, n0, z);
@@ -221,7 +213,6 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (++macc == 2) { macc = 0; mphase ^= 1; }
         }
         if (!ok) break;
-        SX_TRACE(6);
         umma_commit(&corr_full[cacc]);
         if (++cacc == 2) { cacc = 0; cphase ^= 1; }
       }
@@ -243,7 +234,6 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const int stage = it % STAGES;
         const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
         if (!mbar_wait(&raw_full[stage], phase, &abort_flag)) { ok = false; break; }
-        if (tid == 0 && kb == 0) SX_TRACE(3);
         uint8_t* base = tiles + stage * Cfg::STAGE_BYTES;
 #pragma unroll
         for (int i = 0; i < 1024 / CT; ++i) {  // A: 1024 16-byte chunks, position-wise
@@ -283,8 +273,6 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         fence_proxy_async_smem();  // the tensor core reads these tiles through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(&conv_done[stage]);
-        if (tid == 0 && kb == 0) SX_TRACE(4);
-        if (tid == 0 && kb == nkb - 1) SX_TRACE(5);
       }
     }
   } else {
@@ -303,7 +291,6 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
       for (int ch = 0; ch < nchunks; ++ch) {
         if (!mbar_wait(&main_full[macc], mphase, &abort_flag)) { ok = false; break; }
-        if (q == 0 && lane == 0 && ch == 0) SX_TRACE(7);
         tc_fence_after_sync();
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
@@ -320,7 +307,6 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
       if (!ok) break;
       if (!mbar_wait(&corr_full[cacc], cphase, &abort_flag)) break;
-      if (q == 0 && lane == 0) SX_TRACE(8);
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
@@ -348,14 +334,12 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 make_float4(sum[g * 4 + 0], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3]);
           __syncwarp();  // orders the other lanes' stores before lane 0's release
           if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&part_full[rank - 1][q]), 0));
-          if (q == 0 && lane == 0) SX_TRACE(9);
           xphase ^= 1;
           continue;  // only the leader stores
         }
         bool got = true;
         for (int r = 1; r < kSplit; ++r)
           if (!mbar_wait<true>(&part_full[r - 1][q], xphase, &abort_flag)) { got = false; break; }
-        if (q == 0 && lane == 0) SX_TRACE(13);
         if (got) {
           // Remote (distributed shared memory) loads take on the order of 100 ns each: a round issues the loads
           // of all peers for a group of columns before the first add, so 12 (8 for two CTAs) are in flight per
@@ -396,7 +380,6 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         xphase ^= 1;
       }
 
-      if (q == 0 && lane == 0) SX_TRACE(9);
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
       const long long row_off = (long long)z * p.c_batch_stride + (long long)row * p.ldc;
@@ -409,18 +392,15 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         for (int j = 0; j < 32; ++j) v[j] = sum[c * 32 + j];
         ep.template strip<false>(v, row_ok, row_off, col0);
       }
-      if (q == 0 && lane == 0) SX_TRACE(10);
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0) SX_TRACE(11);
   if constexpr (kSplit > 1) cluster_sync_all();  // peers are done with this CTA's shared memory and barriers
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc<1>(tmem_base, Cfg::TMEM_COLS);
-    if (lane == 0) SX_TRACE(12);
   }
   if (threadIdx.x == 0 && abort_flag != 0 && p.status != nullptr) atomicExch(p.status, int(ST_WAIT_TIMEOUT));
 }
@@ -513,25 +493,18 @@ int launch_gemm_f32_fused(const TcGemmArgs& a, cudaStream_t stream) {
 }
 
 // Rows of one problem's output tile: 64 when the problem has at most 64 rows (gemm_f32_small_kernel takes it),
-// else 128 (this file's kernel). SYMPLEX_B200_F32_TILE_ROWS=128 forces this file's kernel (tests compare the two).
+// else 128 (this file's kernel). The option "f32_tile_rows" = 128 forces this file's kernel (tests compare the two).
 int f32_fused_tile_rows(long long M) {
-  if (const char* e = getenv("SYMPLEX_B200_F32_TILE_ROWS")) {
-    if (atoi(e) == 128) return 128;
-  }
+  if (options().f32_tile_rows.load(std::memory_order_relaxed) == 128) return 128;
   return M <= 64 ? 64 : 128;
 }
 
-#ifdef SX_FUSED_TRACE
-extern "C" __attribute__((visibility("default"))) int symplex_b200_debug_fused_trace(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_fused_trace, sizeof(unsigned long long) * 32);
-}
-#endif
 
 // How many CTAs share one output tile (split-K over a cluster): only when the tiles alone would leave most SMs
 // idle and every rank still gets at least two k-blocks of 32.
 int f32_fused_split_k(long long tiles, long long K, int num_sms) {
-  if (const char* e = getenv("SYMPLEX_B200_F32_SPLITK")) {
-    const int v = atoi(e);
+  {
+    const int v = (int)options().f32_split_k.load(std::memory_order_relaxed);
     if (v == 1 || v == 2 || v == 4) return (K + 31) / 32 >= v ? v : 1;  // forced (tests): any tile count
   }
   const long long nkb = (K + 31) / 32;

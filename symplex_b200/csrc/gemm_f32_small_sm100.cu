@@ -31,6 +31,7 @@
 #include "epilogue.cuh"
 #include "gemm_params.h"
 #include "host_api.h"
+#include "options.h"
 #include "sm100_ptx.cuh"
 
 namespace sx {
@@ -65,15 +66,6 @@ __device__ __forceinline__ void small_split4(const float4& x, float4& hi, float4
   lo.z = small_tf32_rna(x.z - hi.z); lo.w = small_tf32_rna(x.w - hi.w);
 }
 
-#ifdef SX_FUSED_TRACE
-__device__ unsigned long long g_small_trace[8 * 16];
-#define SM_TRACE(tile, i) do { if (blockIdx.x == 0 && (tile) < 16) g_small_trace[(i) * 16 + (tile)] = globaltimer_ns(); } while (0)
-extern "C" __attribute__((visibility("default"))) int symplex_b200_debug_small_trace(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_small_trace, sizeof(g_small_trace));
-}
-#else
-#define SM_TRACE(tile, i) do { } while (0)
-#endif
 
 // Loads of a raw stage, volatile so that they stay where they are written (before the stage is handed back).
 __device__ __forceinline__ float4 ld_raw_v4(const uint8_t* p) {
@@ -158,7 +150,6 @@ gemm_f32_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           mbar_arrive_expect_tx(&raw_full[stage], Cfg::RAW_BYTES);
           armed |= 1u << stage;
           armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
-          if (kb == 0) SM_TRACE(t / gridDim.x, 0);
           // boxes span two batch entries: [2][64][32] of A; [2][64 n][32 k] or [2][32 k][64 n] of B
           tma_load_3d(base + Cfg::RAW_A, &tmA, &raw_full[stage], kb * BK, 0, z0);
           if constexpr (kBmn) tma_load_3d(base + Cfg::RAW_B, &tmB, &raw_full[stage], n0, kb * BK, z0);
@@ -217,7 +208,6 @@ gemm_f32_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (++macc == 2) { macc = 0; mphase ^= 1; }
         }
         if (!ok) break;
-        SM_TRACE(t / gridDim.x, 5);
         umma_commit(&corr_full[cacc]);
         if (++cacc == 2) { cacc = 0; cphase ^= 1; }
       }
@@ -236,9 +226,7 @@ gemm_f32_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (it % Cfg::CONV_GROUPS != group) continue;
         const int rs = it % RS, os = it % OS;
         if (!mbar_wait(&raw_full[rs], (uint32_t)(it / RS) & 1u, &abort_flag)) { ok = false; break; }
-        if (tid == 0 && kb == 0) SM_TRACE(t / gridDim.x, 1);
         if (!mbar_wait(&op_empty[os], ((uint32_t)(it / OS) & 1u) ^ 1u, &abort_flag)) { ok = false; break; }
-        if (tid == 0 && kb == 0) SM_TRACE(t / gridDim.x, 2);
         const uint8_t* raw = tiles + rs * Cfg::RAW_BYTES;
         uint8_t* op = tiles + Cfg::OP_BASE + os * Cfg::OP_BYTES;
         // Read the whole raw stage into registers first and hand it back to the producer at once: the next
@@ -296,7 +284,6 @@ gemm_f32_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         fence_proxy_async_smem();  // the tensor core reads the planes through the async proxy
         __syncwarp();
         if (lane == 0) mbar_arrive(&conv_done[os]);
-        if (tid == 0) SM_TRACE(t / gridDim.x, 3 + (kb & 1));
       }
     }
   } else {
@@ -334,7 +321,6 @@ gemm_f32_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
       if (!ok) break;
       if (!mbar_wait(&corr_full[cacc], cphase, &abort_flag)) break;
-      if (q == 0 && lane == 0) SM_TRACE(t / gridDim.x, 6);
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < PN / 32; ++c) {
@@ -391,7 +377,6 @@ gemm_f32_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           ep.template strip<false>(v, row_ok, row_off, col0);
         }
       }
-      if (q == 0 && lane == 0) SM_TRACE(t / gridDim.x, 7);
     }
     if (p.n_dst != 0 && lane == 0) bulk_wait_group<0>();  // every store of this warp has been performed
   }
@@ -459,7 +444,7 @@ int launch_gemm_f32_small(const TcGemmArgs& a, cudaStream_t stream) {
   CUtensorMap tmC = tmA;
   const int elt = a.out_bf16 ? 2 : 4;
   if (reinterpret_cast<uintptr_t>(a.C) % 16 == 0 && (a.ldc * elt) % 16 == 0 && (a.c_batch_stride * elt) % 16 == 0 &&
-      getenv("SYMPLEX_B200_TMA_STORE") == nullptr) {
+      options().tma_store.load(std::memory_order_relaxed) != 0) {
     uint64_t dims[3] = {(uint64_t)a.N, (uint64_t)a.M, (uint64_t)a.batch};
     uint64_t strides[2] = {(uint64_t)a.ldc * elt, (uint64_t)a.c_batch_stride * elt};
     uint32_t box[3] = {(uint32_t)(128 / elt), 32u, 1u};

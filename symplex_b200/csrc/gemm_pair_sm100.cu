@@ -18,6 +18,16 @@
 // the empty / accumulator-full barriers of BOTH CTAs; epilogue warps release an accumulator with a
 // (possibly remote) arrive on the leader's accumulator-empty barrier. No TMA multicast is used.
 //
+// Row-sharded products (kFwd instantiations): two more warps per CTA, the forwarders, copy every tile this CTA has
+// finished from the local C (an L2 hit: the epilogue has just written it) to the same place in every other GPU's C,
+// either with one 16-byte store per peer (XCHG_FORWARD) or with one multimem.st to a multicast mapping that the
+// NVSwitch replicates (XCHG_MULTICAST). The local C is the buffer between the tensor pipe and NVLink, so link
+// back-pressure delays only the forwarders, never the epilogue warps that must free tensor memory for the next tile.
+// The ranks order themselves with flags written into each other's memory: READY (a rank has entered this call, its
+// C may be overwritten) is awaited before the first remote store, DONE (all of a rank's tiles have landed) is
+// written by the last forwarder warp of the grid and awaited by it, so the kernel ends only when the whole gathered
+// C is in place on this GPU.
+//
 // All waits are bounded (sm100_ptx.cuh); on a timeout every role unwinds and the kernel reports
 // ST_WAIT_TIMEOUT through the status word.
 #include <cuda_bf16.h>
@@ -29,7 +39,7 @@
 
 namespace sx {
 
-template <int kMB>
+template <int kMB, bool kFwd = false>
 struct PairCfg {
   static constexpr int ROWS = 128 * kMB;   // rows of A / C per CTA
   static constexpr int BM = 2 * ROWS;      // rows per pair
@@ -40,9 +50,10 @@ struct PairCfg {
   static constexpr int B_BYTES = 128 * 128;  // this CTA's 128 of the 256 columns
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = kMB == 1 ? 6 : 4;
-  static constexpr int THREADS = 64 + 128 * kMB;
-  static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
   static constexpr int EPI_WARPS = 4 * kMB;
+  static constexpr int FWD_WARPS = kFwd ? 2 : 0;  // copy finished tiles to the other GPUs (row-sharded products)
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS + 32 * FWD_WARPS;
+  static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
   static constexpr int STAGING_BYTES = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes, 128B-swizzled
   static constexpr int DYN_SMEM = STAGES * STAGE_BYTES + EPI_WARPS * STAGING_BYTES + 1024;
 };
@@ -72,23 +83,25 @@ __device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int t) {
   return c;
 }
 
-template <typename OutT, bool kBmn, int kMB>
-__global__ void __launch_bounds__(PairCfg<kMB>::THREADS, 1)
+template <typename OutT, bool kBmn, int kMB, bool kFwd>
+__global__ void __launch_bounds__(PairCfg<kMB, kFwd>::THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ DstMaps dst, const GemmParams p) {
-  using Cfg = PairCfg<kMB>;
+  using Cfg = PairCfg<kMB, kFwd>;
   constexpr int BN = Cfg::BN, BK = Cfg::BK, STAGES = Cfg::STAGES;
 
   extern __shared__ uint8_t dyn_smem[];
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint64_t fwd_bar[Cfg::EPI_WARPS];  // per epilogue warp: a finished block is back in its staging tile
   __shared__ uint32_t tmem_base_slot;
+  __shared__ uint32_t stored_warps;  // kFwd: epilogue warps x tiles whose stores to the local C have been performed
   __shared__ int abort_flag;
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t cta_rank = cluster_ctarank();  // 0 = leader
+  const uint64_t wait_ns = p.wait_limit_ns;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
@@ -103,6 +116,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int w = 0; w < Cfg::EPI_WARPS; ++w) mbar_init(&fwd_bar[w], 1);
     abort_flag = 0;
+    stored_warps = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -125,16 +139,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmB);
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t armed = 0, armed_phase = 0;  // leader: stages whose copies (of both CTAs) may still be in flight
       bool ok = true;
       for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
         const PairTile tc = pair_tile<Cfg::BM, BN>(p, t);
         const int my_m0 = tc.m0 + int(cta_rank) * Cfg::ROWS;
         const int my_n0 = tc.n0 + int(cta_rank) * 128;
         for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag, wait_ns)) { ok = false; break; }
           uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
-          if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);
+          if (cta_rank == 0) {
+            mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::STAGE_BYTES);
+            armed |= 1u << stage;
+            armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+          }
           const uint32_t leader_full = mapa_u32(smem_u32(&full_bar[stage]), 0);
           tma_load_3d_pair(sa, &tmA, leader_full, kb * BK, my_m0, tc.z);  // ROWS x 64 box
           if constexpr (kBmn) {
@@ -144,6 +163,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             tma_load_3d_pair(sb, &tmB, leader_full, kb * BK, my_n0, tc.z);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Unwinding: copies that were already issued get a bounded time to land before the CTAs leave. The leader
+        // sees both CTAs' bytes on its full barriers; its partner, which has no barrier of its own to watch, gives
+        // its copies a fixed grace period (a copy takes a few microseconds) and then meets the leader at the
+        // cluster barrier below.
+        const uint64_t t0 = globaltimer_ns();
+        if (cta_rank == 0) {
+          for (int s = 0; s < STAGES; ++s) {
+            if (!(armed & (1u << s))) continue;
+            while (!mbar_try_wait(&full_bar[s], (armed_phase >> s) & 1u)) {
+              if (globaltimer_ns() - t0 > 2000000ull) break;
+            }
+          }
+        } else {
+          while (globaltimer_ns() - t0 < 100000ull) __nanosleep(1000);
         }
       }
     }
@@ -175,10 +211,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       };
       for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
         if constexpr (kMB == 1) {
-          if (!mbar_wait<true>(&acc_empty[slot], acc_phase ^ 1, &abort_flag)) break;
+          if (!mbar_wait<true>(&acc_empty[slot], acc_phase ^ 1, &abort_flag, wait_ns)) break;
           tc_fence_after_sync();
           for (int kb = 0; kb < nkb; ++kb) {
-            if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&full_bar[stage], phase, &abort_flag, wait_ns)) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t a_addr = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
             const uint32_t b_addr = a_addr + Cfg::A_BYTES;
@@ -202,14 +238,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           auto group = [&](int g0, int g1) {  // k-blocks [g0, g1) block-major
             for (int mb = 0; mb < 2 && ok; ++mb) {
               if (g0 == 0) {
-                if (!mbar_wait<true>(&acc_empty[mb], acc_phase ^ 1, &abort_flag)) { ok = false; break; }
+                if (!mbar_wait<true>(&acc_empty[mb], acc_phase ^ 1, &abort_flag, wait_ns)) { ok = false; break; }
                 tc_fence_after_sync();
               }
               int s = stage;
               uint32_t ph = phase;
               for (int kb = g0; kb < g1; ++kb) {
                 if (mb == 0) {
-                  if (!mbar_wait(&full_bar[s], ph, &abort_flag)) { ok = false; break; }
+                  if (!mbar_wait(&full_bar[s], ph, &abort_flag, wait_ns)) { ok = false; break; }
                   tc_fence_after_sync();
                 }
                 issue_block(mb, s, kb != 0 ? 1u : 0u);
@@ -222,7 +258,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           };
           group(0, head_end);
           for (int kb = head_end; ok && kb < tail_begin; ++kb) {
-            if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&full_bar[stage], phase, &abort_flag, wait_ns)) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t a_addr = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
             const uint32_t b_addr = a_addr + Cfg::A_BYTES;
@@ -242,7 +278,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
     }
-  } else {
+  } else if (warp < 2 + Cfg::EPI_WARPS) {
     // ------------------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     // kMB == 1: four warps, each drains all 256 columns of the tile's accumulator.
@@ -260,7 +296,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll 1
       for (int blk = 0; blk < kMB; ++blk) {
         if constexpr (kMB == 2) slot = blk;
-        if (!mbar_wait(&acc_full[slot], acc_phase, &abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&acc_full[slot], acc_phase, &abort_flag, wait_ns)) { ok = false; break; }
         tc_fence_after_sync();
         const int row0 = tc.m0 + int(cta_rank) * Cfg::ROWS + blk * 128 + q * 32;  // this warp's first row
         const int row = row0 + lane;
@@ -333,9 +369,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       } else {
         acc_phase ^= 1;
       }
-      // Forwarding to the peer GPUs. TMEM is free again, so the MMAs of the next tile are already running;
-      // NVLink back-pressure now only delays this warp, not the tensor pipe. Each block this warp wrote to
-      // the local C is read back (an L2 hit) into the staging tile by TMA and stored to every peer's C.
+      if constexpr (kFwd) {
+        // Tell the forwarder warps that this warp's part of the tile is in the local C.
+        if (lane == 0) {
+          bulk_wait_group<0>();  // the stores have been performed
+          smem_counter_add_release(&stored_warps, 1u);
+        }
+      }
+      // XCHG_EPILOGUE_TMA: forwarding to the peer GPUs by this warp. TMEM is free again, so the MMAs of the next
+      // tile are already running. Each block this warp wrote to the local C is read back (an L2 hit) into the
+      // staging tile by TMA and stored to every peer's C.
       if (ok && p.n_dst > 1) {
         if (lane == 0) {
           bulk_wait_group<0>();  // this tile's local stores have been performed
@@ -349,7 +392,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               bulk_wait_group_read<0>();  // the previous block has left the staging tile
               mbar_arrive_expect_tx(&fwd_bar[warp - 2], Cfg::STAGING_BYTES);
               tma_load_3d(staging, &dst.m[0], &fwd_bar[warp - 2], col0, row0, tc.z);
-              if (!mbar_wait(&fwd_bar[warp - 2], fwd_phase, &abort_flag)) { ok = false; break; }
+              if (!mbar_wait(&fwd_bar[warp - 2], fwd_phase, &abort_flag, wait_ns)) { ok = false; break; }
               fwd_phase ^= 1;
               for (int d = 1; d < p.n_dst; ++d) tma_store_3d(&dst.m[d], staging, col0, row0, tc.z);
               bulk_commit_group();
@@ -360,6 +403,83 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     if (p.n_dst != 0 && lane == 0) bulk_wait_group<0>();  // every store of this warp has been performed
+  } else if constexpr (kFwd) {
+    // ------------------------------------------------------------ forwarders (both CTAs)
+    const int fw = warp - 2 - Cfg::EPI_WARPS;
+    const int np = p.n_peers;
+    bool ok = true;
+    // Entering the call: this GPU's earlier work on the stream is complete, so the peers may overwrite its C.
+    if (blockIdx.x == 0 && fw == 0 && lane < np) flag_store_release_sys(p.peer_flags[lane] + FLAG_READY + p.my_rank, p.epoch);
+    // No remote store before every peer has entered the call.
+    if (lane < np) ok = flag_wait_ge(p.flags + FLAG_READY + p.peer_rank[lane], p.epoch, &abort_flag, wait_ns);
+    ok = __all_sync(0xffffffffu, ok);
+    constexpr int ROW_BYTES = BN * int(sizeof(OutT));  // this CTA's rows of a tile are ROW_BYTES wide
+    constexpr int CH = ROW_BYTES / 512;                // 16-byte chunks per lane and row
+    constexpr int U = 8 / CH;                          // rows per round: 8 loads in flight per lane
+    uint8_t* const cbase = reinterpret_cast<uint8_t*>(p.C);
+    uint32_t done_tiles = 0;
+    for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
+      ++done_tiles;
+      if (lane == 0) ok = smem_counter_wait_ge(&stored_warps, done_tiles * Cfg::EPI_WARPS, &abort_flag, wait_ns);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      __syncwarp();
+      if (!ok) break;
+      const PairTile tc = pair_tile<Cfg::BM, BN>(p, t);
+      const int row_base = tc.m0 + int(cta_rank) * Cfg::ROWS;
+      const long long tile_off = ((long long)tc.z * p.c_batch_stride + tc.n0) * (long long)sizeof(OutT);
+      for (int r = fw * U; r < Cfg::ROWS; r += Cfg::FWD_WARPS * U) {
+        if (row_base + r >= p.M) break;
+        uint4 v[U][CH];
+        long long off[U][CH];  // byte offset in C, or -1: outside the matrix
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int ch = 0; ch < CH; ++ch) {
+            const int row = row_base + r + u;
+            const int colb = ch * 512 + lane * 16;
+            const bool in = row < p.M && tc.n0 + colb / int(sizeof(OutT)) < p.N;  // rows are 16-byte multiples
+            off[u][ch] = in ? tile_off + (long long)row * p.ldc * (long long)sizeof(OutT) + colb : -1;
+            if (in) v[u][ch] = ld_global_cg_v4(cbase + off[u][ch]);
+          }
+        }
+        if (p.xchg == XCHG_MULTICAST) {
+          uint8_t* const mc = reinterpret_cast<uint8_t*>(p.mc_C);
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch)
+              if (off[u][ch] >= 0) multimem_st_v4(mc + off[u][ch], v[u][ch]);
+        } else {
+          for (int d = 0; d < np; ++d) {
+            uint8_t* const pc = reinterpret_cast<uint8_t*>(p.peer_C[d]);
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+              for (int ch = 0; ch < CH; ++ch)
+                if (off[u][ch] >= 0) st_global_v4(pc + off[u][ch], v[u][ch]);
+          }
+        }
+      }
+    }
+    // Completion. Every forwarder warp checks in (also after a failure, so the counter returns to zero); the last
+    // one of the grid knows that all of this GPU's tiles are on their way, orders them before the DONE flags it
+    // writes to the peers, and waits for the peers' DONE flags: when the kernel ends, the gathered C is complete.
+    __threadfence_system();
+    __syncwarp();
+    // Low half of the counter: warps that have checked in; high half: how many of them gave up.
+    const bool failed = !ok || *reinterpret_cast<volatile int*>(&abort_flag) != 0;
+    uint32_t prev = 0;
+    if (lane == 0) prev = atomicAdd(p.xchg_counter, 1u + (failed ? 0x10000u : 0u));
+    prev = __shfl_sync(0xffffffffu, prev, 0);
+    if ((prev & 0xffffu) == gridDim.x * Cfg::FWD_WARPS - 1) {
+      if (lane == 0) *p.xchg_counter = 0;
+      __threadfence_system();
+      // A failure anywhere on this GPU withholds DONE: the peers' waits then run out as well, and every rank's
+      // status word reports it.
+      const bool good = !failed && (prev >> 16) == 0;
+      if (good && lane < np) flag_store_release_sys(p.peer_flags[lane] + FLAG_DONE + p.my_rank, p.epoch);
+      if (good && lane < np) flag_wait_ge(p.flags + FLAG_DONE + p.peer_rank[lane], p.epoch, &abort_flag, wait_ns);
+    }
   }
 
   // Both CTAs stay resident until every remote barrier signal and paired MMA has landed.
@@ -376,11 +496,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ------------------------------------------------------------------ host side
 namespace {
 
-template <typename OutT, bool kBmn, int kMB>
+template <typename OutT, bool kBmn, int kMB, bool kFwd>
 int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const DstMaps& dst, const GemmParams& p, int pairs,
                 cudaStream_t stream) {
-  using Cfg = PairCfg<kMB>;
-  auto kern = gemm_pair_kernel<OutT, kBmn, kMB>;
+  using Cfg = PairCfg<kMB, kFwd>;
+  auto kern = gemm_pair_kernel<OutT, kBmn, kMB, kFwd>;
   SX_ENSURE_DYN_SMEM(kern, Cfg::DYN_SMEM);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
@@ -400,8 +520,11 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const DstMaps& d
 template <typename OutT, bool kBmn>
 int launch_pair_mb(int mb, const CUtensorMap& tmA, const CUtensorMap& tmB, const DstMaps& dst, const GemmParams& p,
                    int pairs, cudaStream_t stream) {
-  return mb == 2 ? launch_pair<OutT, kBmn, 2>(tmA, tmB, dst, p, pairs, stream)
-                 : launch_pair<OutT, kBmn, 1>(tmA, tmB, dst, p, pairs, stream);
+  if (p.xchg >= XCHG_FORWARD)
+    return mb == 2 ? launch_pair<OutT, kBmn, 2, true>(tmA, tmB, dst, p, pairs, stream)
+                   : launch_pair<OutT, kBmn, 1, true>(tmA, tmB, dst, p, pairs, stream);
+  return mb == 2 ? launch_pair<OutT, kBmn, 2, false>(tmA, tmB, dst, p, pairs, stream)
+                 : launch_pair<OutT, kBmn, 1, false>(tmA, tmB, dst, p, pairs, stream);
 }
 
 }  // namespace
@@ -460,20 +583,43 @@ int launch_gemm_pair(const TcGemmArgs& a, cudaStream_t stream) {
   const bool c_tma_ok = (a.ldc * out_elt) % 16 == 0 && (a.c_batch_stride * out_elt) % 16 == 0 &&
                         reinterpret_cast<uintptr_t>(a.C) % 16 == 0;
   p.n_dst = 0;
+  p.wait_limit_ns = a.wait_limit_ns ? a.wait_limit_ns : WAIT_LIMIT_NS;
   if (a.n_peers > 0 && !c_tma_ok) return SX_ERR_INVALID;
   if (a.n_peers < 0 || a.n_peers > MAX_DST - 1) return SX_ERR_INVALID;
+  p.xchg = a.n_peers > 0 ? (a.xchg ? a.xchg : XCHG_EPILOGUE_TMA) : XCHG_NONE;
+  const bool fwd = p.xchg >= XCHG_FORWARD;
+  if (fwd) {
+    // The forwarders address C by bytes: one batch entry, flags and the completion counter are required.
+    if (a.batch != 1 || a.flags == nullptr || a.xchg_counter == nullptr || a.epoch == 0) return SX_ERR_INVALID;
+    if (p.xchg == XCHG_MULTICAST && (a.mc_C == nullptr || reinterpret_cast<uintptr_t>(a.mc_C) % 16)) return SX_ERR_INVALID;
+    p.n_peers = a.n_peers;
+    p.my_rank = a.my_rank;
+    for (int i = 0; i < a.n_peers; ++i) {
+      if (a.peer_flags[i] == nullptr || a.peer_rank[i] < 0 || a.peer_rank[i] >= 8) return SX_ERR_INVALID;
+      if (p.xchg == XCHG_FORWARD && (a.peer_C[i] == nullptr || reinterpret_cast<uintptr_t>(a.peer_C[i]) % 16))
+        return SX_ERR_INVALID;
+      p.peer_rank[i] = a.peer_rank[i];
+      p.peer_C[i] = const_cast<void*>(a.peer_C[i]);
+      p.peer_flags[i] = a.peer_flags[i];
+    }
+    p.mc_C = a.mc_C;
+    p.flags = a.flags;
+    p.epoch = a.epoch;
+    p.xchg_counter = a.xchg_counter;
+  }
+  const int n_maps = fwd ? 0 : a.n_peers;  // tensor maps of peer buffers are needed by the TMA forwarding only
   if (c_tma_ok && (a.tma_store || a.n_peers > 0)) {
     const CUtensorMapDataType odt = a.out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     uint64_t dims[3] = {(uint64_t)a.N, (uint64_t)a.M, (uint64_t)a.batch};
     uint64_t strides[2] = {(uint64_t)a.ldc * out_elt, (uint64_t)a.c_batch_stride * out_elt};
     uint32_t box[3] = {(uint32_t)(128 / out_elt), 32u, 1u};
-    for (int i = 0; i <= a.n_peers; ++i) {
+    for (int i = 0; i <= n_maps; ++i) {
       const void* base = i == 0 ? a.C : a.peer_C[i - 1];
       if (base == nullptr || reinterpret_cast<uintptr_t>(base) % 16) return SX_ERR_INVALID;
       int rc = encode_tensor_map_3d(&dmaps.m[i], odt, base, dims, strides, box);
       if (rc != SX_OK) return rc;
     }
-    p.n_dst = 1 + a.n_peers;
+    p.n_dst = 1 + n_maps;
   }
   const long long total = (long long)p.batch * p.m_tiles * p.n_tiles;
   const int max_pairs = a.num_sms / 2;

@@ -39,9 +39,37 @@ struct GemmParams {
   int m_tiles, n_tiles, group_m;
   int n_dst;  // 0: epilogue stores straight from registers; >= 1: staged in shared memory and written by TMA
               // to n_dst destinations (the local C first, then the same tile of every peer GPU's C)
-  // shared-memory descriptor fields for a B tile held MN-major (row-major B[K,N])
-  uint32_t b_lbo, b_sbo, b_kstep;
+  // Exchange of a row-sharded product with the other GPUs of the box (pair kernels only; see Exchange below).
+  int xchg;                // Exchange mode
+  int n_peers;             // other ranks (<= 7)
+  int my_rank;
+  int peer_rank[7];        // rank of peer j
+  void* peer_C[7];         // peer j's copy of the region C points at, mapped into this process
+  void* mc_C;              // multicast mapping of that region (XCHG_MULTICAST)
+  int* flags;              // this rank's flag block (FLAG_WORDS ints, written by the peers)
+  int* peer_flags[7];      // peer j's flag block, mapped into this process
+  int epoch;               // collective call number (> 0, the same on every rank)
+  unsigned* xchg_counter;  // device word of this GPU, zero between launches: forwarder warps that have finished
+  unsigned long long wait_limit_ns;  // bound of every device-side wait of this launch
+  int fault_stop_early;    // self-test only: the TMA producer leaves out the last k-block of the first tile
 };
+
+// How the tiles of a row-sharded product reach the other GPUs.
+enum Exchange : int {
+  XCHG_NONE = 0,
+  XCHG_EPILOGUE_TMA = 1,  // each epilogue warp reads its blocks back from the local C (L2) by TMA and TMA-stores them
+                          // to every peer (n_dst - 1 tensor maps); the caller orders the ranks
+  XCHG_FORWARD = 2,       // dedicated forwarder warps copy finished tiles from the local C to every peer with
+                          // 16-byte loads and stores; ranks are ordered by flags inside the kernel
+  XCHG_MULTICAST = 3,     // the same warps store each 16 bytes once, to the multicast mapping (multimem.st): the
+                          // NVSwitch delivers it to every GPU of the group
+};
+
+// Layout of a flag block: READY[r] = rank r has entered collective call `epoch` (everything it did with the previous
+// C is complete, its C may be overwritten); DONE[r] = all of rank r's tiles of call `epoch` have landed here.
+constexpr int FLAG_READY = 0;
+constexpr int FLAG_DONE = 8;
+constexpr int FLAG_WORDS = 16;
 
 // Tensor maps of the output destinations of the TMA-store epilogue (local C, then peers' C).
 constexpr int MAX_DST = 8;

@@ -115,7 +115,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int it = 0; it < iters; ++it) {
           const int seg = it / nkb;
           const int kb = it - seg * nkb;
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) { ok = false; break; }
+          // Self-test of the unwinding (symplex_b200_selftest_wait_timeout): the last k-block is never loaded, so
+          // the MMA thread's wait for it runs out; nothing asynchronous is left in flight by this thread.
+          if (p.fault_stop_early && it == iters - 1) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag, p.wait_limit_ns)) { ok = false; break; }
           uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
@@ -149,19 +152,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(kKind == 0 ? 1 : 2, false, kBmn, BM, BN);
       constexpr uint64_t a_hi = make_smem_desc_hi(16, 1024);
-      const uint64_t b_hi = kBmn ? make_smem_desc_hi(p.b_lbo, p.b_sbo) : make_smem_desc_hi(16, 1024);
-      const uint32_t b_kstep = kBmn ? p.b_kstep : 32u;
+      // B held MN-major: shared-memory rows are 128 B of N; 8 K-rows form a 1024-B swizzle atom (SBO);
+      // successive 128-B column chunks of the tile are separate TMA boxes of BK K-rows each (LBO).
+      constexpr uint64_t b_hi = kBmn ? make_smem_desc_hi(BK * 128, 1024) : make_smem_desc_hi(16, 1024);
+      constexpr uint32_t b_kstep = kBmn ? Cfg::UMMA_K * 128 : 32u;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, &abort_flag)) break;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, &abort_flag, p.wait_limit_ns)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int it = 0; it < iters; ++it) {
-          if (!mbar_wait(&full_bar[stage], phase, &abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&full_bar[stage], phase, &abort_flag, p.wait_limit_ns)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
           const uint32_t b_addr = a_addr + Cfg::A_BYTES;
@@ -186,7 +191,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const TileCoord tc = tile_coord<BM, BN>(p, t);
-      if (!mbar_wait(&acc_full[acc], acc_phase, &abort_flag)) break;
+      if (!mbar_wait(&acc_full[acc], acc_phase, &abort_flag, p.wait_limit_ns)) break;
       tc_fence_after_sync();
       const int row = tc.m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -301,11 +306,8 @@ int launch_gemm_tc(const TcGemmArgs& a, cudaStream_t stream) {
   p.m_tiles = (int)((a.M + 127) / 128);
   p.n_tiles = (int)((a.N + bn - 1) / bn);
   p.group_m = a.group_m > 0 ? a.group_m : 8;
-  // B held MN-major: shared-memory rows are 128 B of N; 8 K-rows form a 1024-B swizzle atom (SBO);
-  // successive 128-B column chunks of the tile are separate TMA boxes of bk K-rows each (LBO).
-  p.b_lbo = a.dbg_lbo ? a.dbg_lbo : (uint32_t)(bk * 128);
-  p.b_sbo = a.dbg_sbo ? a.dbg_sbo : 1024u;
-  p.b_kstep = a.dbg_kstep ? a.dbg_kstep : (uint32_t)((32 / elt) * 128);
+  p.wait_limit_ns = a.wait_limit_ns ? a.wait_limit_ns : WAIT_LIMIT_NS;
+  p.fault_stop_early = a.fault_stop_early;
 
   const long long total = (long long)p.batch * p.m_tiles * p.n_tiles;
   const int grid = (int)(total < a.num_sms ? total : a.num_sms);

@@ -63,7 +63,17 @@ struct TcGemmArgs {
   int tma_store;               // pair kernels: stage the output in shared memory and write it with TMA
   int n_peers;                 // pair kernels: also write every tile to the same offset of these buffers
   const void* peer_C[7];       //   (other GPUs' copies of C, mapped into this process)
-  uint32_t dbg_lbo, dbg_sbo, dbg_kstep;  // 0 = use the library's values
+  // Exchange mode (Exchange in gemm_params.h; 0 with n_peers > 0 means XCHG_EPILOGUE_TMA). The forwarder modes
+  // order the ranks inside the kernel and need the flag blocks, the call number and this GPU's counter word.
+  int xchg;
+  int my_rank, peer_rank[7];
+  void* mc_C;
+  int* flags;
+  int* peer_flags[7];
+  int epoch;
+  unsigned* xchg_counter;
+  unsigned long long wait_limit_ns;  // 0 = the default bound (2 s)
+  int fault_stop_early;              // single-CTA kernel, self-test only
 };
 
 int launch_gemm_tc(const TcGemmArgs& a, cudaStream_t stream);
@@ -108,6 +118,10 @@ int launch_repack_16(const void* in, long long ld_in, long long batch_stride_in,
 // fp32 -> bf16 (round to nearest even), same shape conventions as launch_repack_16.
 int launch_f32_to_bf16(const float* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
                        int rows, int cols, int batch, cudaStream_t stream);
+
+// Double-precision C = A.B in the reference's cache_tiled_dgemm summation order (dgemm.cu). Leading dimensions in elements.
+int launch_dgemm(const double* A, long long lda, const double* B, long long ldb, double* C, long long ldc, int M, int N,
+                 int K, cudaStream_t stream);
 
 // Static shape of one GEMM kernel variant, for the planning queries of the C ABI (no GPU needed).
 struct KernelShape {

@@ -13,6 +13,12 @@
 // ordering between them, or different host threads) race on it - serialise them. The planes are rewritten in
 // full (padding columns included) by each call before they are read, so nothing has to be cleared between
 // calls and stale contents of an earlier, larger problem are never observed.
+//
+// Failures: the kernels' bounded waits report through a status word that is a second variable of the library image
+// (below), not through the pooled entry points' word. symplex_b200_noalloc_status reads and clears it, again without
+// allocating; a caller that never asks never learns that a wait ran out.
+// "Calls no allocating routine" is about this code: the first CUDA call of a process on a device creates its
+// context and loads the library's kernels, which is also when the 16 MiB array becomes resident.
 #include <mutex>
 
 #include "../../include/symplex_b200.h"
@@ -108,4 +114,23 @@ extern "C" int symplex_b200_sgemm_noalloc(const float* A, const float* B, float*
   rc = launch_gemm_tf32x3(g, s);
   if (rc != SX_OK) return set_last_error(rc, "sgemm_noalloc: GEMM kernel launch failed");
   return SX_OK;
+}
+
+extern "C" int symplex_b200_noalloc_status(void* stream) {
+  NoAllocDevice* d = nullptr;
+  int rc = noalloc_setup(&d);
+  if (rc != SX_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int status = 0;  // a pageable stack word: the copy is staged by the driver, nothing is allocated here
+  if (cudaMemcpyAsync(&status, d->status, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaStreamSynchronize(s) != cudaSuccess) {
+    cudaGetLastError();
+    return set_last_error(SX_ERR_EXEC, "noalloc_status: reading the status word failed");
+  }
+  if (status == 0) return SX_OK;
+  if (cudaMemsetAsync(d->status, 0, sizeof(int), s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
+    cudaGetLastError();
+    return set_last_error(SX_ERR_EXEC, "noalloc_status: clearing the status word failed");
+  }
+  return set_last_error(SX_ERR_TIMEOUT, "sgemm_noalloc: a device-side wait timed out; the output is not valid");
 }

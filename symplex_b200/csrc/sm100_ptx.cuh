@@ -120,12 +120,13 @@ __device__ __forceinline__ bool mbar_try_wait_cluster_acq(uint64_t* bar, uint32_
   return ok != 0;
 }
 
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s: far beyond any legitimate wait
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // default bound, 2 s: far beyond any legitimate wait
 
 // Bounded wait. `abort_flag` is a CTA-shared int: set by whoever times out, polled by
 // everyone else so that the whole CTA unwinds within one polling interval.
 template <bool kClusterAcquire = false>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = WAIT_LIMIT_NS) {
   if (kClusterAcquire ? mbar_try_wait_cluster_acq(bar, parity) : mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -134,12 +135,83 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_LIMIT_NS) {
+      else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }
     }
   }
+}
+
+// ---------------------------------------------------------------- flags and counters (exchange between GPUs)
+// A counter in this CTA's shared memory that producers bump after their global writes have been performed and a
+// consumer polls: release / acquire at CTA scope.
+__device__ __forceinline__ void smem_counter_add_release(uint32_t* ctr, uint32_t v) {
+  asm volatile("red.release.cta.shared::cta.add.u32 [%0], %1;" ::"r"(smem_u32(ctr)), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t smem_counter_load_acquire(const uint32_t* ctr) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(ctr)) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool smem_counter_wait_ge(const uint32_t* ctr, uint32_t want, volatile int* abort_flag,
+                                                     uint64_t limit_ns) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    if (smem_counter_load_acquire(ctr) >= want) return true;
+    __nanosleep(64);
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+// A flag word in global memory that another GPU writes over NVLink (system scope).
+__device__ __forceinline__ void flag_store_release_sys(int* flag, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(v) : "memory");
+}
+__device__ __forceinline__ int flag_load_acquire_sys(const int* flag) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+  return v;
+}
+// Bounded wait until *flag >= want. On expiry raises the CTA's abort flag and returns false.
+__device__ __forceinline__ bool flag_wait_ge(const int* flag, int want, volatile int* abort_flag, uint64_t limit_ns) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    if (flag_load_acquire_sys(flag) - want >= 0) return true;
+    __nanosleep(100);
+    if ((it & 31u) == 0u) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+// 16-byte copies for the forwarder warps: loads that bypass L1 (the data was just written through L2 by TMA), plain
+// stores to a peer's mapped memory, and one store to a multicast mapping that the NVSwitch replicates to every GPU
+// bound to it (stores only: nothing in this library loads from a multicast or peer address).
+__device__ __forceinline__ uint4 ld_global_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_global_v4(void* p, const uint4& v) {
+  asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
 }
 
 // ---------------------------------------------------------------- TMA

@@ -5,14 +5,22 @@ Mirrors the planning types of the reference (``include/symplex/distributed/shard
 turns the plan into an executed computation: one process per GPU, the tcgen05 GEMM library for the math,
 ``torch.distributed`` for the plumbing (process group, symmetric-memory rendezvous, barriers).
 
-Two ways to exchange C:
+Ways to exchange C:
 
-``exchange="peer_store"`` (default on GPUs)
-    C lives in symmetric memory (every rank can address every rank's copy). The GEMM kernel's epilogue
-    writes each finished tile to the local C and, by TMA stores over NVLink, to the same place in every
-    peer's C (``symplex_b200_gemm_peers``): the all-gather is fused into the GEMM and overlaps it tile by
-    tile; there is no separate collective kernel competing for SMs. A barrier before (peers are done
-    reading the previous result) and after (everybody's tiles have landed) orders the ranks.
+``exchange="peer_store"`` (default on GPUs with bf16 inputs)
+    C lives in symmetric memory (every rank can address every rank's copy). ONE kernel per rank
+    (``symplex_b200_sharded_gemm``) computes the local rows and gathers C: the epilogue writes each finished
+    tile to the local C, and dedicated forwarder warps of the same kernel copy it from there (an L2 hit) to
+    the same place in every peer's C with 16-byte stores over NVLink, so link back-pressure never reaches the
+    warps that feed the tensor cores. The ranks order themselves with flags in each other's memory (a rank's
+    C is not overwritten before that rank has entered the call; the kernel ends when every peer's tiles have
+    landed) - no host barrier, no collective kernel competing for SMs.
+``exchange="multicast"``
+    Same kernel, but the forwarders store each tile ONCE to a multicast mapping of C (``multimem.st``) and the
+    NVSwitch delivers it to every GPU: 1/(world-1) of the egress of ``peer_store``.
+``exchange="epilogue_tma"``
+    The first fused design, kept for comparison: the epilogue warps forward their own blocks with TMA stores
+    (``symplex_b200_gemm_peers``), bracketed by two one-element all-reduces.
 ``exchange="nccl"``
     The local rows are computed in ``chunks`` pieces and each piece is gathered in place by an asynchronous
     ``all_gather_into_tensor`` while the next piece computes (also the path the CPU/gloo tests drive).
@@ -134,8 +142,21 @@ def pick_chunks(M: int, world_size: int, requested: Optional[int] = None) -> int
     return 1
 
 
+class ShardedStepTimeout(RuntimeError):
+    """A rank of the group did not enter a sharded step before the deadline."""
+
+
+def _group_store(group):
+    """The key-value store behind a process group (the default group's store for ``None``)."""
+    import torch.distributed as dist
+    from torch.distributed import distributed_c10d as c10d
+    pg = group if group is not None else dist.group.WORLD
+    return c10d._get_process_group_store(pg)
+
+
 class RowShardedGemm:
-    """C = act(alpha * A.B + bias) with A row-sharded, B replicated, C all-gathered (bf16 or fp32).
+    """C = act(alpha * A.B + bias) with A row-sharded, B replicated, C all-gathered (bf16; fp32 through the NCCL
+    exchange).
 
     One instance per process; ``__call__`` takes this rank's rows of A (``[M/world, K]``, ordered as
     ``local_row_index()`` says), the full B, and returns the full C on every rank. The all-gather of
@@ -143,8 +164,12 @@ class RowShardedGemm:
     c+1 computes; the call returns after all chunks have been gathered (stream-ordered, no host sync).
     """
 
+    EXCHANGES = ("peer_store", "multicast", "epilogue_tma", "nccl")
+    FUSED = ("peer_store", "multicast", "epilogue_tma")
+
     def __init__(self, M: int, N: int, K: int, *, group=None, chunks: Optional[int] = None, activation=None,
-                 b_layout: int = 0, local_gemm: Optional[Callable] = None, exchange: Optional[str] = None):
+                 b_layout: int = 0, local_gemm: Optional[Callable] = None, exchange: Optional[str] = None,
+                 wait_limit_ms: int = 0, step_deadline_s: Optional[float] = None):
         import torch.distributed as dist
         self.group = group
         if dist.is_available() and dist.is_initialized():
@@ -155,16 +180,24 @@ class RowShardedGemm:
         if M % self.world != 0:
             raise ValueError(f"M={M} rows do not split evenly over {self.world} ranks")
         self.M, self.N, self.K = M, N, K
+        # Default: the fused exchange; a first call with float32 inputs (which the fused kernels do not take)
+        # moves a defaulted instance to the NCCL pipeline.
+        self._exchange_defaulted = exchange is None
         if exchange is None:
             exchange = "nccl" if (local_gemm is not None or self.world == 1) else "peer_store"
-        if exchange not in ("peer_store", "nccl"):
-            raise ValueError("exchange must be 'peer_store' or 'nccl'")
+        if exchange not in self.EXCHANGES:
+            raise ValueError(f"exchange must be one of {self.EXCHANGES}")
         self.exchange = exchange
-        if exchange == "peer_store":
-            chunks = 1  # one GEMM launch over all local rows; the exchange rides on its epilogue
+        self._requested_chunks = chunks
+        if exchange in self.FUSED:
+            chunks = 1  # one GEMM launch over all local rows; the exchange rides on the same kernel
         self._symm_out = None
         self._peer_ptrs = None
         self._flag = None
+        self._comm = None
+        self.wait_limit_ms = wait_limit_ms
+        self.step_deadline_s = step_deadline_s
+        self._steps = 0
         self.chunks = pick_chunks(M, self.world, chunks)
         self.blocks = owned_row_blocks(M, self.world, self.rank, self.chunks)
         self.activation = activation
@@ -188,15 +221,36 @@ class RowShardedGemm:
         import torch.distributed._symmetric_memory as symm_mem
         if self._symm_out is not None and self._symm_out.dtype == dtype:
             return self._symm_out
-        # plain peer mappings are all this exchange needs; keep NVLink multicast objects out of it
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        # plain peer mappings are all the unicast exchanges need; NVLink multicast objects are created only
+        # for exchange="multicast"
+        if self.exchange != "multicast":
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         buf = symm_mem.empty((self.M, self.N), dtype=dtype, device=device)
+        flags = symm_mem.empty((64,), dtype=torch.int32, device=device)
+        flags.zero_()
         grp = self.group if self.group is not None else dist.group.WORLD
         hdl = symm_mem.rendezvous(buf, grp)
+        fhdl = symm_mem.rendezvous(flags, grp)
         self._symm_out = buf
+        self._symm_flags = flags
         self._peer_ptrs = [int(p) for p in hdl.buffer_ptrs]
-        self._hdl = hdl
+        self._hdl, self._fhdl = hdl, fhdl
         self._flag = torch.zeros(1, device=device, dtype=torch.int32)
+        from . import _capi
+        comm = _capi.Comm()
+        comm.rank, comm.world = self.rank, self.world
+        for r in range(self.world):
+            comm.c_base[r] = int(hdl.buffer_ptrs[r])
+            comm.flags[r] = int(fhdl.buffer_ptrs[r])
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        if self.exchange == "multicast" and mc == 0:
+            raise RuntimeError("exchange='multicast' needs an NVLink multicast mapping of C; this box gave none")
+        comm.c_multicast = mc if self.exchange == "multicast" else None
+        comm.epoch = 0
+        comm.wait_limit_ms = int(self.wait_limit_ms)
+        self._comm = comm
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)  # every rank's flags are zero before anybody's kernel writes one
         return buf
 
     def _barrier(self):
@@ -204,18 +258,65 @@ class RowShardedGemm:
         import torch.distributed as dist
         dist.all_reduce(self._flag, group=self.group)
 
-    def _call_peer_store(self, A_local, B, bias, out_dtype):
-        from . import gemm
+    def _call_fused(self, A_local, B, bias, out_dtype):
+        """One kernel per rank computes and gathers (``symplex_b200_sharded_gemm``)."""
+        import ctypes
+
+        import torch
+
+        from . import _capi, gemm, make_desc
         out = self.output_buffer(out_dtype, A_local.device)
-        row0, nrows = self.blocks[0]
-        elt = out.element_size()
-        mine = out[row0:row0 + nrows]
-        peers = [p + row0 * self.N * elt for r, p in enumerate(self._peer_ptrs) if r != self.rank]
-        self._barrier()  # every rank has finished with the previous contents of C
-        gemm(A_local, B, bias=bias, activation=self.activation, out=mine, b_layout=self.b_layout,
-             peer_outputs=peers)
-        self._barrier()  # every rank's tiles have been written everywhere
+        if self.exchange == "epilogue_tma":
+            row0, nrows = self.blocks[0]
+            elt = out.element_size()
+            mine = out[row0:row0 + nrows]
+            peers = [p + row0 * self.N * elt for r, p in enumerate(self._peer_ptrs) if r != self.rank]
+            self._barrier()  # every rank has finished with the previous contents of C
+            gemm(A_local, B, bias=bias, activation=self.activation, out=mine, b_layout=self.b_layout,
+                 peer_outputs=peers)
+            self._barrier()  # every rank's tiles have been written everywhere
+            return out
+        if A_local.dtype != torch.bfloat16 or B.dtype != torch.bfloat16:
+            raise ValueError("the fused exchanges take bfloat16 inputs; use exchange='nccl' for float32")
+        key = (out_dtype, self.activation, self.b_layout)
+        if getattr(self, "_desc_key", None) != key:
+            self._desc = make_desc(self.M, self.N, self.K, _capi.DT_BF16,
+                                   _capi.DT_F32 if out_dtype == torch.float32 else _capi.DT_BF16,
+                                   b_layout=self.b_layout, activation=self.activation)
+            self._desc_key = key
+        A_local = A_local.contiguous()
+        B = B.contiguous()
+        mode = _capi.XCHG_MULTICAST if self.exchange == "multicast" else _capi.XCHG_UNICAST
+        s = torch.cuda.current_stream(A_local.device).cuda_stream
+        rc = _capi.load().symplex_b200_sharded_gemm(
+            ctypes.byref(self._desc), A_local.data_ptr(), B.data_ptr(), bias.data_ptr() if bias is not None else None,
+            ctypes.byref(self._comm), mode, s)
+        _capi.check(rc)
         return out
+
+    def _host_handshake(self):
+        """Before a step is launched, every rank posts its step number in the process group's store and waits,
+        with a deadline, until all ranks have posted it. A rank that never enters the step (it raised, hung on
+        the host, or exited) is noticed HERE, on the host, as a ``ShardedStepTimeout`` - not as a collective
+        that blocks for ever. Enabled by ``step_deadline_s``."""
+        import time
+
+        import torch.distributed as dist
+        self._steps += 1
+        if self.step_deadline_s is None or self.world == 1:
+            return
+        store = _group_store(self.group)
+        key = f"symplex_b200/row_sharded_gemm/{id(self.group) if self.group is not None else 0}/step{self._steps}"
+        store.add(key, 1)
+        deadline = time.monotonic() + float(self.step_deadline_s)
+        while True:
+            if store.add(key, 0) >= self.world:
+                return
+            if time.monotonic() > deadline:
+                raise ShardedStepTimeout(
+                    f"rank {self.rank}: only {store.add(key, 0)} of {self.world} ranks entered step {self._steps} "
+                    f"within {self.step_deadline_s} s")
+            time.sleep(0.002)
 
     def _gemm_chunk(self, A_blk, B, bias, out_blk):
         if self._local_gemm is not None:
@@ -230,12 +331,18 @@ class RowShardedGemm:
         m_loc = self.M // self.world
         if tuple(A_local.shape) != (m_loc, self.K):
             raise ValueError(f"A_local must be [{m_loc}, {self.K}], got {tuple(A_local.shape)}")
-        if self.exchange == "peer_store" and self.world > 1:
+        if (self._exchange_defaulted and self.exchange in self.FUSED and self.world > 1
+                and A_local.dtype != torch.bfloat16):
+            self.exchange = "nccl"
+            self.chunks = pick_chunks(self.M, self.world, self._requested_chunks)
+            self.blocks = owned_row_blocks(self.M, self.world, self.rank, self.chunks)
+        self._host_handshake()
+        if self.exchange in self.FUSED and self.world > 1:
             dt = out.dtype if out is not None else (out_dtype if out_dtype is not None else A_local.dtype)
             if out is not None and (self._symm_out is None or out.data_ptr() != self._symm_out.data_ptr()):
-                raise ValueError("with exchange='peer_store' the result lives in output_buffer(); pass out=None "
+                raise ValueError("with a fused exchange the result lives in output_buffer(); pass out=None "
                                  "or that buffer")
-            return self._call_peer_store(A_local, B, bias, dt)
+            return self._call_fused(A_local, B, bias, dt)
         if out is None:
             dt = out_dtype if out_dtype is not None else A_local.dtype
             out = torch.empty((self.M, self.N), device=A_local.device, dtype=dt)

@@ -48,3 +48,19 @@ def lib():
         from symplex_b200.build import build_library
         build_library()
     return _capi.load()
+
+
+@pytest.fixture
+def set_option(lib):
+    """``set_option(name, value)``: a tuning override of the library for the duration of one test."""
+    saved = {}
+
+    def _set(name, value):
+        key = name.encode()
+        if key not in saved:
+            saved[key] = lib.symplex_b200_get_option(key)
+        assert lib.symplex_b200_set_option(key, int(value)) == 0
+
+    yield _set
+    for key, old in saved.items():
+        lib.symplex_b200_set_option(key, old)

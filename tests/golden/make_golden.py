@@ -1,12 +1,16 @@
 """Regenerate tests/golden/*.npz from the reference itself (run where the reference checkout exists).
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 Two sources, both the reference's own code, neither modified:
   * its Python package imported in pure-Python mode (python/symplex): ``matmul_jit`` / ``matmul_tiled`` /
     ``matmul`` and the DeviceArray activations ``gelu`` / ``relu`` / ``sigmoid`` / ``tanh``;
   * its C kernel library kernels/matmul.c compiled unchanged (oracle/_ref/libsymplex_kernels.so, built by
     oracle/Makefile): ``symplex_matmul_f32`` and ``symplex_matmul_tiled_f32``.
+  * fused elementwise chains (the programs the reference's interpreter simd_fused_elementwise_f32 / _f64 runs,
+    rust-engine/src/x86_emitter.rs:1937-2470) evaluated by the reference's own Python layer: ``@symplex.jit``
+    functions which, without the native core, execute their trace op by op through NumPy
+    (python/symplex/_jit.py:1329-1330, 1740-1760) - the same separately rounded IEEE operations per element.
 Inputs are seeded; every array needed to replay a case is stored next to the reference's output.
 """
 import ctypes
@@ -17,7 +21,9 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit(__doc__)
+REF = sys.argv[1]
 
 
 def main():
@@ -73,6 +79,31 @@ def main():
     out["fused_X"], out["fused_W"], out["fused_b"] = X, W, b
     out["fused_gelu"] = np.asarray(lin.gelu()._data, dtype=np.float32)
     out["fused_relu"] = np.asarray(lin.relu()._data, dtype=np.float32)
+
+    # Fused elementwise chains through @symplex.jit (NumPy executor). n = 1003: not a multiple of 8, so the
+    # interpreter's vector body and scalar tail are both exercised, and max / min meet the reference's tail rule.
+    import contextlib
+    import io
+    n = 1003
+    for tag, dt in (("f32", np.float32), ("f64", np.float64)):
+        x, a, b, c = (rng.uniform(-1, 1, n).astype(dt) for _ in range(4))
+        pos = rng.uniform(0.1, 3.0, n).astype(dt)
+        out[f"fe_{tag}_x"], out[f"fe_{tag}_a"], out[f"fe_{tag}_b"], out[f"fe_{tag}_c"] = x, a, b, c
+        out[f"fe_{tag}_pos"] = pos
+
+        def run(fn, *args):
+            with contextlib.redirect_stdout(io.StringIO()), contextlib.redirect_stderr(io.StringIO()):
+                r = symplex.jit(fn)(*args)
+            return np.asarray(getattr(r, "_data", r))
+
+        out[f"fe_{tag}_axpb"] = run(lambda x: x * 2.0 + 1.0, x)
+        out[f"fe_{tag}_axpb_sum"] = np.float64(run(lambda x: (x * 2.0 + 1.0).sum(), x))
+        out[f"fe_{tag}_mul_add_relu"] = run(lambda a, b, c: symplex.relu(a * b + c), a, b, c)
+        out[f"fe_{tag}_sub_div"] = run(lambda a, b, pos: (a - b) / pos, a, b, pos)
+        out[f"fe_{tag}_libm"] = run(lambda x, pos: symplex.tanh(symplex.exp(x) * symplex.sqrt(pos)) + symplex.sigmoid(x),
+                                    x, pos)
+        out[f"fe_{tag}_max"] = np.float64(run(lambda a, b: (a * b).max(), a, b))
+        out[f"fe_{tag}_min"] = np.float64(run(lambda a, b: (a + b).min(), a, b))
 
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **out)

@@ -18,7 +18,7 @@ def _declared_functions():
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     text = "\n".join(line for line in text.splitlines() if not line.lstrip().startswith("#"))
     names = re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{}]*\)\s*;", text)
-    return sorted(set(n for n in names if n.startswith(("symplex_", "blas_", "cache_tiled_"))))
+    return sorted(set(n for n in names if n.startswith(("symplex_", "blas_", "cache_tiled_", "poly_"))))
 
 
 def test_header_declares_functions():

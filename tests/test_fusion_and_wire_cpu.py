@@ -60,7 +60,9 @@ def test_tensor_matmul_record_layout_and_errors(lib):
     assert f(rec[:20], 20, slots, 3) == _capi.ERR_INVALID
     assert f(_record(2, 0, 1, 4, 4, 4, 9, 0, 0, opcode=0x70), 34, slots, 3) == _capi.ERR_INVALID
     assert f(_record(5, 0, 1, 4, 4, 4, 9, 0, 0), 34, slots, 3) == _capi.ERR_INVALID   # slot out of range
-    assert f(_record(2, 0, 1, 4, 4, 4, 10, 0, 0), 34, slots, 3) == _capi.ERR_INVALID  # F64 not on this path
+    assert f(_record(2, 0, 1, 4, 4, 4, 12, 0, 0), 34, slots, 3) == _capi.ERR_INVALID  # element type not on this path
+    assert f(_record(2, 0, 1, 4, 4, 4, 10, 0, 1), 34, slots, 3) == _capi.ERR_INVALID  # F64 takes a row-major rhs
+    assert f(_record(2, 0, 1, 4, 4, 4, 10, 0, 0), 34, slots, 3) == _capi.ERR_INVALID  # F64: null slot pointers
     assert f(_record(2, 0, 1, 4, 4, 4, 9, 1, 0), 34, slots, 3) == _capi.ERR_INVALID   # col-major lhs
     assert f(_record(2, 0, 1, 4, 4, 4, 9, 0, 7), 34, slots, 3) == _capi.ERR_INVALID
     assert f(_record(2, 0, 1, 0, 4, 4, 9, 0, 0), 34, slots, 3) == 0                   # zero dimension: no-op

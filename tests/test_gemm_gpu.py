@@ -356,7 +356,7 @@ def test_strided_host_output(lib, oracle):
 
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
-def test_host_path_row_chunked_pipeline(lib, oracle, dtype, monkeypatch):
+def test_host_path_row_chunked_pipeline(lib, oracle, dtype):
     """Large host-buffer problems are copied and computed in row chunks on three streams; the result must be the
     one the single-shot path gives (rows are independent)."""
     rng = np.random.default_rng(31)
@@ -374,15 +374,12 @@ def test_host_path_row_chunked_pipeline(lib, oracle, dtype, monkeypatch):
         C_h = torch.empty(M, N, dtype=torch.float32)
         d = sx.make_desc(M, N, K, activation="relu")
     results = []
-    for env in ({"SYMPLEX_B200_PIPELINE_MB": "1"}, {"SYMPLEX_B200_NO_PIPELINE": "1"}):
-        for k, v in env.items():
-            monkeypatch.setenv(k, v)
-        C_h.fill_(float("nan"))
-        before = sx.launch_count()
-        sx.gemm_host(d, A_h.data_ptr(), B_h.data_ptr(), C_h.data_ptr(), bias.ctypes.data)
-        results.append((C_h.float().numpy().copy(), sx.launch_count() - before))
-        for k in env:
-            monkeypatch.delenv(k)
+    for name, value in (("pipeline_mb", 1), ("pipeline", 0)):
+        with _capi.option(name, value):
+            C_h.fill_(float("nan"))
+            before = sx.launch_count()
+            sx.gemm_host(d, A_h.data_ptr(), B_h.data_ptr(), C_h.data_ptr(), bias.ctypes.data)
+            results.append((C_h.float().numpy().copy(), sx.launch_count() - before))
     (chunked, n_chunked), (single, n_single) = results
     assert n_chunked >= 4 * n_single - 4, "the chunked path should have launched one GEMM per row chunk"
     # Full chunks run the kernel the single-shot call runs: the same bits. The ragged last chunk (100 rows) is a
@@ -395,6 +392,69 @@ def test_host_path_row_chunked_pipeline(lib, oracle, dtype, monkeypatch):
     ref = oracle.epilogue(oracle.matmul_rows(Ar, Br, rows), bias=bias, act=_capi.ACT_RELU)
     tol = TOL_BF16 if dtype == "bf16" else TOL_F32
     assert rel_frobenius(chunked[rows], oracle.bf16_round(ref) if dtype == "bf16" else ref) <= tol
+
+
+def test_headline_bf16_8192_cube_bias_gelu(lib, oracle):
+    """The shape the 70 %-of-peak target is quoted on: 8192^3, bf16, bias + GELU fused, one kernel (exactly two waves
+    of 512 x 256 pair tiles). Oracle on 64 sampled rows plus the whole-output checksum identity without the epilogue."""
+    rng = np.random.default_rng(8192)
+    n = 8192
+    X = oracle.bf16_round(rng.normal(0, 0.02, (n, n)).astype(np.float32))
+    W = oracle.bf16_round(rng.normal(0, 0.02, (n, n)).astype(np.float32))
+    b = rng.normal(0, 0.02, n).astype(np.float32)
+    tX, tW = _bf16_t(X), _bf16_t(W)
+    before = sx.launch_count()
+    Y = _run(tX, tW, bias=torch.from_numpy(b).to(DEV), activation="gelu")
+    assert sx.launch_count() - before == 1
+    rows = np.sort(rng.choice(n, 64, replace=False))
+    ref = oracle.bf16_round(oracle.epilogue(oracle.matmul_rows(X, W, rows), bias=b, act=_capi.ACT_GELU))
+    got = Y[torch.from_numpy(rows).to(DEV)].float().cpu().numpy()
+    assert rel_frobenius(got, ref) <= TOL_BF16
+    plain = _run(tX, tW, out_dtype=torch.float32).cpu().numpy()
+    _checksum_identity(plain, X, W, 1e-5)
+
+
+@pytest.mark.parametrize("chain,alpha", [
+    (["matmul", "mul", "add", "gelu"], 0.5), (["matmul", "add", "relu"], 1.0), (["matmul", "silu"], 1.0),
+    (["matmul", "add"], 1.0), (["matmul", "mul", "add", "tanh", "softmax"], 2.0),
+])
+def test_fusion_chain_to_descriptor_to_kernel(lib, oracle, chain, alpha):
+    """An op list goes through the library's fusion discovery (symplex_b200_discover_fusions), the matched chain is
+    compiled into the epilogue fields of a descriptor (symplex_b200_compile_epilogue), and that descriptor runs as
+    ONE kernel whose result is the oracle's matmul followed by the same ops."""
+    import json
+    M, N, K = 384, 320, 200
+    rng = np.random.default_rng(len(chain))
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    ops = [(name, [M, N], "fp32") for name in chain]
+    arr, _keep = _capi.pack_fusion_ops(ops)
+    buf = ctypes.create_string_buffer(4096)
+    assert lib.symplex_b200_discover_fusions(arr, len(ops), buf, 4096) > 0
+    found = json.loads(buf.value.decode())["boundaries"]
+    d = sx.make_desc(M, N, K)
+    consumed, has_bias, has_scale = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+    assert lib.symplex_b200_compile_epilogue(arr, len(ops), 0, ctypes.byref(d), ctypes.byref(consumed),
+                                             ctypes.byref(has_bias), ctypes.byref(has_scale)) == 0
+    fusable = [c for c in chain if c != "softmax"]
+    assert consumed.value == len(fusable)
+    assert [b["op_indices"] for b in found] == [list(range(len(fusable)))] and found[0]["pattern"] == "MatMulBiasReLU"
+    assert bool(has_bias.value) == ("add" in chain) and bool(has_scale.value) == ("mul" in chain)
+    if has_scale.value:
+        d.alpha = alpha
+    tA, tB = torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV)
+    tb = torch.from_numpy(bias).to(DEV)
+    C = torch.full((M, N), float("nan"), device=DEV)
+    before = sx.launch_count()
+    rc = lib.symplex_b200_gemm(ctypes.byref(d), tA.data_ptr(), tB.data_ptr(), C.data_ptr(),
+                               tb.data_ptr() if has_bias.value else None, None, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _capi.last_error()
+    sx.sync_status()
+    assert sx.launch_count() - before == 1
+    ref = oracle.epilogue(oracle.jit_parallel_matmul(A, B), alpha=alpha if has_scale.value else 1.0,
+                          bias=bias if has_bias.value else None, act=d.activation)
+    assert rel_frobenius(C.cpu().numpy(), ref) <= TOL_F32
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
@@ -414,13 +474,13 @@ def test_peer_outputs_receive_every_tile(lib, shape, out_dtype):
         assert torch.equal(p, want)
 
 
-def test_tma_store_and_direct_store_epilogues_agree(lib, monkeypatch):
+def test_tma_store_and_direct_store_epilogues_agree(lib):
     g = torch.Generator(device=DEV).manual_seed(42)
     A = torch.randn(2048, 512, device=DEV, generator=g).to(torch.bfloat16)
     B = torch.randn(512, 1000, device=DEV, generator=g).to(torch.bfloat16)  # ragged N: TMA clips the last block
     staged = _run(A, B, activation="gelu")
-    monkeypatch.setenv("SYMPLEX_B200_TMA_STORE", "0")
-    direct = _run(A, B, activation="gelu")
+    with _capi.option("tma_store", 0):
+        direct = _run(A, B, activation="gelu")
     assert torch.equal(staged, direct)
 
 
@@ -492,10 +552,10 @@ def test_plan_describes_what_is_launched(lib, M, N, K, dtype, batch):
     (200, 100, 300, 1),      # ragged edges; 10 k-blocks split 3,3,2,2
     (96, 64, 1056, 100),     # 100 tiles on 37 clusters: each cluster loops over several tiles
 ])
-def test_fp32_split_k_over_a_cluster(lib, oracle, monkeypatch, split, M, N, K, batch):
+def test_fp32_split_k_over_a_cluster(lib, oracle, set_option, split, M, N, K, batch):
     """The cluster split-K variants of the fused fp32 kernel (partials exchanged over distributed shared memory)
     must meet the same 1e-5 bound as the unsplit kernel, with and without a fused epilogue, for both B layouts."""
-    monkeypatch.setenv("SYMPLEX_B200_F32_SPLITK", str(split))
+    set_option("f32_split_k", split)
     rng = np.random.default_rng(7)
     shape_a = (batch, M, K) if batch > 1 else (M, K)
     shape_b = (batch, K, N) if batch > 1 else (K, N)
@@ -517,8 +577,8 @@ def test_fp32_split_k_over_a_cluster(lib, oracle, monkeypatch, split, M, N, K, b
     assert rel_frobenius(got, np.maximum(ref + bias, 0)) <= 1e-5
 
 
-def test_fp32_split_k_is_reproducible(lib, monkeypatch):
-    monkeypatch.setenv("SYMPLEX_B200_F32_SPLITK", "4")
+def test_fp32_split_k_is_reproducible(lib, set_option):
+    set_option("f32_split_k", 4)
     A = torch.randn(256, 2048, device="cuda")
     B = torch.randn(2048, 128, device="cuda")
     first = sx.gemm(A, B)
@@ -529,7 +589,7 @@ def test_fp32_split_k_is_reproducible(lib, monkeypatch):
 
 @pytest.mark.parametrize("M,N,K,batch", [(64, 64, 64, 8), (1, 64, 32, 1), (17, 100, 72, 3), (64, 320, 1000, 2), (40, 64, 4096, 1),
                                          (48, 2048, 256, 1)])
-def test_fp32_64_row_mma_shape(lib, oracle, monkeypatch, M, N, K, batch):
+def test_fp32_64_row_mma_shape(lib, oracle, set_option, M, N, K, batch):
     """Problems with at most 64 rows run the M = 64 shape of the tensor-core instruction (accumulator rows in
     lanes 0-15 of each tensor-memory quarter). It must give the bits the 128-row shape gives (the zero rows that
     shape pads with contribute nothing) and meet the 1e-5 bound."""
@@ -541,9 +601,9 @@ def test_fp32_64_row_mma_shape(lib, oracle, monkeypatch, M, N, K, batch):
     bias = rng.uniform(-1, 1, N).astype(np.float32)
     tA, tB, tb = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), torch.from_numpy(bias).cuda()
     out = {}
-    monkeypatch.setenv("SYMPLEX_B200_F32_SPLITK", "1")
+    set_option("f32_split_k", 1)
     for rows in ("64", "128"):
-        monkeypatch.setenv("SYMPLEX_B200_F32_TILE_ROWS", rows)
+        set_option("f32_tile_rows", int(rows))
         out[rows] = (sx.gemm(tA, tB, bias=tb, activation="tanh").cpu().numpy(),
                      sx.gemm(tA, tB.transpose(-1, -2).contiguous(), b_layout=sx.COL_MAJOR,
                              out_dtype=torch.bfloat16).float().cpu().numpy())

@@ -120,3 +120,57 @@ def test_single_process_without_process_group():
     torch.testing.assert_close(op(A, B, out_dtype=torch.float32), A @ B)
     with pytest.raises(ValueError):
         op(torch.randn(100, 16), B)
+
+
+def _absent_rank_worker(rank, world, port, q):
+    """Rank 1 completes step 1 and then never enters step 2 (it just waits for the others to notice, on the host).
+    Rank 0 must get a ShardedStepTimeout after its deadline instead of blocking inside the collective."""
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, N, K = 256, 16, 8
+        g = torch.Generator().manual_seed(5)
+        A, B = torch.randn(M, K, generator=g), torch.randn(K, N, generator=g)
+        op = sharding.RowShardedGemm(M, N, K, chunks=1, local_gemm=_cpu_gemm, step_deadline_s=1.0)
+        idx = op.local_row_index()
+        C = op(A[idx].contiguous(), B, out_dtype=torch.float32)  # step 1: everybody is there
+        ok1 = bool(torch.equal(C, A @ B))
+        outcome = "absent"
+        if rank == 0:
+            t0 = time.monotonic()
+            try:
+                op(A[idx].contiguous(), B, out_dtype=torch.float32)  # step 2: rank 1 never comes
+                outcome = "returned"
+            except sharding.ShardedStepTimeout as e:
+                outcome = f"timeout after {time.monotonic() - t0:.2f} s: {e}"
+        else:
+            time.sleep(2.5)  # stays alive (its store connection too) while rank 0 runs into its deadline
+        q.put((rank, ok1, outcome))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_rank_that_never_enters_the_step_is_noticed_on_the_host():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_absent_rank_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict((r, (ok, out)) for r, ok, out in [q.get(timeout=120) for _ in range(world)])
+    for p in procs:
+        p.join(timeout=60)
+    assert results[0][0] and results[1][0], "step 1 (all ranks present) must succeed"
+    assert results[0][1].startswith("timeout after"), results[0][1]
+    assert "1 of 2 ranks entered step 2" in results[0][1]
+    assert 0.9 <= float(results[0][1].split()[2]) <= 2.4
+
+
+def test_fp32_inputs_move_a_defaulted_instance_to_the_nccl_exchange():
+    op = sharding.RowShardedGemm(256, 32, 16, local_gemm=_cpu_gemm)
+    assert op.exchange == "nccl"
+    with pytest.raises(ValueError):
+        sharding.RowShardedGemm(256, 32, 16, exchange="carrier_pigeon")
