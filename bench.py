@@ -1,14 +1,18 @@
 #!/usr/bin/env python
 """Benchmark of the GEMM hot path: `python bench.py --gpus N --steps K --warmup W [--impl reference]`.
 
-Default workload = BASELINE config 5, the row-sharded bf16 GEMM A[65536,8192] x B[8192,8192] -> bf16 C,
-rows of A split evenly over the N GPUs, C all-gathered over NVLink (N = 1: the same GEMM on one GPU,
-no collective). Total work is fixed as N grows ("scaling": "strong"). One step = one full product.
+Default workload: the row-sharded bf16 GEMM A[65536,8192] x B[8192,8192] -> bf16 C, rows of A split evenly
+over the N GPUs, C all-gathered over NVLink inside the GEMM kernel (N = 1: the same GEMM on one GPU, no
+exchange). Total work is fixed as N grows ("scaling": "strong"). One step = one full product.
 
 Prints ONE JSON line (rank 0). `value` is device-resident throughput (inputs in HBM, CUDA events, max over
 ranks); `e2e` is the same product through the host-buffer entry points with the pinned-host -> device and
-device -> host copies inside the timed region. `roofline` describes the GEMM kernel alone, `cpu_baseline`
-the reference's CPU path timed on this box's host cores on a bounded row sample.
+device -> host copies inside the timed region. `roofline` describes the GEMM kernel alone (plus an `nvlink`
+block for the exchange at N > 1), `cpu_baseline` the reference's CPU path timed on this box's host cores on a
+bounded row sample (`cpu_baseline.all`: the x86-JIT order, the BLIS order, the reference's C kernel and np.matmul).
+`parity_check` is a float64 check of the finished product on every rank; the exit code is 3 if it fails.
+On one GPU the default run appends `secondary`: short runs of the other GEMM workloads under the same timing rules.
+`config` names the workload (the same keys in both arms); how this arm ran it is in `detail`.
 
 `--impl reference` times the reference's own CPU implementation of the path instead (its C kernel compiled
 unchanged when available, else the oracle port), on a bounded row sample of the same workload per step.
@@ -428,6 +432,424 @@ def main_elementwise(args):
     return 0
 
 
+def base_config(name, w, gpus):
+    """The workload as both arms of the benchmark name it (identical keys and values in either arm)."""
+    return {"workload": name, "M": w["M"], "N": w["N"], "K": w["K"], "batch": w["batch"],
+            "inputs": w["dt"], "output": w["out"], "b_layout": "col_major" if w["b_col"] else "row_major",
+            "epilogue": ("bias+" if w["bias"] else "") + (w["act"] or "none"),
+            "partition": f"rows of A over {gpus} GPU(s), B replicated, C all-gathered" if w["sharded"]
+            else "replicas only"}
+
+
+def cpu_baselines(w, seconds_each):
+    """The CPU comparators of this path, each timed on its own bounded row sample of workload `w`:
+    the x86-JIT order (AVX-512 twin of the size-baked kernel, 1 thread, as the reference runs it), the BLIS order on
+    min(ceil(M / 128), cores) threads, the reference's C kernel compiled unchanged (one row block per thread) and
+    np.matmul (OpenBLAS, all cores - the comparator the reference's own benchmark uses)."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from oracle_loader import load_oracle
+    orc = load_oracle()
+    cores = _host_threads()
+    N, K = w["N"], w["K"]
+    out = []
+
+    def timed(fn, rows0, label, kind, threads, par=1):
+        """Calibrate on rows0 rows, then time one run sized for ~seconds_each (par: threads the sized run will use
+        beyond those of the calibration run)."""
+        A, B, C = cpu_sample(w, max(rows0, 8))
+        rows0 = min(rows0, A.shape[0])
+        fn(A[:rows0], B, C[:rows0], 1 if par > 1 else threads)  # warm: pages, code
+        t0 = time.perf_counter()
+        fn(A[:rows0], B, C[:rows0], 1 if par > 1 else threads)
+        rate = par * rows0 / max(time.perf_counter() - t0, 1e-6)
+        M = int(max(rows0, min(w["M"], rate * seconds_each)))
+        if M > A.shape[0]:
+            reps = (M + A.shape[0] - 1) // A.shape[0]
+            A = np.ascontiguousarray(np.tile(A, (reps, 1))[:M])
+            C = np.zeros((M, N), np.float32)
+        t0 = time.perf_counter()
+        fn(A[:M], B, C[:M], threads)
+        dt = time.perf_counter() - t0
+        out.append({"kind": kind, "name": label, "cores": threads, "value": 2.0 * M * N * K / dt / 1e12,
+                    "unit": "TFLOP/s", "sample": f"{M} of {w['M']} rows of A (all of B)"})
+
+    def avx512(A, B, C, threads):
+        if orc.lib.oracle_matmul_jit_avx512(A.ctypes.data, B.ctypes.data, C.ctypes.data, A.shape[0], N, K) != 0:
+            orc.lib.oracle_matmul_jit_order(A.ctypes.data, B.ctypes.data, C.ctypes.data, A.shape[0], N, K, 1)
+    timed(avx512, 2, "x86-JIT order: AVX-512 twin of compile_matmul_avx512 (oracle), single thread as in the reference",
+          "port", 1)
+    blis_threads = int(max(1, min(cores, (w["M"] + 127) // 128)))
+
+    def blis(A, B, C, threads):
+        orc.lib.oracle_matmul_blis_order(A.ctypes.data, B.ctypes.data, C.ctypes.data, A.shape[0], N, K, int(threads))
+    timed(blis, 8, "BLIS order (oracle restatement), rows split over min(ceil(M / 128), cores) threads as the "
+          "reference's rayon row blocks", "port", blis_threads, par=blis_threads)
+    run, kind, rcores, name = _load_cpu_reference()
+
+    def ref(A, B, C, threads):
+        run(A, B, C, A.shape[0], N, K)
+    timed(ref, 2 * cores, name, kind, rcores)
+
+    def npmm(A, B, C, threads):
+        np.matmul(A, B, out=C)
+    timed(npmm, min(w["M"], 64 * cores), "np.matmul (OpenBLAS, all cores)", "numpy", cores)
+    return out
+
+
+class Ctx:
+    """Process-wide state of one benchmark run (one rank)."""
+
+
+def parity_check(ctx, w, A_of_rows, B, bias, C, row_base, n_rows_total):
+    """Check a finished product on the device, in fp64: (i) where the epilogue is linear, the whole-output identity
+    C.1 = A.(B.1) + N-sum of the bias over this rank's rows of A against the gathered C; (ii) 64 sampled rows of the
+    WHOLE C (also rows computed by other ranks) against a float64 evaluation of the same formula.
+    `A_of_rows(rows)` returns the A rows for global row numbers (gathered from their owners when sharded)."""
+    torch = ctx.torch
+    M, N, K = n_rows_total, w["N"], w["K"]
+    dev = C.device
+    Bm = B.transpose(-1, -2) if w["b_col"] else B  # [K, N] view
+    res = {"rows": 64, "ok": True}
+    g = torch.Generator(device="cpu").manual_seed(4242)
+    rows = torch.sort(torch.randperm(M, generator=g)[:64]).values.to(dev)
+    Ar = A_of_rows(rows).double()
+    want = Ar @ Bm.double()
+    if bias is not None:
+        want = want + bias.double()
+    if w["act"] == "gelu":
+        want = 0.5 * want * (1.0 + torch.tanh(0.7978845608028654 * (want + 0.044715 * want ** 3)))
+    elif w["act"] == "relu":
+        want = torch.clamp(want, min=0)
+    got = C[rows].double()
+    rel = float((got - want).norm() / want.norm().clamp_min(1e-300))
+    tol = 1e-2 if (w["dt"] == "bf16" or w["out"] == "bf16") else 1e-5
+    res["max_rel"] = rel
+    res["tolerance"] = tol
+    res["ok"] = bool(rel <= tol)
+    if w["act"] is None:
+        # whole output: row sums, evaluated in chunks so the float64 copies stay small
+        bsum = Bm.double().sum(dim=1)
+        lhs = torch.cat([C[i:i + 4096].double().sum(dim=1) for i in range(0, M, 4096)])
+        mine = ctx.local_A.double() @ bsum
+        scale = ctx.local_A.double().abs() @ Bm.double().abs().sum(dim=1)
+        if ctx.world > 1 and w["sharded"]:
+            # every rank contributes the sums of the rows it owns, at their global row numbers
+            rhs = torch.zeros(M, device=dev, dtype=torch.float64)
+            sc = torch.zeros(M, device=dev, dtype=torch.float64)
+            rhs[ctx.local_rows] = mine
+            sc[ctx.local_rows] = scale
+            ctx.dist.all_reduce(rhs)
+            ctx.dist.all_reduce(sc)
+        else:
+            rhs, sc = mine, scale
+        if bias is not None:
+            rhs = rhs + bias.double().sum()
+        ident = float((lhs - rhs).norm() / sc.norm())
+        res["checksum_rel"] = ident
+        res["ok"] = bool(res["ok"] and ident <= (1e-3 if w["out"] == "bf16" else 1e-5))
+    return res
+
+
+def run_gemm_workload(ctx, args, name, primary):
+    """Measure one GEMM workload on this rank (and its peers); returns the JSON line as a dict (rank 0) or None.
+    `primary`: the workload the line is about (full protocol: K timed steps, e2e, CPU baselines, spread of single
+    steps). Secondary workloads get a short device-timed run with the same timing rules and a parity check."""
+    torch, dist, sx, lib = ctx.torch, ctx.dist, ctx.sx, ctx.lib
+    from symplex_b200.sharding import RowShardedGemm
+    w = WORKLOADS[name]
+    rank, local_rank, world, dev = ctx.rank, ctx.local_rank, ctx.world, ctx.dev
+    peaks, peak_note = ctx.peaks, ctx.peak_note
+    config = base_config(name, w, args.gpus)
+    detail = {}
+
+    tdt = torch.bfloat16 if w["dt"] == "bf16" else torch.float32
+    odt = torch.bfloat16 if w["out"] == "bf16" else torch.float32
+    M, N, K, batch = w["M"], w["N"], w["K"], w["batch"]
+    g = torch.Generator(device=dev).manual_seed(1234)  # same B on every rank
+    b_shape = (N, K) if w["b_col"] else (K, N)
+    scale = 0.02 if w["act"] == "gelu" else 1.0
+    if batch > 1:
+        Bm = (torch.randn((batch,) + b_shape, device=dev, generator=g) * scale).to(tdt)
+    else:
+        Bm = (torch.randn(b_shape, device=dev, generator=g) * scale).to(tdt)
+    bias = (torch.randn(N, device=dev, generator=g) * scale) if w["bias"] else None
+    b_layout = sx.COL_MAJOR if w["b_col"] else sx.ROW_MAJOR
+
+    sharded = w["sharded"]
+    op = None
+    if sharded:
+        op = RowShardedGemm(M, N, K, chunks=args.chunks, activation=w["act"], b_layout=b_layout,
+                            exchange=args.exchange)
+        m_loc = M // op.world
+        ga = torch.Generator(device=dev).manual_seed(100 + rank)
+        A = (torch.randn(m_loc, K, device=dev, generator=ga) * scale).to(tdt)
+        fused = op.exchange in op.FUSED and op.world > 1
+        C = op.output_buffer(odt, dev) if fused else torch.empty(M, N, device=dev, dtype=odt)
+        detail["chunks"] = op.chunks
+        detail["exchange"] = {
+            "peer_store": "in the GEMM kernel: forwarder warps copy each finished tile to every peer's C (16-byte "
+                          "stores over NVLink), ranks ordered by flags in peer memory",
+            "multicast": "in the GEMM kernel: forwarder warps store each finished tile once to a multicast mapping "
+                         "(multimem.st), the NVSwitch delivers it to every GPU",
+            "epilogue_tma": "in the GEMM kernel: epilogue warps forward their blocks to every peer by TMA stores",
+            "nccl": "NCCL all_gather_into_tensor per row chunk, overlapped with the next chunk's GEMM",
+        }[op.exchange] if op.world > 1 else "none (1 GPU)"
+        detail["exchange_mode"] = op.exchange if op.world > 1 else "none"
+        ctx.local_A = A
+
+        def step():
+            op(A, Bm, bias=bias, out=C)
+        launches_per_step_flops = flops_of(w) / max(1, op.world) / op.chunks
+    else:
+        ga = torch.Generator(device=dev).manual_seed(100 + rank)
+        a_shape = (batch, M, K) if batch > 1 else (M, K)
+        # small problems: rotate over several operand sets so each step reads cold data (larger than L2 in total)
+        bytes_per_set = (M * K + K * N) * batch * (2 if w["dt"] == "bf16" else 4) + M * N * batch * (2 if w["out"] == "bf16" else 4)
+        nsets = 1 if bytes_per_set > 256e6 else int(min(64, 512e6 // bytes_per_set + 1))
+        As = [(torch.randn(a_shape, device=dev, generator=ga) * scale).to(tdt) for _ in range(nsets)]
+        Bs = [Bm] + [(torch.randn_like(Bm.float()) * scale).to(tdt) for _ in range(nsets - 1)]
+        Cs = [torch.empty((batch, M, N) if batch > 1 else (M, N), device=dev, dtype=odt) for _ in range(nsets)]
+        counter = [0]
+        detail["l2"] = ("inputs larger than L2" if nsets == 1 else f"rotating over {nsets} operand sets "
+                        f"({nsets * bytes_per_set / 1e6:.0f} MB > L2) so every step reads cold data")
+        ctx.local_A = As[0] if batch == 1 else None
+
+        def step():
+            i = counter[0] % nsets
+            counter[0] += 1
+            sx.gemm(As[i], Bs[i], bias=bias, activation=w["act"], out=Cs[i], b_layout=b_layout)
+        launches_per_step_flops = flops_of(w)
+    if sharded:
+        detail["l2"] = "inputs larger than L2 (per GPU: A %.0f MiB, B %.0f MiB, C %.0f MiB)" % (
+            A.numel() * A.element_size() / 2**20, Bm.numel() * Bm.element_size() / 2**20,
+            C.numel() * C.element_size() / 2**20)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    steps, warmup = args.steps, args.warmup
+    if not primary:
+        # a short run: at least 3 warm-up steps, then enough steps for ~0.4 s (so the clock sampler sees the load)
+        warmup = 3
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        step()
+        torch.cuda.synchronize()
+        est = max(time.perf_counter() - t0, 2e-5)
+        steps = int(max(10, min(400, 0.4 / est)))
+    else:
+        for _ in range(warmup):
+            step()
+    barrier()
+    sx.sync_status()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3 if primary else 0.1)
+    launches0 = lib.symplex_b200_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    launches = lib.symplex_b200_launch_count() - launches0
+    sx.sync_status()
+
+    # Steps of a few tens of microseconds: the Python caller cannot issue launches that fast, so the loop above
+    # times the host. The same K steps are then captured into one CUDA graph and the replay is timed - the
+    # library's launches are capturable (no allocation or synchronisation on a warm call).
+    graph = None
+    if not sharded and world == 1 and elapsed_ms / steps < 0.1:
+        detail["eager_ms_per_step"] = elapsed_ms / steps
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(steps):
+                step()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        elapsed_ms = e0.elapsed_time(e1)
+        detail["launch"] = f"one CUDA graph of {steps} steps (eager launches are host-bound at this size)"
+        sx.sync_status()
+
+    # Spread of single steps (outside the timed region above, which stays K back-to-back steps): one event between
+    # consecutive steps; for graph-launched workloads one event between consecutive replays of the K-step graph.
+    # One GPU only: these steps directly follow the timed ones, so on a power-capped board they show the sustained
+    # rate (the clock has settled by then) next to the burst the first K steps may have run at.
+    step_spread = None
+    if world == 1 and primary:
+        nspread = max(3, min(steps, 20))
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(nspread + 1)]
+        marks[0].record()
+        for i in range(nspread):
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
+            marks[i + 1].record()
+        torch.cuda.synchronize()
+        per = [marks[i].elapsed_time(marks[i + 1]) / (steps if graph is not None else 1) for i in range(nspread)]
+        step_spread = {"min": min(per), "median": statistics.median(per), "max": max(per), "n": nspread}
+        sx.sync_status()
+
+    # per-launch duration of the GEMM kernel alone (no exchange), CUDA events on the launching stream
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sharded:
+        blk = (M // op.world) // op.chunks
+        Ak = A[:blk]
+        Ck = torch.empty(blk, N, device=dev, dtype=odt) if world > 1 else C[:blk]
+
+        def kernel_only():
+            sx.gemm(Ak, Bm, bias=bias, activation=w["act"], out=Ck, b_layout=b_layout)
+    else:
+        kernel_only = step
+    if (sharded and op.world == 1) or graph is not None or not sharded:
+        kernel_ms = elapsed_ms / steps  # one step is exactly one launch of the GEMM kernel
+    else:
+        kernel_only()
+        torch.cuda.synchronize()
+        kreps = max(3, min(steps, 10))
+        k0.record()
+        for _ in range(kreps):
+            kernel_only()
+        k1.record()
+        torch.cuda.synchronize()
+        kernel_ms = k0.elapsed_time(k1) / kreps
+    clocks = sampler.stop() if sampler else None
+
+    # ---------------- result check (every rank, every N): sampled rows in float64 + whole-output row sums
+    if sharded:
+        step()
+        barrier()
+        # global row -> (owner, position in the owner's local A): chunk-major blocks (sharding.owned_row_blocks)
+        blk_rows = (M // world) // op.chunks
+        chunk_rows = M // op.chunks
+        ctx.local_rows = op.local_row_index().to(dev)
+
+        def A_of_rows(rows):
+            if world == 1:
+                return A[rows]
+            c, within = rows // chunk_rows, rows % chunk_rows
+            mine = (within // blk_rows) == rank
+            local = c * blk_rows + within % blk_rows
+            buf = torch.zeros(rows.numel(), K, device=dev, dtype=torch.float32)
+            buf[mine] = A[local[mine]].float()
+            dist.all_reduce(buf)
+            return buf
+        check = parity_check(ctx, w, A_of_rows, Bm, bias, C, 0, M)
+    elif batch == 1:
+        sx.gemm(As[0], Bs[0], bias=bias, activation=w["act"], out=Cs[0], b_layout=b_layout)
+        torch.cuda.synchronize()
+        check = parity_check(ctx, w, lambda rows: As[0][rows], Bs[0], bias, Cs[0], 0, M)
+    else:
+        sx.gemm(As[0], Bs[0], bias=bias, activation=w["act"], out=Cs[0], b_layout=b_layout)
+        torch.cuda.synchronize()
+        want = torch.bmm(As[0].double(), (Bs[0].transpose(-1, -2) if w["b_col"] else Bs[0]).double())
+        rel = float((Cs[0].double() - want).norm() / want.norm())
+        check = {"rows": int(batch * M), "max_rel": rel, "tolerance": 1e-5, "ok": bool(rel <= 1e-5)}
+    sx.sync_status()
+    okt = torch.tensor([1.0 if check["ok"] else 0.0, check["max_rel"]], device=dev, dtype=torch.float64)
+    if world > 1:
+        okmin = okt.clone()
+        dist.all_reduce(okmin, op=dist.ReduceOp.MIN)
+        okmax = okt.clone()
+        dist.all_reduce(okmax, op=dist.ReduceOp.MAX)
+        check["ok"] = bool(okmin[0].item() > 0.5)
+        check["max_rel"] = float(okmax[1].item())
+        check["ranks"] = world
+    ctx.parity_ok = ctx.parity_ok and check["ok"]
+
+    t = torch.tensor([elapsed_ms, float(launches)], device=dev, dtype=torch.float64)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        elapsed_ms = tmax[0].item()
+        launches = int(tsum[1].item())
+    ms_per_step = elapsed_ms / steps
+    replicas = 1 if sharded else world
+    value = flops_of(w) * replicas / (ms_per_step * 1e-3) / 1e12
+
+    # ---------------- end to end through the host-buffer entry points (pinned host memory)
+    e2e = None
+    if primary and not args.no_e2e:
+        e2e = run_e2e(args, w, sx, lib, torch, dist, dev, rank, world, Bm, bias, b_layout, tdt, odt,
+                      op if sharded else None, scale)
+    ctx.local_A = None
+    if rank != 0:
+        return None
+
+    achieved = launches_per_step_flops / (kernel_ms * 1e-3) / 1e12
+    traffic = NCU_TRAFFIC_BYTES.get(name)
+    if sharded:  # rows of A per launch, scaled from the 8192-row capture of the same kernel
+        traffic = NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192 * (M / args.gpus / detail["chunks"]) / 8192.0
+    tensor_bound = w["dt"] == "bf16" or w["K"] >= 1024
+    if w["dt"] == "bf16":
+        peak = float(peaks["bf16_tflops"])
+        peak_desc = f"bf16 dense burst, {peak_note}"
+    else:
+        peak = float(peaks["bf16_tflops"]) / 6.0
+        peak_desc = f"derived 3xTF32 ceiling = bf16 burst / 2 / 3, {peak_note}"
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": traffic, "kernel_ms": kernel_ms, "peak_kind": peak_desc,
+                "flops_per_launch": launches_per_step_flops}
+    if w["dt"] == "bf16" and "bf16_tflops_sustained" in peaks:
+        roofline["frac_of_sustained"] = achieved / float(peaks["bf16_tflops_sustained"])
+    if not tensor_bound:
+        algo_bytes = ((M * K + K * N) * 4 + M * N * 4) * batch
+        ach = algo_bytes / (kernel_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": ach, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
+                    "frac": ach / float(peaks["hbm_gbs"]), "traffic": traffic,
+                    "kernel_ms": kernel_ms, "peak_kind": f"HBM copy, {peak_note}", "bytes_per_launch": algo_bytes,
+                    "note": "one step = one launch of the in-kernel-split fp32 GEMM kernel (no pre-pass)"}
+    if sharded and world > 1:
+        # The exchange: every GPU must receive the other ranks' rows of C; with unicast stores it also sends its own
+        # rows world - 1 times, with the multicast mapping once. Time = the step (exchange and GEMM are one kernel).
+        c_bytes = float(M) * N * (2 if w["out"] == "bf16" else 4)
+        recv = c_bytes * (world - 1) / world
+        send = c_bytes / world * (1 if op.exchange == "multicast" else (world - 1))
+        link_ms = recv / 900e9 * 1e3
+        roofline["nvlink"] = {
+            "bytes_in_per_gpu": recv, "bytes_out_per_gpu": send,
+            "achieved_in_gbs": recv / (ms_per_step * 1e-3) / 1e9, "achieved_out_gbs": send / (ms_per_step * 1e-3) / 1e9,
+            "frac_of_900_in": recv / (ms_per_step * 1e-3) / 900e9, "nominal_link_ms": link_ms,
+            "compute_ms": kernel_ms, "step_ms": ms_per_step,
+            "achieved_over_bound": max(link_ms, kernel_ms) / ms_per_step,
+            "note": "bound = the slower of the GEMM alone and the inbound bytes at the nominal 900 GB/s per direction"}
+
+    line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if sharded else "weak", "vs_baseline": None,
+            "dtype": "bf16" if w["dt"] == "bf16" else "f32 (3xTF32 on tensor cores)", "data": "synthetic",
+            "config": config, "detail": detail,
+            "frac_of_bf16_peak": value / (args.gpus * float(peaks["bf16_tflops"])),
+            "roofline": roofline, "parity_check": check, "gpu_launches": launches, "clocks": clocks}
+    if primary:
+        cpu_baseline = None
+        if not args.no_cpu_baseline and world == 1:
+            tfl, dt, kind, cores, sample = time_cpu_reference(w, 4.0, steps=3, warmup=1)
+            cpu_baseline = {"value": tfl, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample}
+            try:
+                cpu_baseline["all"] = cpu_baselines(w, 3.0)
+            except Exception as e:  # the headline baseline above stands on its own
+                cpu_baseline["all_error"] = repr(e)
+        line.update({"cpu_baseline": cpu_baseline, "e2e": e2e, "step_ms": step_spread})
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -436,10 +858,12 @@ def main():
     ap.add_argument("--impl", default="symplex_b200", choices=["symplex_b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(ELEMENTWISE_WORKLOADS))
     ap.add_argument("--chunks", type=int, default=None, help="row chunks per rank for the NCCL all-gather pipeline")
-    ap.add_argument("--exchange", default=None, choices=["peer_store", "nccl"],
-                    help="how C is all-gathered at N > 1 (default: fused peer stores from the GEMM epilogue)")
+    ap.add_argument("--exchange", default=None, choices=["peer_store", "multicast", "epilogue_tma", "nccl"],
+                    help="how C is all-gathered at N > 1 (default: forwarder warps inside the GEMM kernel)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="default workload on one GPU: skip the short runs of the other workloads")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl != "reference":
         args.warmup = 3  # timing rule: at least 3 warm-up steps
@@ -450,15 +874,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    config = {"workload": args.workload, "M": w["M"], "N": w["N"], "K": w["K"], "batch": w["batch"],
-              "inputs": w["dt"], "output": w["out"], "b_layout": "col_major" if w["b_col"] else "row_major",
-              "epilogue": ("bias+" if w["bias"] else "") + (w["act"] or "none"),
-              "partition": f"rows of A over {args.gpus} GPU(s), B replicated, C all-gathered" if w["sharded"]
-              else "replicas only"}
 
     if args.impl == "reference":
         if rank != 0:
             return 0
+        config = base_config(args.workload, w, args.gpus)
         # a step is a row sample of up to ~3 s (sized by a calibration pass), shrunk so that all steps end within about a minute
         seconds = max(0.25, min(3.0, 60.0 / (args.steps + max(1, args.warmup))))
         tflops, dt, kind, cores, sample = time_cpu_reference(w, seconds, args.steps, max(1, args.warmup))
@@ -477,220 +897,49 @@ def main():
 
     import symplex_b200 as sx
     from symplex_b200 import _capi
-    from symplex_b200.sharding import RowShardedGemm
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: there is no CPU fallback (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
+    ctx = Ctx()
+    ctx.torch, ctx.dist, ctx.sx = torch, dist, sx
+    ctx.rank, ctx.local_rank, ctx.world = rank, local_rank, world
+    ctx.dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    lib = _capi.load()
-    peaks, peak_note = load_peaks()
-
-    tdt = torch.bfloat16 if w["dt"] == "bf16" else torch.float32
-    odt = torch.bfloat16 if w["out"] == "bf16" else torch.float32
-    M, N, K, batch = w["M"], w["N"], w["K"], w["batch"]
-    g = torch.Generator(device=dev).manual_seed(1234)  # same B on every rank
-    b_shape = (N, K) if w["b_col"] else (K, N)
-    scale = 0.02 if w["act"] == "gelu" else 1.0
-    if batch > 1:
-        Bm = (torch.randn((batch,) + b_shape, device=dev, generator=g) * scale).to(tdt)
-    else:
-        Bm = (torch.randn(b_shape, device=dev, generator=g) * scale).to(tdt)
-    bias = (torch.randn(N, device=dev, generator=g) * scale) if w["bias"] else None
-    b_layout = sx.COL_MAJOR if w["b_col"] else sx.ROW_MAJOR
-
-    sharded = w["sharded"]
-    if sharded:
-        op = RowShardedGemm(M, N, K, chunks=args.chunks, activation=w["act"], b_layout=b_layout,
-                            exchange=args.exchange)
-        m_loc = M // op.world
-        ga = torch.Generator(device=dev).manual_seed(100 + rank)
-        A = (torch.randn(m_loc, K, device=dev, generator=ga) * scale).to(tdt)
-        peer_store = op.exchange == "peer_store" and op.world > 1
-        C = op.output_buffer(odt, dev) if peer_store else torch.empty(M, N, device=dev, dtype=odt)
-        config["chunks"] = op.chunks
-        config["exchange"] = ("fused into the GEMM epilogue: TMA stores to every peer's C over NVLink" if peer_store
-                              else ("NCCL all_gather_into_tensor per chunk" if op.world > 1 else "none (1 GPU)"))
-
-        def step():
-            op(A, Bm, bias=bias, out=C)
-        launches_per_step_flops = flops_of(w) / max(1, op.world) / op.chunks
-    else:
-        ga = torch.Generator(device=dev).manual_seed(100 + rank)
-        a_shape = (batch, M, K) if batch > 1 else (M, K)
-        # small problems: rotate over several operand sets so each step reads cold data (larger than L2 in total)
-        bytes_per_set = (M * K + K * N) * batch * (2 if w["dt"] == "bf16" else 4) + M * N * batch * (2 if w["out"] == "bf16" else 4)
-        nsets = 1 if bytes_per_set > 256e6 else int(min(64, 512e6 // bytes_per_set + 1))
-        As = [(torch.randn(a_shape, device=dev, generator=ga) * scale).to(tdt) for _ in range(nsets)]
-        Bs = [Bm] + [(torch.randn_like(Bm.float()) * scale).to(tdt) for _ in range(nsets - 1)]
-        Cs = [torch.empty((batch, M, N) if batch > 1 else (M, N), device=dev, dtype=odt) for _ in range(nsets)]
-        counter = [0]
-        config["l2"] = ("inputs larger than L2" if nsets == 1 else f"rotating over {nsets} operand sets "
-                        f"({nsets * bytes_per_set / 1e6:.0f} MB > L2) so every step reads cold data")
-
-        def step():
-            i = counter[0] % nsets
-            counter[0] += 1
-            sx.gemm(As[i], Bs[i], bias=bias, activation=w["act"], out=Cs[i], b_layout=b_layout)
-        launches_per_step_flops = flops_of(w)
-    if sharded:
-        config["l2"] = "inputs larger than L2 (per GPU: A %.0f MiB, B %.0f MiB, C %.0f MiB)" % (
-            A.numel() * A.element_size() / 2**20, Bm.numel() * Bm.element_size() / 2**20,
-            C.numel() * C.element_size() / 2**20)
-
-    def barrier():
+        dist.init_process_group("nccl", device_id=ctx.dev)
+    ctx.lib = _capi.load()
+    ctx.peaks, ctx.peak_note = load_peaks()
+    ctx.parity_ok = True
+    ctx.local_A = None
+    rc = 0
+    try:
+        line = run_gemm_workload(ctx, args, args.workload, primary=True)
+        if world == 1 and args.workload == DEFAULT_WORKLOAD and not args.no_secondary:
+            secondary = []
+            for name in WORKLOADS:
+                if name == args.workload:
+                    continue
+                torch.cuda.empty_cache()
+                sec = run_gemm_workload(ctx, args, name, primary=False)
+                secondary.append({k: sec[k] for k in ("config", "detail", "value", "unit", "steps", "warmup", "ms_per_step",
+                                                      "dtype", "roofline", "parity_check", "gpu_launches", "clocks")})
+            line["secondary"] = secondary
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        if not ctx.parity_ok:
+            if rank == 0:
+                print("bench.py: a result check failed (parity_check.ok is false)", file=sys.stderr, flush=True)
+            rc = 3
+    finally:
+        # every rank leaves in step: no rank's memory disappears while a peer still has it mapped
         if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    sx.sync_status()
-
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    if sampler:
-        sampler.start()
-        time.sleep(0.3)
-    launches0 = lib.symplex_b200_launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    elapsed_ms = e0.elapsed_time(e1)
-    launches = lib.symplex_b200_launch_count() - launches0
-    sx.sync_status()
-
-    # Steps of a few tens of microseconds: the Python caller cannot issue launches that fast, so the loop above
-    # times the host. The same K steps are then captured into one CUDA graph and the replay is timed - the
-    # library's launches are capturable (no allocation or synchronisation on a warm call).
-    if not sharded and world == 1 and elapsed_ms / args.steps < 0.1:
-        config["eager_ms_per_step"] = elapsed_ms / args.steps
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for _ in range(args.steps):
-                step()
-        graph.replay()
-        torch.cuda.synchronize()
-        e0.record()
-        graph.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        elapsed_ms = e0.elapsed_time(e1)
-        config["launch"] = f"one CUDA graph of {args.steps} steps (eager launches are host-bound at this size)"
-        sx.sync_status()
-
-    # Spread of single steps (outside the timed region above, which stays K back-to-back steps): one event between
-    # consecutive steps; for graph-launched workloads one event between consecutive replays of the K-step graph.
-    # One GPU only: these steps directly follow the timed ones, so on a power-capped board they show the sustained
-    # rate (the clock has settled by then) next to the burst the first K steps may have run at.
-    step_spread = None
-    if world == 1:
-        nspread = max(3, min(args.steps, 20))
-        marks = [torch.cuda.Event(enable_timing=True) for _ in range(nspread + 1)]
-        marks[0].record()
-        for i in range(nspread):
-            if "launch" in config:
-                graph.replay()
-            else:
-                step()
-            marks[i + 1].record()
-        torch.cuda.synchronize()
-        per = [marks[i].elapsed_time(marks[i + 1]) / (args.steps if "launch" in config else 1)
-               for i in range(nspread)]
-        step_spread = {"min": min(per), "median": statistics.median(per), "max": max(per), "n": nspread}
-        sx.sync_status()
-
-    # per-launch duration of the GEMM kernel alone (no collective), CUDA events on the launching stream
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if sharded:
-        blk = (M // op.world) // op.chunks
-        Ak, Ck = A[:blk], C[:blk]
-
-        def kernel_only():
-            sx.gemm(Ak, Bm, bias=bias, activation=w["act"], out=Ck, b_layout=b_layout)
-    else:
-        kernel_only = step
-    if (sharded and op.world == 1) or "launch" in config:
-        kernel_ms = elapsed_ms / args.steps  # one step is exactly one launch of the GEMM kernel
-    else:
-        kernel_only()
-        torch.cuda.synchronize()
-        kreps = max(3, min(args.steps, 10))
-        k0.record()
-        for _ in range(kreps):
-            kernel_only()
-        k1.record()
-        torch.cuda.synchronize()
-        kernel_ms = k0.elapsed_time(k1) / kreps
-    clocks = sampler.stop() if sampler else None
-
-    t = torch.tensor([elapsed_ms, float(launches)], device=dev, dtype=torch.float64)
-    if world > 1:
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tsum = t.clone()
-        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        elapsed_ms = tmax[0].item()
-        launches = int(tsum[1].item())
-    ms_per_step = elapsed_ms / args.steps
-    replicas = 1 if sharded else world
-    value = flops_of(w) * replicas / (ms_per_step * 1e-3) / 1e12
-
-    # ---------------- end to end through the host-buffer entry points (pinned host memory)
-    e2e = None
-    if not args.no_e2e:
-        e2e = run_e2e(args, w, sx, lib, torch, dist, dev, rank, world, Bm, bias, b_layout, tdt, odt,
-                      op if sharded else None, scale)
-
-    if rank != 0:
-        if world > 1:
+            try:
+                torch.cuda.synchronize()
+                dist.barrier()
+            except Exception:
+                pass
             dist.destroy_process_group()
-        return 0
-
-    achieved = launches_per_step_flops / (kernel_ms * 1e-3) / 1e12
-    traffic = NCU_TRAFFIC_BYTES.get(args.workload)
-    if sharded:  # rows of A per launch, scaled from the 8192-row capture of the same kernel
-        traffic = NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192 * (M / args.gpus / config["chunks"]) / 8192.0
-    tensor_bound = w["dt"] == "bf16" or w["K"] >= 1024
-    if w["dt"] == "bf16":
-        peak = float(peaks["bf16_tflops"])
-        peak_desc = f"bf16 dense burst, {peak_note}"
-    else:
-        peak = float(peaks["bf16_tflops"]) / 6.0
-        peak_desc = f"derived 3xTF32 ceiling = bf16 burst / 2 / 3, {peak_note}"
-    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": traffic, "kernel_ms": kernel_ms, "peak_kind": peak_desc,
-                "flops_per_launch": launches_per_step_flops}
-    if not tensor_bound:
-        algo_bytes = ((M * K + K * N) * 4 + M * N * 4) * batch
-        ach = algo_bytes / (kernel_ms * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "achieved": ach, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
-                    "frac": ach / float(peaks["hbm_gbs"]), "traffic": traffic,
-                    "kernel_ms": kernel_ms, "peak_kind": f"HBM copy, {peak_note}", "bytes_per_launch": algo_bytes,
-                    "note": "one step = one launch of the in-kernel-split fp32 GEMM kernel (no pre-pass)"}
-
-    cpu_baseline = None
-    if not args.no_cpu_baseline and world == 1:
-        tfl, dt, kind, cores, sample = time_cpu_reference(w, 4.0, steps=3, warmup=1)
-        cpu_baseline = {"value": tfl, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample}
-
-    line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong" if sharded else "weak", "vs_baseline": None,
-            "dtype": "bf16" if w["dt"] == "bf16" else "f32 (3xTF32 on tensor cores)", "data": "synthetic",
-            "config": config, "frac_of_bf16_peak": value / (args.gpus * float(peaks["bf16_tflops"])),
-            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
-            "clocks": clocks, "step_ms": step_spread}
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
-    return 0
+    return rc
 
 
 def run_e2e(args, w, sx, lib, torch, dist, dev, rank, world, Bm, bias, b_layout, tdt, odt, op, scale):
@@ -715,10 +964,47 @@ def run_e2e(args, w, sx, lib, torch, dist, dev, rank, world, Bm, bias, b_layout,
 
         def host_step():
             sx.gemm_host(d, hA.data_ptr(), hB.data_ptr(), hC.data_ptr(), hbias.data_ptr() if hbias is not None else None)
+        api = "symplex_b200_gemm_host (C ABI, pinned host buffers)"
+    elif op.exchange in ("peer_store", "multicast"):
+        # Per rank: the local rows go through in row chunks. Chunk c's rows of A are copied in on one stream, its
+        # GEMM + exchange (one kernel) runs on a second as soon as they have landed, and this rank's rows of the
+        # chunk's result go back to the host on a third - so copy-in, compute and copy-out of neighbouring chunks
+        # overlap, as the one-GPU host entry point does it. B and the bias travel first, every step.
+        from symplex_b200.sharding import RowShardedGemm
+        nch = 4 if (m_loc % 4 == 0 and (m_loc // 4) % 256 == 0) else 1
+        pipe = RowShardedGemm(M, N, K, chunks=nch, activation=w["act"], b_layout=b_layout, exchange=op.exchange)
+        nch = pipe.chunks
+        dC = pipe.output_buffer(odt, dev)
+        dA = torch.empty(hA.shape, device=dev, dtype=tdt)
+        dB = torch.empty(hB.shape, device=dev, dtype=tdt)
+        dbias = torch.empty_like(bias) if bias is not None else None
+        blk = m_loc // nch
+        s_in, s_mm, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
+        ev_in = [torch.cuda.Event() for _ in range(nch)]
+        ev_mm = [torch.cuda.Event() for _ in range(nch)]
+
+        def host_step():
+            with torch.cuda.stream(s_in):
+                dB.copy_(hB, non_blocking=True)
+                if dbias is not None:
+                    dbias.copy_(hbias, non_blocking=True)
+                for c in range(nch):
+                    dA[c * blk:(c + 1) * blk].copy_(hA[c * blk:(c + 1) * blk], non_blocking=True)
+                    ev_in[c].record(s_in)
+            for c, (row0, nrows) in enumerate(pipe.blocks):
+                s_mm.wait_event(ev_in[c])
+                pipe.run_chunk(c, dA[c * blk:(c + 1) * blk], dB, dbias, odt, stream=s_mm.cuda_stream)
+                ev_mm[c].record(s_mm)
+                s_out.wait_event(ev_mm[c])
+                with torch.cuda.stream(s_out):
+                    hC[c * nrows:(c + 1) * nrows].copy_(dC[row0:row0 + nrows], non_blocking=True)
+            torch.cuda.synchronize()
+        api = (f"RowShardedGemm.run_chunk per row chunk ({nch} per rank) with pinned host shards: copy-in, "
+               "GEMM + exchange and copy-out of neighbouring chunks overlap on three streams")
     else:
         dA = torch.empty(hA.shape, device=dev, dtype=tdt)
         dB = torch.empty(hB.shape, device=dev, dtype=tdt)
-        dC = op.output_buffer(odt, dev) if op.exchange == "peer_store" else torch.empty(M, N, device=dev, dtype=odt)
+        dC = op.output_buffer(odt, dev) if op.exchange in op.FUSED else torch.empty(M, N, device=dev, dtype=odt)
 
         def host_step():
             dA.copy_(hA, non_blocking=True)
@@ -727,6 +1013,7 @@ def run_e2e(args, w, sx, lib, torch, dist, dev, rank, world, Bm, bias, b_layout,
             for c, (row0, nrows) in enumerate(op.blocks):  # this rank's rows of C go back to its host buffer
                 hC[c * nrows:(c + 1) * nrows].copy_(dC[row0:row0 + nrows], non_blocking=True)
             torch.cuda.synchronize()
+        api = "RowShardedGemm with pinned host shards per rank (copy-in, step, copy-out back to back)"
 
     host_step()
     if world > 1:
@@ -741,11 +1028,11 @@ def run_e2e(args, w, sx, lib, torch, dist, dev, rank, world, Bm, bias, b_layout,
     if world > 1:
         dist.all_reduce(dt, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    sx.sync_status()
     replicas = 1 if op is not None else world
     return {"value": flops_of(w) * replicas / dt.item() / 1e12, "unit": "TFLOP/s", "ms_per_step": dt.item() * 1e3,
             "h2d_bytes_per_step": int(tot[0].item()), "d2h_bytes_per_step": int(tot[1].item()), "steps": steps,
-            "api": "symplex_b200_gemm_host (C ABI, pinned host buffers)" if (op is None or world == 1)
-            else "RowShardedGemm with pinned host shards per rank"}
+            "api": api}
 
 
 if __name__ == "__main__":

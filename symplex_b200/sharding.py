@@ -189,8 +189,10 @@ class RowShardedGemm:
             raise ValueError(f"exchange must be one of {self.EXCHANGES}")
         self.exchange = exchange
         self._requested_chunks = chunks
-        if exchange in self.FUSED:
+        if exchange in self.FUSED and chunks is None:
             chunks = 1  # one GEMM launch over all local rows; the exchange rides on the same kernel
+        if exchange == "epilogue_tma":
+            chunks = 1
         self._symm_out = None
         self._peer_ptrs = None
         self._flag = None
@@ -249,6 +251,19 @@ class RowShardedGemm:
         comm.epoch = 0
         comm.wait_limit_ms = int(self.wait_limit_ms)
         self._comm = comm
+        # One communicator per row chunk: the same ranks and flags, C (and its multicast mapping) advanced to the
+        # chunk's block of rows. The call counter is shared (see _call_fused).
+        self._chunk_comms = []
+        blk_bytes = (self.M // self.chunks) * self.N * buf.element_size()
+        for c in range(self.chunks):
+            cc = _capi.Comm()
+            cc.rank, cc.world = self.rank, self.world
+            for r in range(self.world):
+                cc.c_base[r] = int(hdl.buffer_ptrs[r]) + c * blk_bytes
+                cc.flags[r] = int(fhdl.buffer_ptrs[r])
+            cc.c_multicast = (mc + c * blk_bytes) if self.exchange == "multicast" else None
+            cc.wait_limit_ms = int(self.wait_limit_ms)
+            self._chunk_comms.append(cc)
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)  # every rank's flags are zero before anybody's kernel writes one
         return buf
@@ -259,12 +274,8 @@ class RowShardedGemm:
         dist.all_reduce(self._flag, group=self.group)
 
     def _call_fused(self, A_local, B, bias, out_dtype):
-        """One kernel per rank computes and gathers (``symplex_b200_sharded_gemm``)."""
-        import ctypes
-
-        import torch
-
-        from . import _capi, gemm, make_desc
+        """One kernel per rank (and row chunk) computes and gathers (``symplex_b200_sharded_gemm``)."""
+        from . import gemm
         out = self.output_buffer(out_dtype, A_local.device)
         if self.exchange == "epilogue_tma":
             row0, nrows = self.blocks[0]
@@ -276,23 +287,45 @@ class RowShardedGemm:
                  peer_outputs=peers)
             self._barrier()  # every rank's tiles have been written everywhere
             return out
-        if A_local.dtype != torch.bfloat16 or B.dtype != torch.bfloat16:
+        A_local = A_local.contiguous()
+        B = B.contiguous()
+        blk = (self.M // self.world) // self.chunks
+        for c in range(self.chunks):
+            self.run_chunk(c, A_local[c * blk:(c + 1) * blk], B, bias, out_dtype)
+        return out
+
+    def run_chunk(self, c, A_blk, B, bias=None, out_dtype=None, stream=None):
+        """Chunk ``c`` of a fused step: one ``symplex_b200_sharded_gemm`` call (GEMM + exchange in one kernel) over
+        this rank's ``M / (world * chunks)`` rows of the chunk, whose result lands, on every rank, in rows
+        ``c * M / chunks + rank * M / (world * chunks) + ...`` of ``output_buffer()``. Collective: every rank runs
+        the chunks in the same order. A caller that stages A chunk by chunk (host buffers) calls this directly."""
+        import ctypes
+
+        import torch
+
+        from . import _capi, make_desc
+        if self.exchange not in ("peer_store", "multicast") or self.world == 1:
+            raise ValueError("run_chunk() belongs to the exchanges that run inside the GEMM kernel")
+        if out_dtype is None:
+            out_dtype = self._symm_out.dtype if self._symm_out is not None else A_blk.dtype
+        self.output_buffer(out_dtype, A_blk.device)
+        if A_blk.dtype != torch.bfloat16 or B.dtype != torch.bfloat16:
             raise ValueError("the fused exchanges take bfloat16 inputs; use exchange='nccl' for float32")
         key = (out_dtype, self.activation, self.b_layout)
         if getattr(self, "_desc_key", None) != key:
-            self._desc = make_desc(self.M, self.N, self.K, _capi.DT_BF16,
+            self._desc = make_desc(self.M // self.chunks, self.N, self.K, _capi.DT_BF16,
                                    _capi.DT_F32 if out_dtype == torch.float32 else _capi.DT_BF16,
                                    b_layout=self.b_layout, activation=self.activation)
             self._desc_key = key
-        A_local = A_local.contiguous()
-        B = B.contiguous()
         mode = _capi.XCHG_MULTICAST if self.exchange == "multicast" else _capi.XCHG_UNICAST
-        s = torch.cuda.current_stream(A_local.device).cuda_stream
+        s = stream if stream is not None else torch.cuda.current_stream(A_blk.device).cuda_stream
+        cc = self._chunk_comms[c]
+        cc.epoch = self._comm.epoch  # one call counter for all chunks: the flags are shared
         rc = _capi.load().symplex_b200_sharded_gemm(
-            ctypes.byref(self._desc), A_local.data_ptr(), B.data_ptr(), bias.data_ptr() if bias is not None else None,
-            ctypes.byref(self._comm), mode, s)
+            ctypes.byref(self._desc), A_blk.data_ptr(), B.data_ptr(), bias.data_ptr() if bias is not None else None,
+            ctypes.byref(cc), mode, s)
+        self._comm.epoch = cc.epoch
         _capi.check(rc)
-        return out
 
     def _host_handshake(self):
         """Before a step is launched, every rank posts its step number in the process group's store and waits,
