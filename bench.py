@@ -48,7 +48,23 @@ WORKLOADS = {
                                                 act="gelu", bias=True, sharded=False),
     "cfg4_batched_fp32_2048x64_cube": dict(M=64, N=64, K=64, batch=2048, dt="f32", out="f32", b_col=False, act=None,
                                            bias=False, sharded=False),
+    # Workloads that reach the kernels the ones above do not (for profiling and for the record; not in `secondary`):
+    # the single-CTA bf16 kernel (what small and narrow problems run), the 256 x 256 CTA-pair tile, the fp32
+    # pre-pass with a transposing split (row-major B), bf16 operands whose rows are not 16-byte multiples (padded
+    # copies first), and the f64 product behind blas_dgemm.
+    "aux_bf16_2048_cube_single_cta_tiles": dict(M=2048, N=2048, K=2048, batch=1, dt="bf16", out="bf16", b_col=False,
+                                                act=None, bias=False, sharded=False, options={"pair_mode": 0}),
+    "aux_bf16_2048_cube_pair_256x256_tiles": dict(M=2048, N=2048, K=2048, batch=1, dt="bf16", out="bf16", b_col=False,
+                                                  act=None, bias=False, sharded=False, options={"pair_mode": 1}),
+    "aux_fp32_4096_cube_rowmajor_b": dict(M=4096, N=4096, K=4096, batch=1, dt="f32", out="f32", b_col=False, act=None,
+                                          bias=False, sharded=False),
+    "aux_bf16_4096x4096x4100_unaligned_rows": dict(M=4096, N=4096, K=4100, batch=1, dt="bf16", out="bf16", b_col=True,
+                                                   act=None, bias=False, sharded=False),
+    "aux_f64_2048_cube": dict(M=2048, N=2048, K=2048, batch=1, dt="f64", out="f64", b_col=False, act=None, bias=False,
+                              sharded=False),
 }
+SECONDARY = ["headline_bf16_8192_cube_bias_gelu", "cfg1_fp32_512_cube", "cfg2_bf16_4096_cube_colmajor_b",
+             "cfg2_fp32_4096_cube_colmajor_b", "cfg3_fused_gelu_mlp_8192x4096x16384", "cfg4_batched_fp32_2048x64_cube"]
 DEFAULT_WORKLOAD = "cfg5_row_sharded_bf16_65536x8192x8192"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
@@ -84,6 +100,10 @@ ELEMENTWISE_WORKLOADS = {
     # the f64 twin (what the reference's Python layer calls for float64 NumPy arrays)
     "f3_fused_axpb_f64_64M": dict(n=64 << 20, n_inputs=1, ops=[(2, 0, 0, 1, 0), (0, 2, 0, 1, 1)], consts=[2.0, 1.0],
                                   reduce_op=255, desc="dst = x * 2.0 + 1.0 (float64)", f64=True),
+    # arrays that start 4 bytes off a 16-byte boundary: the plain-load kernel instead of the bulk-copy ring
+    "f3_fused_axpb_store_unaligned_64M": dict(n=64 << 20, n_inputs=1, ops=[(2, 0, 0, 1, 0), (0, 2, 0, 1, 1)],
+                                              consts=[2.0, 1.0], reduce_op=255, desc="dst = x * 2.0 + 1.0, unaligned arrays",
+                                              misalign=1),
 }
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -320,8 +340,9 @@ def main_elementwise(args):
     peaks, peak_note = load_peaks()
     g = torch.Generator(device=dev).manual_seed(99 + rank)
     tdt = torch.float64 if f64 else torch.float32
-    arrays = [torch.rand(n, device=dev, generator=g, dtype=tdt) * 2 - 1 for _ in range(w["n_inputs"])]
-    out = None if reduce else torch.empty(n, device=dev, dtype=tdt)
+    mis = int(w.get("misalign", 0))  # elements by which every array is shifted off its 16-byte boundary
+    arrays = [(torch.rand(n + mis, device=dev, generator=g, dtype=tdt) * 2 - 1)[mis:] for _ in range(w["n_inputs"])]
+    out = None if reduce else torch.empty(n + mis, device=dev, dtype=tdt)[mis:]
 
     # Arguments of the C-ABI call are packed once: a step is then one library call = one kernel launch, with
     # a few microseconds of host work (the kernels run 0.1-0.2 ms, so per-step Python work would show).
@@ -414,7 +435,8 @@ def main_elementwise(args):
     roofline = {"bound": "hbm", "achieved": ach, "peak": float(peaks["hbm_gbs"]), "unit": "GB/s",
                 "frac": ach / float(peaks["hbm_gbs"]), "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
                 "kernel_ms": ms_per_step, "peak_kind": f"HBM copy, {peak_note}", "bytes_per_launch": algo_bytes,
-                "note": "one step = one launch of fused_elementwise_ring_kernel"}
+                "note": "one step = one launch of " + ("fused_elementwise_plain_kernel" if mis else
+                                                         "fused_elementwise_ring_kernel")}
     cpu_baseline = None
     if not args.no_cpu_baseline and world == 1:
         gbs, dt, sample = _elementwise_cpu(w, 16 << 20, steps=3, warmup=1)
@@ -501,6 +523,12 @@ class Ctx:
     """Process-wide state of one benchmark run (one rank)."""
 
 
+def _capi_check(rc):
+    if rc != 0:
+        from symplex_b200 import _capi
+        raise SystemExit(f"symplex_b200 call failed ({rc}): {_capi.last_error()}")
+
+
 def parity_check(ctx, w, A_of_rows, B, bias, C, row_base, n_rows_total):
     """Check a finished product on the device, in fp64: (i) where the epilogue is linear, the whole-output identity
     C.1 = A.(B.1) + N-sum of the bias over this rank's rows of A against the gathered C; (ii) 64 sampled rows of the
@@ -523,7 +551,7 @@ def parity_check(ctx, w, A_of_rows, B, bias, C, row_base, n_rows_total):
         want = torch.clamp(want, min=0)
     got = C[rows].double()
     rel = float((got - want).norm() / want.norm().clamp_min(1e-300))
-    tol = 1e-2 if (w["dt"] == "bf16" or w["out"] == "bf16") else 1e-5
+    tol = 1e-2 if (w["dt"] == "bf16" or w["out"] == "bf16") else (1e-13 if w["dt"] == "f64" else 1e-5)
     res["max_rel"] = rel
     res["tolerance"] = tol
     res["ok"] = bool(rel <= tol)
@@ -548,6 +576,7 @@ def parity_check(ctx, w, A_of_rows, B, bias, C, row_base, n_rows_total):
         ident = float((lhs - rhs).norm() / sc.norm())
         res["checksum_rel"] = ident
         res["ok"] = bool(res["ok"] and ident <= (1e-3 if w["out"] == "bf16" else 1e-5))
+
     return res
 
 
@@ -563,9 +592,15 @@ def run_gemm_workload(ctx, args, name, primary):
     config = base_config(name, w, args.gpus)
     detail = {}
 
-    tdt = torch.bfloat16 if w["dt"] == "bf16" else torch.float32
-    odt = torch.bfloat16 if w["out"] == "bf16" else torch.float32
+    f64 = w["dt"] == "f64"
+    tdt = torch.bfloat16 if w["dt"] == "bf16" else (torch.float64 if f64 else torch.float32)
+    odt = torch.bfloat16 if w["out"] == "bf16" else (torch.float64 if f64 else torch.float32)
     M, N, K, batch = w["M"], w["N"], w["K"], w["batch"]
+    saved_options = []
+    for oname, oval in (w.get("options") or {}).items():  # tuning overrides that select the kernel under test
+        saved_options.append((oname.encode(), lib.symplex_b200_get_option(oname.encode())))
+        _capi_check(lib.symplex_b200_set_option(oname.encode(), int(oval)))
+        detail.setdefault("options", {})[oname] = oval
     g = torch.Generator(device=dev).manual_seed(1234)  # same B on every rank
     b_shape = (N, K) if w["b_col"] else (K, N)
     scale = 0.02 if w["act"] == "gelu" else 1.0
@@ -605,7 +640,8 @@ def run_gemm_workload(ctx, args, name, primary):
         ga = torch.Generator(device=dev).manual_seed(100 + rank)
         a_shape = (batch, M, K) if batch > 1 else (M, K)
         # small problems: rotate over several operand sets so each step reads cold data (larger than L2 in total)
-        bytes_per_set = (M * K + K * N) * batch * (2 if w["dt"] == "bf16" else 4) + M * N * batch * (2 if w["out"] == "bf16" else 4)
+        esz = {"bf16": 2, "f32": 4, "f64": 8}
+        bytes_per_set = (M * K + K * N) * batch * esz[w["dt"]] + M * N * batch * esz[w["out"]]
         nsets = 1 if bytes_per_set > 256e6 else int(min(64, 512e6 // bytes_per_set + 1))
         As = [(torch.randn(a_shape, device=dev, generator=ga) * scale).to(tdt) for _ in range(nsets)]
         Bs = [Bm] + [(torch.randn_like(Bm.float()) * scale).to(tdt) for _ in range(nsets - 1)]
@@ -615,10 +651,18 @@ def run_gemm_workload(ctx, args, name, primary):
                         f"({nsets * bytes_per_set / 1e6:.0f} MB > L2) so every step reads cold data")
         ctx.local_A = As[0] if batch == 1 else None
 
+        stream = torch.cuda.current_stream(dev).cuda_stream
+
+        def gemm_into(A_, B_, C_):
+            if f64:  # the product behind blas_dgemm / cache_tiled_dgemm_thin, on device pointers
+                _capi_check(lib.symplex_b200_dgemm(A_.data_ptr(), B_.data_ptr(), C_.data_ptr(), M, N, K, 0, 0, 0, stream))
+            else:
+                sx.gemm(A_, B_, bias=bias, activation=w["act"], out=C_, b_layout=b_layout)
+
         def step():
             i = counter[0] % nsets
             counter[0] += 1
-            sx.gemm(As[i], Bs[i], bias=bias, activation=w["act"], out=Cs[i], b_layout=b_layout)
+            gemm_into(As[i], Bs[i], Cs[i])
         launches_per_step_flops = flops_of(w)
     if sharded:
         detail["l2"] = "inputs larger than L2 (per GPU: A %.0f MiB, B %.0f MiB, C %.0f MiB)" % (
@@ -750,11 +794,11 @@ def run_gemm_workload(ctx, args, name, primary):
             return buf
         check = parity_check(ctx, w, A_of_rows, Bm, bias, C, 0, M)
     elif batch == 1:
-        sx.gemm(As[0], Bs[0], bias=bias, activation=w["act"], out=Cs[0], b_layout=b_layout)
+        gemm_into(As[0], Bs[0], Cs[0])
         torch.cuda.synchronize()
         check = parity_check(ctx, w, lambda rows: As[0][rows], Bs[0], bias, Cs[0], 0, M)
     else:
-        sx.gemm(As[0], Bs[0], bias=bias, activation=w["act"], out=Cs[0], b_layout=b_layout)
+        gemm_into(As[0], Bs[0], Cs[0])
         torch.cuda.synchronize()
         want = torch.bmm(As[0].double(), (Bs[0].transpose(-1, -2) if w["b_col"] else Bs[0]).double())
         rel = float((Cs[0].double() - want).norm() / want.norm())
@@ -789,6 +833,8 @@ def run_gemm_workload(ctx, args, name, primary):
         e2e = run_e2e(args, w, sx, lib, torch, dist, dev, rank, world, Bm, bias, b_layout, tdt, odt,
                       op if sharded else None, scale)
     ctx.local_A = None
+    for oname, old in saved_options:
+        lib.symplex_b200_set_option(oname, old)
     if rank != 0:
         return None
 
@@ -796,10 +842,16 @@ def run_gemm_workload(ctx, args, name, primary):
     traffic = NCU_TRAFFIC_BYTES.get(name)
     if sharded:  # rows of A per launch, scaled from the 8192-row capture of the same kernel
         traffic = NCU_TRAFFIC_PER_8192_ROWS_BF16_N8192_K8192 * (M / args.gpus / detail["chunks"]) / 8192.0
-    tensor_bound = w["dt"] == "bf16" or w["K"] >= 1024
+    tensor_bound = w["dt"] in ("bf16", "f64") or w["K"] >= 1024
     if w["dt"] == "bf16":
         peak = float(peaks["bf16_tflops"])
         peak_desc = f"bf16 dense burst, {peak_note}"
+    elif f64:
+        # No measured fp64 figure exists for these boards; NVIDIA quotes 40 TFLOP/s (fp64, vector and tensor alike) for
+        # the part. The kernel also rounds every product and sum separately, as the reference does: 2 instructions per
+        # multiply-add, so half of that figure is its own ceiling.
+        peak = 40.0
+        peak_desc = "nominal fp64 rate of the part (no measured figure); unfused multiply + add halves it"
     else:
         peak = float(peaks["bf16_tflops"]) / 6.0
         peak_desc = f"derived 3xTF32 ceiling = bf16 burst / 2 / 3, {peak_note}"
@@ -833,7 +885,7 @@ def run_gemm_workload(ctx, args, name, primary):
     line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if sharded else "weak", "vs_baseline": None,
-            "dtype": "bf16" if w["dt"] == "bf16" else "f32 (3xTF32 on tensor cores)", "data": "synthetic",
+            "dtype": {"bf16": "bf16", "f32": "f32 (3xTF32 on tensor cores)", "f64": "f64"}[w["dt"]], "data": "synthetic",
             "config": config, "detail": detail,
             "frac_of_bf16_peak": value / (args.gpus * float(peaks["bf16_tflops"])),
             "roofline": roofline, "parity_check": check, "gpu_launches": launches, "clocks": clocks}
@@ -916,9 +968,7 @@ def main():
         line = run_gemm_workload(ctx, args, args.workload, primary=True)
         if world == 1 and args.workload == DEFAULT_WORKLOAD and not args.no_secondary:
             secondary = []
-            for name in WORKLOADS:
-                if name == args.workload:
-                    continue
+            for name in SECONDARY:
                 torch.cuda.empty_cache()
                 sec = run_gemm_workload(ctx, args, name, primary=False)
                 secondary.append({k: sec[k] for k in ("config", "detail", "value", "unit", "steps", "warmup", "ms_per_step",

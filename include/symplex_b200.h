@@ -5,8 +5,10 @@
  * tiled dense matmul and the elementwise epilogues fused into it on a B200. Plain pointers and sizes
  * only. Unless a function says otherwise it returns 0 on success or one of the negative
  * SYMPLEX_ERR_* codes; nothing throws across this boundary and there is no CPU fallback: without a
- * usable GPU every compute entry point fails with SYMPLEX_ERR_DRIVER (void entry points leave C
- * untouched and record the error for symplex_b200_last_error()).
+ * usable GPU every compute entry point fails with SYMPLEX_ERR_DRIVER. The void entry points, which
+ * have no return value, fill C with NaN when they fail for any reason (no device, out of memory, a
+ * device-side timeout) and record why: symplex_b200_last_error() reads "no error" after a void entry
+ * point that succeeded.
  */
 #ifndef SYMPLEX_B200_H
 #define SYMPLEX_B200_H

@@ -94,8 +94,9 @@ def matmul_tiled(A, B) -> np.ndarray:
     C = np.zeros((M, N), dtype=np.float32)
     lib = _capi.load()
     lib.symplex_matmul_tiled_f32(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K)
-    if M and N and K and not lib.symplex_cuda_available():
-        raise SymplexB200Error(_capi.ERR_DRIVER, _capi.last_error())
+    # The C entry point has no return value; after a failure it has filled C with NaN and left the reason.
+    if M and N and _capi.last_error() != "no error":
+        raise SymplexB200Error(_capi.ERR_EXEC if lib.symplex_cuda_available() else _capi.ERR_DRIVER, _capi.last_error())
     return C
 
 

@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <limits>
 #include <memory>
 #include <mutex>
 
@@ -809,6 +810,19 @@ static int fe_host(const symplex_fused_op* ops, size_t n_ops, const void* const*
   return SX_OK;
 }
 
+// The void drop-ins have no return value to report a failure with (no device, out of memory, a device-side
+// timeout). They make it impossible to miss instead: C is filled with NaN, and symplex_b200_last_error() holds the
+// reason; after a successful call it reads "no error".
+template <typename T>
+static void void_abi_result(int64_t rc, T* C, size_t count) {
+  if (rc == 0) {
+    snprintf(g_err, sizeof(g_err), "no error");
+    return;
+  }
+  if (C != nullptr)
+    for (size_t i = 0; i < count; ++i) C[i] = std::numeric_limits<T>::quiet_NaN();
+}
+
 }  // namespace sx
 
 // =================================================================== extern "C"
@@ -1025,9 +1039,10 @@ int64_t symplex_exec_fused_matmul_bias_relu(const float* a, const float* b, floa
 void symplex_matmul_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K) {
   if (M > 0 && N > 0 && K == 0) {  // kernels/matmul.c zeroes C before accumulating
     memset(C, 0, (size_t)M * N * sizeof(float));
+    snprintf(g_err, sizeof(g_err), "no error");
     return;
   }
-  (void)sgemm_host(A, B, C, M, N, K);
+  void_abi_result(sgemm_host(A, B, C, M, N, K), C, M > 0 && N > 0 ? (size_t)M * (size_t)N : 0);
 }
 void symplex_matmul_tiled_f32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K) {
   symplex_matmul_f32(A, B, C, M, N, K);
@@ -1087,10 +1102,10 @@ static int dgemm_host(const double* a, const double* b, double* c, size_t m, siz
 }
 
 void blas_dgemm(const double* a, const double* b, double* c, size_t m, size_t n, size_t k) {
-  (void)dgemm_host(a, b, c, m, n, k);
+  void_abi_result(dgemm_host(a, b, c, m, n, k), c, m * n);
 }
 void cache_tiled_dgemm_thin(const double* a, const double* b, double* c, size_t m, size_t n, size_t k) {
-  (void)dgemm_host(a, b, c, m, n, k);
+  void_abi_result(dgemm_host(a, b, c, m, n, k), c, m * n);
 }
 
 int64_t symplex_b200_exec_tensor_matmul(const uint8_t* rec, size_t len, void* const* slots, size_t nslots) {

@@ -169,6 +169,7 @@ struct FeMath<float> {
   __device__ static void store16_streaming(float* p, const float (&v)[4]) {
     __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
   }
+  __device__ static uint32_t bits(float a) { return __float_as_uint(a); }
 };
 template <>
 struct FeMath<double> {
@@ -194,6 +195,10 @@ struct FeMath<double> {
   }
   __device__ static void store16_streaming(double* p, const double (&v)[2]) {
     __stcs(reinterpret_cast<double2*>(p), make_double2(v[0], v[1]));
+  }
+  __device__ static uint32_t bits(double a) {
+    const unsigned long long u = (unsigned long long)__double_as_longlong(a);
+    return (uint32_t)u ^ (uint32_t)(u >> 32);
   }
 };
 
@@ -514,8 +519,14 @@ fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P)
       ld.stride = CHUNK;
       T res[W];
       fe_eval<T, W, MAXOPS>(P, ld, res);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp's reads of the stage are done
+      // Hand the stage back only after the values computed from it exist: the arrive takes a warp vote over a fold
+      // of the results as an operand, so neither the compiler nor the hardware can issue it while a shared-memory
+      // load of this stage (or the arithmetic that consumes it) is still outstanding in any lane.
+      uint32_t fold = 0;
+#pragma unroll
+      for (int i = 0; i < W; ++i) fold |= FeMath<T>::bits(res[i]);
+      const uint32_t vote = __ballot_sync(0xffffffffu, fold == 0x5a5a5a5au);
+      if (lane == 0) mbar_arrive_after(&empty_bar[stage], vote);  // this warp's reads of the stage are done
       if (reduce) {
         fe_accumulate<T, W>(P.reduce_op, acc, res);
       } else {

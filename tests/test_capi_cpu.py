@@ -125,6 +125,13 @@ def test_no_gpu_fails_loudly_never_computes(lib):
     assert core.cuda_matmul(A.ctypes.data, A.ctypes.data, C.ctypes.data, 8, 8, 8) == -1
     assert core.jit_parallel_matmul(A.ctypes.data, A.ctypes.data, C.ctypes.data, 8, 8, 8) < 0
     assert np.all(C == -3.0)
+    # the void drop-ins cannot return a code: they poison C and leave the reason
+    lib.symplex_matmul_f32(A.ctypes.data, A.ctypes.data, C.ctypes.data, 8, 8, 8)
+    assert np.isnan(C).all() and _capi.last_error() != "no error"
+    D = np.full((8, 8), -3.0)
+    Ad = np.ones((8, 8))
+    lib.blas_dgemm(Ad.ctypes.data, Ad.ctypes.data, D.ctypes.data, 8, 8, 8)
+    assert np.isnan(D).all()
     info = core.cuda_device_info()
     assert info["available"] is False and "error" in info
     with pytest.raises(sx.SymplexB200Error):

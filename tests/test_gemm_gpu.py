@@ -1,6 +1,6 @@
 """Parity of the CUDA path against the CPU oracle, through the C ABI, on a B200.
 
-Tolerances are BASELINE's: relative Frobenius error <= 1e-5 for the fp32 (3xTF32) path against the
+Tolerances of the task statement: relative Frobenius error <= 1e-5 for the fp32 (3xTF32) path against the
 reference's fp32 result, <= 1e-2 for bf16 inputs against the reference run on bf16-rounded inputs.
 Large configurations are checked on a sample of rows (exact for a row-partitioned contraction) plus a
 whole-output checksum identity.
@@ -39,7 +39,7 @@ def _bf16_t(x_np):
 # ------------------------------------------------------------------ fp32 path, host-pointer drop-ins
 
 def test_config1_fp32_512_cube(lib, oracle):
-    """BASELINE config 1: the shape the reference's own JIT-vs-NumPy bench runs."""
+    """The fp32 512-cube: the shape the reference's own JIT-vs-NumPy bench runs."""
     rng = np.random.default_rng(0)
     A = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
     B = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
@@ -147,7 +147,7 @@ def _run(A_t, B_t, **kw):
 
 
 def test_config2_bf16_4096_colmajor_b(lib, oracle):
-    """BASELINE config 2 (bf16): row-major A, column-major B, fp32 output; oracle on 512 sampled rows."""
+    """The bf16 4096-cube: row-major A, column-major B, fp32 output; oracle on 512 sampled rows."""
     rng = np.random.default_rng(2)
     n = 4096
     A = oracle.bf16_round(rng.standard_normal((n, n)).astype(np.float32))
@@ -181,7 +181,7 @@ def _checksum_identity(C, A, B, tol):
 
 
 def test_config3_fused_gelu_mlp_layer(lib, oracle):
-    """BASELINE config 3: Y = GELU(X.W + b), bf16 in/out, one kernel; oracle on 96 sampled rows."""
+    """The fused MLP layer Y = GELU(X.W + b), bf16 in/out, one kernel; oracle on 96 sampled rows."""
     rng = np.random.default_rng(4)
     M, K, N = 8192, 4096, 16384
     X = oracle.bf16_round(rng.normal(0, 0.02, (M, K)).astype(np.float32))
@@ -199,7 +199,7 @@ def test_config3_fused_gelu_mlp_layer(lib, oracle):
 
 
 def test_config4_batched_small_gemm(lib, oracle):
-    """BASELINE config 4: 2048 independent fp32 64x64x64 problems, strided-batched."""
+    """The batched small GEMM: 2048 independent fp32 64x64x64 problems, strided-batched."""
     rng = np.random.default_rng(5)
     nb = 2048
     A = rng.uniform(-1, 1, (nb, 64, 64)).astype(np.float32)
@@ -212,7 +212,7 @@ def test_config4_batched_small_gemm(lib, oracle):
 
 
 def test_config5_row_sharded_shape_on_one_gpu(lib, oracle):
-    """BASELINE config 5 at one GPU: bf16 [65536, 8192] x [8192, 8192] -> bf16, no collective."""
+    """The row-sharded product on one GPU: bf16 [65536, 8192] x [8192, 8192] -> bf16, no collective."""
     from symplex_b200.sharding import RowShardedGemm
     g = torch.Generator(device=DEV).manual_seed(6)
     M, N, K = 65536, 8192, 8192
@@ -547,7 +547,7 @@ def test_plan_describes_what_is_launched(lib, M, N, K, dtype, batch):
 
 @pytest.mark.parametrize("split", [1, 2, 4])
 @pytest.mark.parametrize("M,N,K,batch", [
-    (512, 512, 512, 1),      # BASELINE config 1: 32 tiles, 16 k-blocks
+    (512, 512, 512, 1),      # the fp32 512-cube: 32 tiles, 16 k-blocks
     (128, 64, 8192, 1),      # one tile, long K
     (200, 100, 300, 1),      # ragged edges; 10 k-blocks split 3,3,2,2
     (96, 64, 1056, 100),     # 100 tiles on 37 clusters: each cluster loops over several tiles

@@ -15,7 +15,7 @@ from symplex_b200.sharding import ShardingStrategy
 
 
 def test_plan_matches_row_sharded_config():
-    # BASELINE config 5: A [65536, 8192] split by rows, B replicated, bf16 C all-gathered
+    # the row-sharded workload: A [65536, 8192] split by rows, B replicated, bf16 C all-gathered
     plan = sharding.analyze_matmul(65536, 8192, 8192, 8)
     a, b, c = plan.tensor_shards
     assert (a.strategy, a.local_shape) == (ShardingStrategy.SHARD_DIM_0, [8192, 8192])
