@@ -522,9 +522,10 @@ fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P)
       // Hand the stage back only after the values computed from it exist: the arrive takes a warp vote over a fold
       // of the results as an operand, so neither the compiler nor the hardware can issue it while a shared-memory
       // load of this stage (or the arithmetic that consumes it) is still outstanding in any lane.
+      // (one element per 16-byte vector is enough: a vector load returns its elements together)
       uint32_t fold = 0;
 #pragma unroll
-      for (int i = 0; i < W; ++i) fold |= FeMath<T>::bits(res[i]);
+      for (int i = 0; i < W; i += VE) fold |= FeMath<T>::bits(res[i]);
       const uint32_t vote = __ballot_sync(0xffffffffu, fold == 0x5a5a5a5au);
       if (lane == 0) mbar_arrive_after(&empty_bar[stage], vote);  // this warp's reads of the stage are done
       if (reduce) {
