@@ -370,6 +370,15 @@ static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_
     if (cost512 <= cost256 && cost512 <= cost0) mode = 2;
     else if (cost256 <= cost0) mode = 1;
   }
+  // Row-sharded products whose exchange takes longer than their math (inbound bytes at the measured peer-copy
+  // rate against the flops at the kernel's sustained rate): the link is the critical path from the first finished
+  // tile to the last, so the 256 x 256 tiles, whose first tile is ready in half the time, beat the wider tile's better
+  // tensor-pipe utilisation.
+  if (n_peers > 0 && mode == 2) {
+    const double compute_s = 2.0 * (double)p.M * (double)p.N * (double)p.K / (1663.5e12 * 0.85);
+    const double link_s = (double)p.M * (double)p.N * (p.bf16_out ? 2.0 : 4.0) * n_peers / 770e9;
+    if (link_s > compute_s) mode = 1;
+  }
   if (opt.pair_mode.load(std::memory_order_relaxed) >= 0) mode = (int)opt.pair_mode.load(std::memory_order_relaxed);
   if (n_peers > 0 && mode == 0) mode = 1;  // only the pair kernels carry the peer-store epilogue
   return {mode == 2 ? KK_BF16_PAIR512 : mode == 1 ? KK_BF16_PAIR256 : KK_BF16_TC, bn};

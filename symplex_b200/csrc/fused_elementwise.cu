@@ -519,18 +519,21 @@ fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P)
       ld.stride = CHUNK;
       T res[W];
       fe_eval<T, W, MAXOPS>(P, ld, res);
-      // Hand the stage back only after the values computed from it exist: the arrive takes a warp vote over a fold
-      // of the results as an operand, so neither the compiler nor the hardware can issue it while a shared-memory
-      // load of this stage (or the arithmetic that consumes it) is still outstanding in any lane.
-      // (one element per 16-byte vector is enough: a vector load returns its elements together)
-      uint32_t fold = 0;
-#pragma unroll
-      for (int i = 0; i < W; i += VE) fold |= FeMath<T>::bits(res[i]);
-      const uint32_t vote = __ballot_sync(0xffffffffu, fold == 0x5a5a5a5au);
-      if (lane == 0) mbar_arrive_after(&empty_bar[stage], vote);  // this warp's reads of the stage are done
+      // Hand the stage back only after the values computed from it exist, so that neither the compiler nor the
+      // hardware can have a shared-memory load of this stage (or the arithmetic that consumes it) outstanding when
+      // the producer is allowed to overwrite it.
       if (reduce) {
+        // The arrive takes a warp vote over a fold of the results as an operand (one element per 16-byte vector is
+        // enough: a vector load returns its elements together).
+        uint32_t fold = 0;
+#pragma unroll
+        for (int i = 0; i < W; i += VE) fold |= FeMath<T>::bits(res[i]);
+        const uint32_t vote = __ballot_sync(0xffffffffu, fold == 0x5a5a5a5au);
+        if (lane == 0) mbar_arrive_after(&empty_bar[stage], vote);
         fe_accumulate<T, W>(P.reduce_op, acc, res);
       } else {
+        // The global stores below take every result as an operand and cannot be moved across the arrive (both are
+        // memory operations): once they have issued, the loads have returned.
         T* out = P.dst + c * CHUNK + tid * VE;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -539,6 +542,8 @@ fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P)
           for (int k = 0; k < VE; ++k) v[k] = res[u * VE + k];
           FeMath<T>::store16_streaming(out + u * (FE_THREADS * VE), v);
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);  // this warp's reads of the stage are done
       }
       if (++stage == stages) {
         stage = 0;

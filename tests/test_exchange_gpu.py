@@ -45,9 +45,12 @@ def _sharded(lib, desc, A_local, B, bias, comm, mode=_capi.XCHG_UNICAST):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("shape", [(2048, 1024, 512), (1024, 520, 136), (8192, 2048, 256), (600, 264, 72)])
-def test_forwarders_copy_every_tile_to_the_peer(lib, oracle, shape, out_dtype):
-    M, N, K = shape
+@pytest.mark.parametrize("shape", [(2048, 1024, 512), (1024, 520, 136), (8192, 2048, 256), (600, 264, 72),
+                                   (4096, 1024, 512, 1), (4096, 1024, 512, 2)])
+def test_forwarders_copy_every_tile_to_the_peer(lib, oracle, set_option, shape, out_dtype):
+    if len(shape) == 4:  # both tile shapes of the CTA-pair kernel carry the forwarder warps
+        set_option("pair_mode", shape[3])
+    M, N, K = shape[:3]
     world, m_loc = 2, M // 2
     g = torch.Generator(device=DEV).manual_seed(5)
     A = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
