@@ -62,6 +62,12 @@ WORKLOADS = {
                                                    act=None, bias=False, sharded=False),
     "aux_f64_2048_cube": dict(M=2048, N=2048, K=2048, batch=1, dt="f64", out="f64", b_col=False, act=None, bias=False,
                               sharded=False),
+    # The kernel of the row-sharded product (GEMM + forwarder warps) on ONE GPU: rank 0 of 4, whose three "peers" are
+    # buffers in this GPU's own memory and whose flags are preset, so the one kernel never waits for another. Same
+    # tiles, same forwarder traffic (3 x 256 MiB of stores per step) as one rank of a 4-GPU run, without NVLink.
+    "aux_bf16_sharded_kernel_rank0_of_4_local_peers": dict(M=16384, N=8192, K=8192, batch=1, dt="bf16", out="bf16",
+                                                           b_col=False, act=None, bias=False, sharded=False,
+                                                           emulate_ranks=4),
 }
 SECONDARY = ["headline_bf16_8192_cube_bias_gelu", "cfg1_fp32_512_cube", "cfg2_bf16_4096_cube_colmajor_b",
              "cfg2_fp32_4096_cube_colmajor_b", "cfg3_fused_gelu_mlp_8192x4096x16384", "cfg4_batched_fp32_2048x64_cube"]
@@ -228,6 +234,12 @@ def _load_cpu_reference():
         orc.lib.oracle_jit_parallel_matmul(A.ctypes.data, B.ctypes.data, C.ctypes.data, M, N, K,
                                            _parts(cores, M, N, K))
     return run, "port", cores, f"oracle port of jit_parallel_matmul, row blocks on up to {cores} threads"
+
+
+def cpu_step_seconds(args):
+    """Seconds of CPU work one step of the CPU arm is sized for: a row sample of up to ~3 s, shrunk so that all of the
+    arm's steps end within about a minute. Both arms size their sample with this, so they time the same rows."""
+    return max(0.25, min(3.0, 60.0 / (args.steps + max(1, args.warmup))))
 
 
 def cpu_sample(w, rows):
@@ -652,12 +664,41 @@ def run_gemm_workload(ctx, args, name, primary):
         ctx.local_A = As[0] if batch == 1 else None
 
         stream = torch.cuda.current_stream(dev).cuda_stream
+        emu = int(w.get("emulate_ranks", 0))
+        if emu:
+            import ctypes as _ct
+            from symplex_b200 import _capi as _c
+            peers_c = [torch.empty(emu * M, N, device=dev, dtype=odt) for _ in range(emu - 1)]
+            flags_ = [torch.full((64,), 1 << 30, device=dev, dtype=torch.int32) for _ in range(emu)]
+            emu_desc = sx.make_desc(emu * M, N, K, sx.DT_BF16, sx.DT_BF16 if w["out"] == "bf16" else sx.DT_F32)
+            emu_full = {}
+            detail["exchange"] = (f"rank 0 of {emu}: forwarder warps copy every tile to {emu - 1} buffers in local memory; "
+                                  "flags preset (no other kernel is waited for)")
 
         def gemm_into(A_, B_, C_):
-            if f64:  # the product behind blas_dgemm / cache_tiled_dgemm_thin, on device pointers
+            if emu:  # C_ is rank 0's rows; the communicator wants the full buffer they are the top of
+                key = C_.data_ptr()
+                if key not in emu_full:
+                    comm = _c.Comm()
+                    comm.rank, comm.world = 0, emu
+                    full = torch.empty(emu * M, N, device=dev, dtype=odt)
+                    comm.c_base[0] = full.data_ptr()
+                    for r in range(1, emu):
+                        comm.c_base[r] = peers_c[r - 1].data_ptr()
+                    for r in range(emu):
+                        comm.flags[r] = flags_[r].data_ptr()
+                    emu_full[key] = (comm, full)
+                comm, full = emu_full[key]
+                _capi_check(lib.symplex_b200_sharded_gemm(_ct.byref(emu_desc), A_.data_ptr(), B_.data_ptr(), None,
+                                                          _ct.byref(comm), _c.XCHG_UNICAST, stream))
+                if not emu_timed[0]:
+                    C_.copy_(full[:M])
+            elif f64:  # the product behind blas_dgemm / cache_tiled_dgemm_thin, on device pointers
                 _capi_check(lib.symplex_b200_dgemm(A_.data_ptr(), B_.data_ptr(), C_.data_ptr(), M, N, K, 0, 0, 0, stream))
             else:
                 sx.gemm(A_, B_, bias=bias, activation=w["act"], out=C_, b_layout=b_layout)
+
+        emu_timed = [True]  # the timed steps leave the result in the communicator's buffer; the check copies it out
 
         def step():
             i = counter[0] % nsets
@@ -794,9 +835,13 @@ def run_gemm_workload(ctx, args, name, primary):
             return buf
         check = parity_check(ctx, w, A_of_rows, Bm, bias, C, 0, M)
     elif batch == 1:
+        emu_timed[0] = False
         gemm_into(As[0], Bs[0], Cs[0])
         torch.cuda.synchronize()
         check = parity_check(ctx, w, lambda rows: As[0][rows], Bs[0], bias, Cs[0], 0, M)
+        if emu:  # every "peer" buffer received rank 0's rows as well
+            check["peers_identical"] = bool(all(torch.equal(pc[:M], Cs[0]) for pc in peers_c))
+            check["ok"] = bool(check["ok"] and check["peers_identical"])
     else:
         gemm_into(As[0], Bs[0], Cs[0])
         torch.cuda.synchronize()
@@ -892,7 +937,8 @@ def run_gemm_workload(ctx, args, name, primary):
     if primary:
         cpu_baseline = None
         if not args.no_cpu_baseline and world == 1:
-            tfl, dt, kind, cores, sample = time_cpu_reference(w, 4.0, steps=3, warmup=1)
+            # the same row sample as the `--impl reference` arm takes for these --steps / --warmup, timed 3 times
+            tfl, dt, kind, cores, sample = time_cpu_reference(w, cpu_step_seconds(args), steps=3, warmup=1)
             cpu_baseline = {"value": tfl, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample}
             try:
                 cpu_baseline["all"] = cpu_baselines(w, 3.0)
@@ -931,9 +977,7 @@ def main():
         if rank != 0:
             return 0
         config = base_config(args.workload, w, args.gpus)
-        # a step is a row sample of up to ~3 s (sized by a calibration pass), shrunk so that all steps end within about a minute
-        seconds = max(0.25, min(3.0, 60.0 / (args.steps + max(1, args.warmup))))
-        tflops, dt, kind, cores, sample = time_cpu_reference(w, seconds, args.steps, max(1, args.warmup))
+        tflops, dt, kind, cores, sample = time_cpu_reference(w, cpu_step_seconds(args), args.steps, max(1, args.warmup))
         line = {"impl": "reference", "metric": "gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
                 "scaling": "strong" if w["sharded"] else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",

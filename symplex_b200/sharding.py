@@ -227,6 +227,10 @@ class RowShardedGemm:
         # for exchange="multicast"
         if self.exchange != "multicast":
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        elif os.environ.get("TORCH_SYMM_MEM_DISABLE_MULTICAST") == "1":
+            # an earlier unicast instance of this process switched multicast objects off; torch may have latched
+            # that at its first symmetric allocation, in which case the check below reports it
+            os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "0"
         buf = symm_mem.empty((self.M, self.N), dtype=dtype, device=device)
         flags = symm_mem.empty((64,), dtype=torch.int32, device=device)
         flags.zero_()
