@@ -426,6 +426,7 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
   g.K = p.K;
   g.wait_limit_ns = (unsigned long long)opt.wait_limit_ms.load(std::memory_order_relaxed) * 1000000ull;
   if (peers && peers->wait_limit_ns) g.wait_limit_ns = peers->wait_limit_ns;
+  g.group_m = (int)opt.group_m.load(std::memory_order_relaxed);
   if (n_peers > 0 && p.f32_in)
     return fail(SX_ERR_INVALID, "peer destinations are supported for bf16 inputs only");
   int rc;
@@ -506,7 +507,6 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
   const KernelChoice kc = choose_kernel(p, d->tile_n, st->num_sms, n_peers, false);
   g.bn = kc.bn;
   const int mode = kc.kind == KK_BF16_PAIR512 ? 2 : kc.kind == KK_BF16_PAIR256 ? 1 : 0;
-  g.group_m = (int)opt.group_m.load(std::memory_order_relaxed);
   g.tma_store = opt.tma_store.load(std::memory_order_relaxed) != 0;
   if (n_peers > 0) {
     g.n_peers = n_peers;

@@ -42,6 +42,19 @@ struct X3Cfg {
   static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
 };
 
+// Tile order: bands of group_m tile rows, column-major inside a band, so the tiles that run at the same time share
+// a band of A planes (group_m x 128 rows) and a sliding window of B planes that together fit in L2; walking all
+// tile rows of a column first (the whole of A's planes per column) re-streamed A from DRAM for every few columns.
+__device__ __forceinline__ void x3_tile(const GemmParams& p, int r, int BM, int BN, int& m0, int& n0) {
+  const int band = p.group_m * p.n_tiles;
+  const int g = r / band;
+  const int first_m = g * p.group_m;
+  const int gsz = min(p.m_tiles - first_m, p.group_m);
+  const int in_band = r - g * band;
+  m0 = (first_m + in_band % gsz) * BM;
+  n0 = (in_band / gsz) * BN;
+}
+
 template <typename OutT, int kBN>
 __global__ void __launch_bounds__(192, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -97,7 +110,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
         const int z = t / per, r = t - z * per;
-        const int m0 = (r % p.m_tiles) * BM, n0 = (r / p.m_tiles) * BN;
+        int m0, n0;
+        x3_tile(p, r, BM, BN, m0, n0);
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) { ok = false; break; }
           uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
@@ -175,7 +189,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     bool ok = true;
     for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
       const int z = t / per, r = t - z * per;
-      const int m0 = (r % p.m_tiles) * BM, n0 = (r / p.m_tiles) * BN;
+      int m0, n0;
+      x3_tile(p, r, BM, BN, m0, n0);
       float sum[BN];
 #pragma unroll
       for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
@@ -282,6 +297,7 @@ int launch_gemm_tf32x3(const TcGemmArgs& a, cudaStream_t stream) {
   p.status = a.status;
   p.m_tiles = (int)((a.M + 127) / 128);
   p.n_tiles = (int)((a.N + bn - 1) / bn);
+  p.group_m = a.group_m > 0 ? a.group_m : 8;
   const long long total = (long long)p.batch * p.m_tiles * p.n_tiles;
   const int grid = (int)(total < a.num_sms ? total : a.num_sms);
   if (a.out_bf16) {

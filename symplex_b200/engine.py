@@ -7,6 +7,7 @@ sm_100a library, so construction only checks that it can be loaded.
 from __future__ import annotations
 
 from . import _capi
+from .fusion import discover_fusions  # noqa: F401  (symplex_engine.discover_fusions, rust-engine/src/lib.rs:344-413)
 
 
 class _KernelBase:
