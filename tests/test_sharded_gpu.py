@@ -70,8 +70,8 @@ def _worker(rank, world, port, M, N, K, chunks, exchange, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange,chunks", [("peer_store", 1), ("multicast", 1), ("epilogue_tma", 1), ("nccl", 1),
-                                             ("nccl", 4)])
+@pytest.mark.parametrize("exchange,chunks", [("peer_store", 1), ("peer_store", 2), ("multicast", 1), ("epilogue_tma", 1),
+                                             ("nccl", 1), ("nccl", 4)])
 def test_row_sharded_gemm_matches_single_gpu(exchange, chunks):
     world = min(torch.cuda.device_count(), 8)
     if world < 2:
