@@ -169,7 +169,7 @@ struct FeMath<float> {
   __device__ static void store16_streaming(float* p, const float (&v)[4]) {
     __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
   }
-  __device__ static uint32_t bits(float a) { return __float_as_uint(a); }
+  __device__ static void pin(float a) { asm volatile("" ::"f"(a) : "memory"); }
 };
 template <>
 struct FeMath<double> {
@@ -196,10 +196,7 @@ struct FeMath<double> {
   __device__ static void store16_streaming(double* p, const double (&v)[2]) {
     __stcs(reinterpret_cast<double2*>(p), make_double2(v[0], v[1]));
   }
-  __device__ static uint32_t bits(double a) {
-    const unsigned long long u = (unsigned long long)__double_as_longlong(a);
-    return (uint32_t)u ^ (uint32_t)(u >> 32);
-  }
+  __device__ static void pin(double a) { asm volatile("" ::"d"(a) : "memory"); }
 };
 
 // Unary ops (and the pass-through for unknown codes) on W values.
@@ -523,13 +520,14 @@ fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P)
       // hardware can have a shared-memory load of this stage (or the arithmetic that consumes it) outstanding when
       // the producer is allowed to overwrite it.
       if (reduce) {
-        // The arrive takes a warp vote over a fold of the results as an operand (one element per 16-byte vector is
-        // enough: a vector load returns its elements together).
-        uint32_t fold = 0;
+        // Pin every result before the arrive at no cost: an empty volatile asm that takes the value as an operand
+        // makes the compiler produce it first (volatile asms keep their order, and the arrive is one), and a warp
+        // issues in order, so the instruction that produced it - which could only issue once its shared-memory
+        // operands had returned - has issued before the arrive does. __syncwarp brings all lanes to that point.
 #pragma unroll
-        for (int i = 0; i < W; i += VE) fold |= FeMath<T>::bits(res[i]);
-        const uint32_t vote = __ballot_sync(0xffffffffu, fold == 0x5a5a5a5au);
-        if (lane == 0) mbar_arrive_after(&empty_bar[stage], vote);
+        for (int i = 0; i < W; ++i) FeMath<T>::pin(res[i]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
         fe_accumulate<T, W>(P.reduce_op, acc, res);
       } else {
         // The global stores below take every result as an operand and cannot be moved across the arrive (both are

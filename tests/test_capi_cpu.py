@@ -188,3 +188,18 @@ def test_execute_kernel_args_validation(lib):
     assert lib.symplex_b200_execute(b"matmul", None) == _capi.ERR_INVALID
     if not lib.symplex_cuda_available():
         assert lib.symplex_b200_execute(b"symplex_matmul_4x5x6", ctypes.byref(ok)) == _capi.ERR_DRIVER
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 (and as C++) on its own."""
+    import shutil
+    import subprocess
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "symplex_b200.h"\nint main(void) { symplex_b200_comm c; symplex_gemm_desc d; (void)c; (void)d; return 0; }\n')
+    inc = os.path.join(ROOT, "include")
+    for cmd in (["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only"],
+                ["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++"]):
+        if shutil.which(cmd[0]) is None:
+            pytest.skip(f"{cmd[0]} not installed")
+        r = subprocess.run(cmd + ["-I", inc, str(src)], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
