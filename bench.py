@@ -68,6 +68,10 @@ WORKLOADS = {
     "aux_bf16_sharded_kernel_rank0_of_4_local_peers": dict(M=16384, N=8192, K=8192, batch=1, dt="bf16", out="bf16",
                                                            b_col=False, act=None, bias=False, sharded=False,
                                                            emulate_ranks=4),
+    # One rank of 8: 8192 local rows, seven destinations - the link-bound case, which takes the 256 x 256 tiles.
+    "aux_bf16_sharded_kernel_rank0_of_8_local_peers": dict(M=8192, N=8192, K=8192, batch=1, dt="bf16", out="bf16",
+                                                           b_col=False, act=None, bias=False, sharded=False,
+                                                           emulate_ranks=8),
 }
 SECONDARY = ["headline_bf16_8192_cube_bias_gelu", "cfg1_fp32_512_cube", "cfg2_bf16_4096_cube_colmajor_b",
              "cfg2_fp32_4096_cube_colmajor_b", "cfg3_fused_gelu_mlp_8192x4096x16384", "cfg4_batched_fp32_2048x64_cube"]
