@@ -943,7 +943,9 @@ int symplex_b200_sharded_gemm(const symplex_gemm_desc* d, const void* A_local, c
     pa.epoch = (int)(uint32_t)comm->epoch;  // compared modulo 2^32 on the device
     if (comm->wait_limit_ms > 0) pa.wait_limit_ns = (unsigned long long)comm->wait_limit_ms * 1000000ull;
   }
-  return run_gemm(&dl, p, A_local, B, C_local, bias, nullptr, scratch, st, s, &pa);
+  rc = run_gemm(&dl, p, A_local, B, C_local, bias, nullptr, scratch, st, s, &pa);
+  if (rc != SX_OK && pa.xchg != XCHG_EPILOGUE_TMA) comm->epoch -= 1;  // nothing was launched: not a collective call
+  return rc;
 }
 
 int symplex_b200_gemm_ws(const symplex_gemm_desc* d, const void* A, const void* B, void* C, const float* bias,

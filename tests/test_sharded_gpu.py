@@ -88,6 +88,8 @@ def test_row_sharded_gemm_matches_single_gpu(exchange, chunks):
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
+    if exchange == "multicast" and any("gave none" in r[6] for r in results):
+        pytest.skip("this box offers no NVLink multicast mapping")
     for rank, used, used_exchange, same, maxdiff, err, problem in sorted(results):
         assert not problem, f"rank {rank}: {problem}"
         assert used == chunks and used_exchange == exchange
