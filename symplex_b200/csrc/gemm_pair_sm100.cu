@@ -51,7 +51,9 @@ struct PairCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = kMB == 1 ? 6 : 4;
   static constexpr int EPI_WARPS = 4 * kMB;
-  static constexpr int FWD_WARPS = kFwd ? 2 : 0;  // copy finished tiles to the other GPUs (row-sharded products)
+  // Forwarder warps copy finished tiles to the other GPUs (row-sharded products). The 256 x 256 shape, which the
+  // link-bound calls take, has the registers for four of them (320 threads); the 512 x 256 shape for two (384).
+  static constexpr int FWD_WARPS = kFwd ? (kMB == 1 ? 4 : 2) : 0;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS + 32 * FWD_WARPS;
   static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
   static constexpr int STAGING_BYTES = 32 * 128;  // per epilogue warp: 32 rows x 128 bytes, 128B-swizzled
@@ -427,10 +429,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const PairTile tc = pair_tile<Cfg::BM, BN>(p, t);
       const int row_base = tc.m0 + int(cta_rank) * Cfg::ROWS;
       const long long tile_off = ((long long)tc.z * p.c_batch_stride + tc.n0) * (long long)sizeof(OutT);
-      for (int r = fw * U; r < Cfg::ROWS; r += Cfg::FWD_WARPS * U) {
-        if (row_base + r >= p.M) break;
-        uint4 v[U][CH];
-        long long off[U][CH];  // byte offset in C, or -1: outside the matrix
+      // Rounds of U rows, software-pipelined: the loads of the next round are in flight while this round is stored.
+      auto load_round = [&](int r, uint4 (&v)[U][CH], long long (&off)[U][CH]) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
 #pragma unroll
@@ -438,10 +438,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int row = row_base + r + u;
             const int colb = ch * 512 + lane * 16;
             const bool in = row < p.M && tc.n0 + colb / int(sizeof(OutT)) < p.N;  // rows are 16-byte multiples
-            off[u][ch] = in ? tile_off + (long long)row * p.ldc * (long long)sizeof(OutT) + colb : -1;
+            off[u][ch] = in ? tile_off + (long long)row * p.ldc * (long long)sizeof(OutT) + colb : -1;  // -1: outside C
             if (in) v[u][ch] = ld_global_cg_v4(cbase + off[u][ch]);
           }
         }
+      };
+      auto store_round = [&](const uint4 (&v)[U][CH], const long long (&off)[U][CH]) {
         if (p.xchg == XCHG_MULTICAST) {
           uint8_t* const mc = reinterpret_cast<uint8_t*>(p.mc_C);
 #pragma unroll
@@ -459,6 +461,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (off[u][ch] >= 0) st_global_v4(pc + off[u][ch], v[u][ch]);
           }
         }
+      };
+      constexpr int STEP = Cfg::FWD_WARPS * U;
+      uint4 va[U][CH], vb[U][CH];
+      long long oa[U][CH], ob[U][CH];
+      int r = fw * U;
+      bool have = r < Cfg::ROWS && row_base + r < p.M;
+      if (have) load_round(r, va, oa);
+      while (have) {
+        const int rn = r + STEP;
+        const bool next = rn < Cfg::ROWS && row_base + rn < p.M;
+        if (next) load_round(rn, vb, ob);
+        store_round(va, oa);
+        if (next) {
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch) {
+              va[u][ch] = vb[u][ch];
+              oa[u][ch] = ob[u][ch];
+            }
+        }
+        r = rn;
+        have = next;
       }
     }
     // Completion. Every forwarder warp checks in (also after a failure, so the counter returns to zero); the last
