@@ -34,10 +34,10 @@ static std::atomic<int64_t>* option_by_name(const char* name) {
   Options& o = options();
   struct Entry { const char* name; std::atomic<int64_t>* v; };
   const Entry table[] = {
-      {"tile_n", &o.tile_n}, {"pair_mode", &o.pair_mode}, {"f32_fused", &o.f32_fused},
+      {"tile_n", &o.tile_n}, {"pair_mode", &o.pair_mode}, {"stream_k", &o.stream_k}, {"f32_fused", &o.f32_fused},
       {"f32_split_k", &o.f32_split_k}, {"f32_tile_rows", &o.f32_tile_rows}, {"group_m", &o.group_m},
       {"tma_store", &o.tma_store}, {"pipeline_mb", &o.pipeline_mb}, {"pipeline", &o.pipeline},
-      {"wait_limit_ms", &o.wait_limit_ms}, {"trace", &o.trace},
+      {"wait_limit_ms", &o.wait_limit_ms}, {"trace", &o.trace}, {"stream_k_launches", &o.stream_k_launches},
   };
   for (const Entry& e : table)
     if (strcmp(e.name, name) == 0) return e.v;
@@ -136,6 +136,8 @@ struct DeviceState {
   int num_sms = 0;
   int* status = nullptr;  // device word written by kernels that unwind
   unsigned* xchg_counter = nullptr;  // device word of the sharded GEMM's forwarder warps (zero between launches)
+  int* sk_flags = nullptr;           // stream-K flag words of the pair kernel (zeroed once, then compared with sk_epoch)
+  int sk_epoch = 0;                  // stream-K launches so far on this device; advanced under `mu`
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   cudaEvent_t scratch_free = nullptr;  // recorded after the last launch that reads the pooled scratch
@@ -161,6 +163,8 @@ static int device_state(DeviceState** out) {
     SX_CUDA(cudaMalloc(&st.status, 64));
     SX_CUDA(cudaMemset(st.status, 0, 64));
     st.xchg_counter = reinterpret_cast<unsigned*>(st.status) + 8;
+    SX_CUDA(cudaMalloc(&st.sk_flags, stream_k_flag_words(st.num_sms) * sizeof(int)));
+    SX_CUDA(cudaMemset(st.sk_flags, 0, stream_k_flag_words(st.num_sms) * sizeof(int)));
     SX_CUDA(cudaEventCreateWithFlags(&st.scratch_free, cudaEventDisableTiming));
     SX_CUDA(cudaMalloc(&st.fe_scratch, FE_SCRATCH_SETS * FE_REDUCE_SCRATCH_BYTES));
     SX_CUDA(cudaMemset(st.fe_scratch, 0, FE_SCRATCH_SETS * FE_REDUCE_SCRATCH_BYTES));
@@ -335,9 +339,12 @@ enum KernelKind { KK_F32_FUSED, KK_F32_SPLIT, KK_BF16_TC, KK_BF16_PAIR256, KK_BF
 struct KernelChoice {
   KernelKind kind;
   int bn;  // tile width of the single-CTA kernels
+  bool stream_k = false;  // KK_BF16_PAIR512 only
 };
 
-static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_peers, bool f32_fused_ok) {
+// sk_ok: the caller can give the 512 x 256 pair kernel its stream-K workspace (pooled scratch, no peers).
+static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_peers, bool f32_fused_ok,
+                                  bool sk_ok = false) {
   const Options& opt = options();
   int forced = tile_n;
   if (opt.tile_n.load(std::memory_order_relaxed) != 0) forced = (int)opt.tile_n.load(std::memory_order_relaxed);
@@ -358,6 +365,7 @@ static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_
   // of 512x256 (108 us) rather than 4 of 256x256 (116 us); 2048^3 one wave of 256x256 pairs (19.6 us) rather than
   // two of 128x128 (28.4 us).
   int mode = 0;  // 0 single CTA, 1 pair 256x256, 2 pair 512x256
+  bool stream_k = false;
   if (forced == 0 && p.M > 128 && p.N >= 256) {
     const long long pairs = num_sms / 2;
     const long long nt = (p.N + 255) / 256;
@@ -366,7 +374,24 @@ static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_
     const double eff0 = bn == 256 ? 0.70 : bn == 128 ? 0.56 : 0.40;
     const double cost0 = (double)((t0 + num_sms - 1) / num_sms) * (128.0 * bn) / eff0;
     const double cost256 = (double)((t256 + pairs - 1) / pairs) * (128.0 * 256.0) / 0.80;
-    const double cost512 = p.M > 256 ? (double)((t512 + pairs - 1) / pairs) * (256.0 * 256.0) / 0.875 : 1e300;
+    double cost512 = p.M > 256 ? (double)((t512 + pairs - 1) / pairs) * (256.0 * 256.0) / 0.875 : 1e300;
+    // Stream-K removes the idle part of the last wave. It has two prices: the pairs no longer walk the k-blocks of
+    // neighbouring tiles in step, so fewer of their operand requests meet in L2 (measured: 7-8 % more time per
+    // k-block), and the partial sums make one trip through L2 (about 6 us, an eighth of a tile at K = 4096). Measured
+    // at burst clocks against whole tiles: 4608 x 4608 x 8192 (2.19 waves) +22 %, 8192 x 4864 x 8192 (4.11 waves) +22 %,
+    // 4096^3 (1.73 waves) -7 %, 5120 x 5120 x 8192 (2.70 waves) -4 %: taken when the last wave would leave more than
+    // 15 % of the pair-time unused.
+    const long long nkb = (p.K + 63) / 64;
+    const long long sk_setting = opt.stream_k.load(std::memory_order_relaxed);
+    if (sk_ok && sk_setting != 0 && n_peers == 0 && p.M > 256 && (t512 >= pairs || sk_setting > 0) && t512 * nkb >= pairs * 16 &&
+        t512 * nkb <= 0x7fffffffLL) {
+      const double waves = (double)((t512 + pairs - 1) / pairs);
+      const double cost_sk = ((double)t512 / (double)pairs * 1.08 + 0.125 * 64.0 / (double)nkb) * (256.0 * 256.0) / 0.875;
+      if (sk_setting > 0 || ((double)t512 / (waves * pairs) < 0.85 && cost_sk < cost512)) {
+        cost512 = cost_sk;
+        stream_k = true;
+      }
+    }
     if (cost512 <= cost256 && cost512 <= cost0) mode = 2;
     else if (cost256 <= cost0) mode = 1;
   }
@@ -381,7 +406,7 @@ static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_
   }
   if (opt.pair_mode.load(std::memory_order_relaxed) >= 0) mode = (int)opt.pair_mode.load(std::memory_order_relaxed);
   if (n_peers > 0 && mode == 0) mode = 1;  // only the pair kernels carry the peer-store epilogue
-  return {mode == 2 ? KK_BF16_PAIR512 : mode == 1 ? KK_BF16_PAIR256 : KK_BF16_TC, bn};
+  return {mode == 2 ? KK_BF16_PAIR512 : mode == 1 ? KK_BF16_PAIR256 : KK_BF16_TC, bn, stream_k && mode == 2};
 }
 
 // Peer destinations of a launch (row-sharded products); see Exchange in gemm_params.h.
@@ -405,12 +430,22 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
   const Options& opt = options();
   const int n_peers = peers ? peers->n_peers : 0;
   uint8_t* w = nullptr;
+  // The kernel of a bf16 product is chosen before any scratch is taken: stream-K adds its workspace behind the
+  // prepared operand copies, and the pooled block must be asked for once, at its full size.
+  KernelChoice kc{};
+  size_t sk_bytes = 0;
+  if (!p.f32_in) {
+    kc = choose_kernel(p, d->tile_n, st->num_sms, n_peers, false, scratch.pool != nullptr);
+    if (kc.stream_k) sk_bytes = stream_k_workspace_bytes(st->num_sms);
+  }
+  const size_t sk_off = align256(p.total);
   auto need_scratch = [&]() -> int {
-    if (w != nullptr || p.total == 0) return SX_OK;
+    const size_t want = sk_bytes ? sk_off + sk_bytes : p.total;
+    if (w != nullptr || want == 0) return SX_OK;
     void* ws = nullptr;
-    int rc = scratch.get(p.total, &ws);
+    int rc = scratch.get(want, &ws);
     if (rc != SX_OK) return rc;
-    if (ws == nullptr) return fail(SX_ERR_INVALID, "this problem needs %zu bytes of scratch", p.total);
+    if (ws == nullptr) return fail(SX_ERR_INVALID, "this problem needs %zu bytes of scratch", want);
     w = static_cast<uint8_t*>(ws);
     return SX_OK;
   };
@@ -504,7 +539,6 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
     g.B = Buse; g.ldb = ldb; g.b_plane_stride = b_bs;
   }
   if (n_peers > 7) return fail(SX_ERR_INVALID, "at most 7 peer destinations");
-  const KernelChoice kc = choose_kernel(p, d->tile_n, st->num_sms, n_peers, false);
   g.bn = kc.bn;
   const int mode = kc.kind == KK_BF16_PAIR512 ? 2 : kc.kind == KK_BF16_PAIR256 ? 1 : 0;
   g.tma_store = opt.tma_store.load(std::memory_order_relaxed) != 0;
@@ -523,10 +557,23 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
     }
   }
   if (mode == 2) g.bn = 512;
+  if (kc.stream_k) {
+    // The pool's mutex is held from here until the launch has been enqueued, so the flag words and the call number
+    // have one user at a time; the pool's event orders the launches of different streams on the GPU.
+    if ((rc = need_scratch()) != SX_OK) return rc;
+    g.sk_ws = reinterpret_cast<float*>(w + sk_off);
+    g.sk_flags = st->sk_flags;
+    if (st->sk_epoch == 0x7fffffff) {  // the call number wraps: start over from cleared flags
+      SX_CUDA(cudaDeviceSynchronize());
+      SX_CUDA(cudaMemset(st->sk_flags, 0, stream_k_flag_words(st->num_sms) * sizeof(int)));
+      st->sk_epoch = 0;
+    }
+    g.sk_epoch = ++st->sk_epoch;
+  }
   if (opt.trace.load(std::memory_order_relaxed))
-    fprintf(stderr, "[symplex_b200] gemm %lldx%lldx%lld batch %d bf16 -> %s, tile width %d, %d peer(s), exchange %d\n", p.M,
-            p.N, p.K, p.batch, mode == 2 ? "512x256 CTA pairs" : mode == 1 ? "256x256 CTA pairs" : "single-CTA tiles", g.bn,
-            n_peers, g.xchg);
+    fprintf(stderr, "[symplex_b200] gemm %lldx%lldx%lld batch %d bf16 -> %s%s, tile width %d, %d peer(s), exchange %d\n", p.M,
+            p.N, p.K, p.batch, mode == 2 ? "512x256 CTA pairs" : mode == 1 ? "256x256 CTA pairs" : "single-CTA tiles",
+            kc.stream_k ? " (stream-K)" : "", g.bn, n_peers, g.xchg);
   rc = mode != 0 ? launch_gemm_pair(g, stream) : launch_gemm_tc(g, stream);
   if (rc != SX_OK) {
     if (rc == SX_ERR_INVALID && strncmp(g_err, "cuTensorMap", 11) != 0)
@@ -536,6 +583,7 @@ static int run_gemm(const symplex_gemm_desc* d, const Plan& p, const void* A, co
     return rc;
   }
   ++g_launches;
+  if (kc.stream_k) options().stream_k_launches.fetch_add(1, std::memory_order_relaxed);
   return SX_OK;
 }
 
@@ -1343,7 +1391,7 @@ int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm
     return rc;
   }
   if (num_sms <= 0) num_sms = 148;
-  const KernelChoice kc = choose_kernel(p, d->tile_n, num_sms, 0, true);
+  const KernelChoice kc = choose_kernel(p, d->tile_n, num_sms, 0, true, true);
   KernelShape ks;
   double eff;  // fraction of the tensor peak the variant sustains on large problems (measured)
   switch (kc.kind) {
@@ -1371,7 +1419,7 @@ int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm
   if (kc.kind == KK_F32_FUSED && f32_fused_tile_rows(p.M) == 64)
     out->tiles = nt * ((p.batch + 1) / 2);  // that kernel's unit of work holds two problems' 64 x 64 tiles
   const long long units = num_sms / ks.cluster;  // persistent: one CTA (or one cluster) per SM (group of SMs)
-  const long long active = out->tiles < units ? out->tiles : units;
+  const long long active = kc.stream_k ? units : out->tiles < units ? out->tiles : units;
   out->grid_dims[0] = (int32_t)(active * ks.cluster); out->grid_dims[1] = 1; out->grid_dims[2] = 1;
   out->block_dims[0] = ks.threads; out->block_dims[1] = 1; out->block_dims[2] = 1;
   out->prepass_launches = kc.kind == KK_F32_SPLIT ? 2 : (p.a_prep ? 1 : 0) + (p.b_prep ? 1 : 0);
@@ -1385,7 +1433,9 @@ int symplex_b200_gemm_plan(const symplex_gemm_desc* d, int num_sms, symplex_gemm
   // pre-pass's extra read and write of the operands), a fixed launch cost per kernel.
   const double peak = p.f32_in ? 1663.5e12 / 6.0 : 1663.5e12;
   const long long waves = (out->tiles + units - 1) / units;
-  const double occupancy = (double)out->tiles / (double)(waves * units);
+  // Stream-K (the library's own scratch pool only, so not counted in workspace_bytes): every pair gets the same
+  // number of k-blocks; the partial sums' trip through L2 costs about 4 %.
+  const double occupancy = kc.stream_k ? 0.96 : (double)out->tiles / (double)(waves * units);
   const double t_tensor = out->flops / (peak * eff * occupancy);
   double hbm_bytes = out->bytes;
   if (kc.kind == KK_F32_SPLIT) hbm_bytes += 3.0 * ((double)p.M * p.K + (double)p.K * p.N) * 4.0 * p.batch;

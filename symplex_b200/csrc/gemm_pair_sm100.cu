@@ -28,6 +28,14 @@
 // written by the last forwarder warp of the grid and awaited by it, so the kernel ends only when the whole gathered
 // C is in place on this GPU.
 //
+// Stream-K (kSK instantiations, 512 x 256 tiles): when the tiles do not fill the last wave of CTA pairs, the k-blocks
+// of all tiles are laid out as one line and cut into one equal range per pair (PairWork below). A range that ends
+// inside a tile leaves that tile's partial sums, raw fp32 straight from tensor memory, in the pair's slot of a
+// workspace; the pair whose range holds the tile's last k-block adds them to its own accumulators in a fixed order
+// (nearest pair first) and runs the epilogue. A pair writes its partial sums FIRST and adds other pairs' sums LAST, and
+// only ever waits for pairs with a lower index, so the wait is over before it starts unless the grid is not
+// co-resident, and even then it cannot deadlock while CTAs are dispatched in index order.
+//
 // All waits are bounded (sm100_ptx.cuh); on a timeout every role unwinds and the kernel reports
 // ST_WAIT_TIMEOUT through the status word.
 #include <cuda_bf16.h>
@@ -85,7 +93,78 @@ __device__ __forceinline__ PairTile pair_tile(const GemmParams& p, int t) {
   return c;
 }
 
-template <typename OutT, bool kBmn, int kMB, bool kFwd>
+// The work of one CTA pair, item by item: (tile, k-blocks [kb0, kb1), kind).
+enum WorkKind : int { WORK_FULL = 0, WORK_PARTIAL = 1, WORK_OWNER = 2 };
+constexpr int SK_GRAIN = 4;  // range boundaries are multiples of this many k-blocks
+
+// First unit (tile * nkb + k-block) of pair q's range; q == pairs gives the end of the line.
+__device__ __forceinline__ long long sk_start(long long total_units, int pairs, int q) {
+  if (q >= pairs) return total_units;
+  return (total_units * q / pairs) / SK_GRAIN * SK_GRAIN;
+}
+
+template <bool kSK>
+struct PairWork {
+  int t, kb0, kb1, kind;  // the current item; t < 0: no more work
+  // whole tiles, strided (no stream-K) or consecutive (stream-K)
+  int next_full, end_full, stride, nkb;
+  // stream-K: the range's partial first tile (owner) and partial last tile (contributor)
+  int own_t, own_k0, part_t, part_k0, part_k1, stage;
+
+  __device__ PairWork(int pair_id, int num_pairs, int total_tiles, int nkb_) : nkb(nkb_) {
+    kb0 = 0;
+    kb1 = nkb;
+    kind = WORK_FULL;
+    own_t = part_t = -1;
+    own_k0 = part_k0 = part_k1 = 0;
+    stage = 0;
+    if constexpr (!kSK) {
+      next_full = pair_id;
+      end_full = total_tiles;
+      stride = num_pairs;
+    } else {
+      stride = 1;
+      const long long total = (long long)total_tiles * nkb;
+      const long long u0 = sk_start(total, num_pairs, pair_id), u1 = sk_start(total, num_pairs, pair_id + 1);
+      const int ta = int(u0 / nkb), ka = int(u0 - (long long)ta * nkb);
+      const int tb = int(u1 / nkb), kbe = int(u1 - (long long)tb * nkb);
+      if (ta == tb) {  // inside one tile and short of its end
+        next_full = end_full = 0;
+        if (u1 > u0) { part_t = ta; part_k0 = ka; part_k1 = kbe; }
+      } else {
+        if (kbe > 0) { part_t = tb; part_k0 = 0; part_k1 = kbe; }
+        if (ka > 0) { own_t = ta; own_k0 = ka; }
+        next_full = ka > 0 ? ta + 1 : ta;
+        end_full = tb;
+      }
+    }
+    next();
+  }
+  __device__ bool valid() const { return t >= 0; }
+  __device__ void next() {
+    if constexpr (!kSK) {
+      t = next_full < end_full ? next_full : -1;
+      next_full += stride;
+    } else {
+      // order: the contribution to another pair's tile, whole tiles, the tile that needs other pairs' contributions
+      if (stage == 0) {
+        stage = 1;
+        if (part_t >= 0) { t = part_t; kb0 = part_k0; kb1 = part_k1; kind = WORK_PARTIAL; return; }
+      }
+      if (stage == 1) {
+        if (next_full < end_full) { t = next_full++; kb0 = 0; kb1 = nkb; kind = WORK_FULL; return; }
+        stage = 2;
+      }
+      if (stage == 2) {
+        stage = 3;
+        if (own_t >= 0) { t = own_t; kb0 = own_k0; kb1 = nkb; kind = WORK_OWNER; return; }
+      }
+      t = -1;
+    }
+  }
+};
+
+template <typename OutT, bool kBmn, int kMB, bool kFwd, bool kSK>
 __global__ void __launch_bounds__(PairCfg<kMB, kFwd>::THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ DstMaps dst, const GemmParams p) {
@@ -143,11 +222,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       uint32_t armed = 0, armed_phase = 0;  // leader: stages whose copies (of both CTAs) may still be in flight
       bool ok = true;
-      for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
-        const PairTile tc = pair_tile<Cfg::BM, BN>(p, t);
+      for (PairWork<kSK> w(pair_id, num_pairs, total_tiles, nkb); ok && w.valid(); w.next()) {
+        const PairTile tc = pair_tile<Cfg::BM, BN>(p, w.t);
         const int my_m0 = tc.m0 + int(cta_rank) * Cfg::ROWS;
         const int my_n0 = tc.n0 + int(cta_rank) * 128;
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag, wait_ns)) { ok = false; break; }
           uint8_t* sa = tiles + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
@@ -211,11 +290,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           umma<2, 0>(tmem_base + mb * BN, smem_desc(a_hi, a_addr + k * 32), smem_desc(b_hi, b_addr + k * b_kstep),
                      idesc, accumulate | (k != 0 ? 1u : 0u));
       };
-      for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
+      for (PairWork<kSK> w(pair_id, num_pairs, total_tiles, nkb); ok && w.valid(); w.next()) {
+        const int nk = w.kb1 - w.kb0;  // k-blocks of this item, counted from 0 below
         if constexpr (kMB == 1) {
           if (!mbar_wait<true>(&acc_empty[slot], acc_phase ^ 1, &abort_flag, wait_ns)) break;
           tc_fence_after_sync();
-          for (int kb = 0; kb < nkb; ++kb) {
+          for (int kb = 0; kb < nk; ++kb) {
             if (!mbar_wait(&full_bar[stage], phase, &abort_flag, wait_ns)) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t a_addr = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
@@ -235,8 +315,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // first and the last SKEW k-blocks are issued block-major, so block 0 completes 4*SKEW MMAs before
           // block 1 and the next tile can start on block 0 while block 1 is still being drained.
           constexpr int SKEW = 2;
-          const int head_end = min(SKEW, nkb);
-          const int tail_begin = max(head_end, nkb - SKEW);
+          const int head_end = min(SKEW, nk);
+          const int tail_begin = max(head_end, nk - SKEW);
           auto group = [&](int g0, int g1) {  // k-blocks [g0, g1) block-major
             for (int mb = 0; mb < 2 && ok; ++mb) {
               if (g0 == 0) {
@@ -254,7 +334,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (mb == 1) umma_commit_pair(&empty_bar[s], 3);
                 advance(s, ph);
               }
-              if (ok && g1 == nkb) umma_commit_pair(&acc_full[mb], 3);
+              if (ok && g1 == nk) umma_commit_pair(&acc_full[mb], 3);
             }
             for (int kb = g0; kb < g1; ++kb) advance(stage, phase);
           };
@@ -274,7 +354,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             umma_commit_pair(&empty_bar[stage], 3);
             advance(stage, phase);
           }
-          if (ok && tail_begin < nkb) group(tail_begin, nkb);
+          if (ok && tail_begin < nk) group(tail_begin, nk);
           if (!ok) break;
           acc_phase ^= 1;
         }
@@ -293,8 +373,53 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int slot = 0;
     uint32_t acc_phase = 0, fwd_phase = 0;
     bool ok = true;
-    for (int t = pair_id; ok && t < total_tiles; t += num_pairs) {
-      const PairTile tc = pair_tile<Cfg::BM, BN>(p, t);
+    // Stream-K: this warp's chunks (32 rows x 32 columns of fp32, lane-interleaved float4s) inside a pair's slot of the
+    // workspace, and its flag word. A warp only ever exchanges partial sums with the same warp of the same CTA rank
+    // of another pair, which drains the same part of the tile.
+    constexpr int SK_CHUNK = 32 * 32;  // floats
+    constexpr int SK_SLOT = 2 * kMB * Cfg::EPI_WARPS * STRIPS * SK_CHUNK;
+    const int sk_warp_word = int(cta_rank) * Cfg::EPI_WARPS + (warp - 2);
+    auto sk_chunk = [&](int pair, int blk, int c) -> float* {
+      return p.sk_ws + (long long)pair * SK_SLOT +
+             (((int(cta_rank) * kMB + blk) * Cfg::EPI_WARPS + (warp - 2)) * STRIPS + (c - half * STRIPS)) * SK_CHUNK + lane * 4;
+    };
+    auto sk_dump = [&](const uint32_t (&r)[32], float* dst) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        st_global_v4(dst + j * 128, make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
+    };
+    auto sk_add = [&](float (&v)[32], int contributors, int blk, int c) {
+      for (int i = 0; i < contributors; ++i) {  // fixed order: the nearest pair first
+        const float* src = sk_chunk(pair_id - 1 - i, blk, c);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {  // four 16-byte loads in flight per lane
+          uint4 x[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) x[j] = ld_global_cg_v4(src + (4 * h + j) * 128);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            v[16 * h + 4 * j] += __uint_as_float(x[j].x);
+            v[16 * h + 4 * j + 1] += __uint_as_float(x[j].y);
+            v[16 * h + 4 * j + 2] += __uint_as_float(x[j].z);
+            v[16 * h + 4 * j + 3] += __uint_as_float(x[j].w);
+          }
+        }
+      }
+    };
+    for (PairWork<kSK> w(pair_id, num_pairs, total_tiles, nkb); ok && w.valid(); w.next()) {
+      const PairTile tc = pair_tile<Cfg::BM, BN>(p, w.t);
+      int contributors = 0;  // stream-K, WORK_OWNER: pairs whose partial sums belong to this tile
+      if constexpr (kSK) {
+        if (w.kind == WORK_OWNER) {
+          const long long total = (long long)total_tiles * nkb, tile_u0 = (long long)w.t * nkb;
+          for (int q = pair_id - 1; q >= 0 && sk_start(total, num_pairs, q + 1) > tile_u0; --q) ++contributors;
+          for (int i = lane; i < contributors; i += 32)
+            ok = ok && flag_wait_ge_gpu(p.sk_flags + (pair_id - 1 - i) * (2 * Cfg::EPI_WARPS) + sk_warp_word, p.sk_epoch,
+                                        &abort_flag, wait_ns);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+      }
 #pragma unroll 1
       for (int blk = 0; blk < kMB; ++blk) {
         if constexpr (kMB == 2) slot = blk;
@@ -312,18 +437,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_32x32(taddr, r0);
           tmem_ld_32x32(taddr + 32, r1);
           tmem_ld_wait();
+          if constexpr (kSK) {
+            if (w.kind == WORK_PARTIAL) {  // raw partial sums, whatever part of them lies inside C
+              sk_dump(r0, sk_chunk(pair_id, blk, c));
+              sk_dump(r1, sk_chunk(pair_id, blk, c + 1));
+              continue;
+            }
+          }
           const int col0 = tc.n0 + c * 32;
           if (col0 >= p.N) continue;
           const bool second = col0 + 32 < p.N;
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r0[j]);
+          if constexpr (kSK) sk_add(v, contributors, blk, c);
           ep.template math<true>(v, row_ok, row_off, col0);
           if (p.n_dst == 0) {
             ep.store(v, row_ok, row_off, col0);
             if (!second) continue;
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
+            if constexpr (kSK) sk_add(v, contributors, blk, c + 1);
             ep.template strip<true>(v, row_ok, row_off, col0 + 32);
           } else {
             // Staged path: the warp's 32 x 128-byte block goes to shared memory and one lane hands it to the
@@ -344,6 +478,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (second) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r1[j]);
+              if constexpr (kSK) sk_add(v, contributors, blk, c + 1);
               ep.template math<true>(v, row_ok, row_off, col0 + 32);
               if constexpr (sizeof(OutT) == 4) {
                 if (lane == 0) bulk_wait_group_read<0>();
@@ -370,6 +505,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (++slot == 2) { slot = 0; acc_phase ^= 1; }
       } else {
         acc_phase ^= 1;
+      }
+      if constexpr (kSK) {
+        if (ok && w.kind == WORK_PARTIAL) {  // this warp's part of the partial sums is in the workspace
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) flag_store_release_gpu(p.sk_flags + pair_id * (2 * Cfg::EPI_WARPS) + sk_warp_word, p.sk_epoch);
+        }
       }
       if constexpr (kFwd) {
         // Tell the forwarder warps that this warp's part of the tile is in the local C.
@@ -521,11 +663,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // ------------------------------------------------------------------ host side
 namespace {
 
-template <typename OutT, bool kBmn, int kMB, bool kFwd>
+template <typename OutT, bool kBmn, int kMB, bool kFwd, bool kSK = false>
 int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const DstMaps& dst, const GemmParams& p, int pairs,
                 cudaStream_t stream) {
   using Cfg = PairCfg<kMB, kFwd>;
-  auto kern = gemm_pair_kernel<OutT, kBmn, kMB, kFwd>;
+  auto kern = gemm_pair_kernel<OutT, kBmn, kMB, kFwd, kSK>;
   SX_ENSURE_DYN_SMEM(kern, Cfg::DYN_SMEM);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
@@ -545,6 +687,7 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const DstMaps& d
 template <typename OutT, bool kBmn>
 int launch_pair_mb(int mb, const CUtensorMap& tmA, const CUtensorMap& tmB, const DstMaps& dst, const GemmParams& p,
                    int pairs, cudaStream_t stream) {
+  if (p.sk_ws != nullptr) return launch_pair<OutT, kBmn, 2, false, true>(tmA, tmB, dst, p, pairs, stream);
   if (p.xchg >= XCHG_FORWARD)
     return mb == 2 ? launch_pair<OutT, kBmn, 2, true>(tmA, tmB, dst, p, pairs, stream)
                    : launch_pair<OutT, kBmn, 1, true>(tmA, tmB, dst, p, pairs, stream);
@@ -648,7 +791,19 @@ int launch_gemm_pair(const TcGemmArgs& a, cudaStream_t stream) {
   }
   const long long total = (long long)p.batch * p.m_tiles * p.n_tiles;
   const int max_pairs = a.num_sms / 2;
-  const int pairs = (int)(total < max_pairs ? total : max_pairs);
+  int pairs = (int)(total < max_pairs ? total : max_pairs);
+  if (a.sk_ws != nullptr) {
+    // Stream-K: every pair of the device takes an equal range of k-blocks. Each range must be long enough to hold
+    // the grain it is rounded to, or a pair would be left without work and the owner of its tile would wait for it.
+    const long long nkb = (a.K + 63) / 64;
+    if (mb != 2 || a.n_peers > 0 || a.sk_flags == nullptr || a.sk_epoch == 0 || total * nkb < (long long)max_pairs * 2 * SK_GRAIN ||
+        total * nkb > 0x7fffffffLL || reinterpret_cast<uintptr_t>(a.sk_ws) % 16)
+      return SX_ERR_INVALID;
+    p.sk_ws = a.sk_ws;
+    p.sk_flags = a.sk_flags;
+    p.sk_epoch = a.sk_epoch;
+    pairs = max_pairs;
+  }
   if (a.out_bf16)
     return a.b_mn ? launch_pair_mb<__nv_bfloat16, true>(mb, tmA, tmB, dmaps, p, pairs, stream)
                   : launch_pair_mb<__nv_bfloat16, false>(mb, tmA, tmB, dmaps, p, pairs, stream);
@@ -656,6 +811,9 @@ int launch_gemm_pair(const TcGemmArgs& a, cudaStream_t stream) {
                 : launch_pair_mb<float, false>(mb, tmA, tmB, dmaps, p, pairs, stream);
 }
 
+
+size_t stream_k_workspace_bytes(int num_sms) { return (size_t)(num_sms / 2) * 512 * 256 * sizeof(float); }
+int stream_k_flag_words(int num_sms) { return (num_sms / 2) * 2 * PairCfg<2>::EPI_WARPS; }
 
 KernelShape describe_gemm_pair(int kmb) {
   auto mk = [](auto cfg) {

@@ -52,6 +52,12 @@ struct GemmParams {
   unsigned* xchg_counter;  // device word of this GPU, zero between launches: forwarder warps that have finished
   unsigned long long wait_limit_ns;  // bound of every device-side wait of this launch
   int fault_stop_early;    // self-test only: the TMA producer leaves out the last k-block of the first tile
+  // Stream-K (512 x 256 pair kernel, sk_ws != null): the k-blocks of all tiles are cut into one equal range per CTA
+  // pair; a pair that works on a part of a tile without its last k-block leaves its partial sums in its slot of
+  // sk_ws and raises its words of sk_flags to sk_epoch, the pair with the tile's last k-block adds them.
+  float* sk_ws;            // one slot of 512 x 256 floats per CTA pair of the grid
+  int* sk_flags;           // 16 words per CTA pair (2 CTAs x 8 epilogue warps), never reset: compared with sk_epoch
+  int sk_epoch;            // number of this launch among the stream-K launches of the device (!= 0)
 };
 
 // How the tiles of a row-sharded product reach the other GPUs.

@@ -74,7 +74,14 @@ struct TcGemmArgs {
   unsigned* xchg_counter;
   unsigned long long wait_limit_ns;  // 0 = the default bound (2 s)
   int fault_stop_early;              // single-CTA kernel, self-test only
+  // 512 x 256 pair kernel: stream-K over the k-blocks of all tiles (GemmParams::sk_*). Not with peers.
+  float* sk_ws;
+  int* sk_flags;
+  int sk_epoch;
 };
+// Stream-K of the 512 x 256 pair kernel: bytes of partial-sum workspace and flag words for a device with num_sms SMs.
+size_t stream_k_workspace_bytes(int num_sms);
+int stream_k_flag_words(int num_sms);
 
 int launch_gemm_tc(const TcGemmArgs& a, cudaStream_t stream);
 int pick_bn(long long M, long long N, int batch, int num_sms, int forced);

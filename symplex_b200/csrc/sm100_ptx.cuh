@@ -197,6 +197,28 @@ __device__ __forceinline__ bool flag_wait_ge(const int* flag, int want, volatile
     }
   }
 }
+// The same for a flag that another CTA of this GPU writes (stream-K partial sums): device scope.
+__device__ __forceinline__ void flag_store_release_gpu(int* flag, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool flag_wait_ge_gpu(const int* flag, int want, volatile int* abort_flag, uint64_t limit_ns) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v - want >= 0) return true;
+    __nanosleep(64);
+    if ((it & 31u) == 0u) {
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
 // 16-byte copies for the forwarder warps: loads that bypass L1 (the data was just written through L2 by TMA), plain
 // stores to a peer's mapped memory, and one store to a multicast mapping that the NVSwitch replicates to every GPU
 // bound to it (stores only: nothing in this library loads from a multicast or peer address).
