@@ -60,16 +60,18 @@ WORKLOADS = {
                                           bias=False, sharded=False),
     "aux_bf16_4096x4096x4100_unaligned_rows": dict(M=4096, N=4096, K=4100, batch=1, dt="bf16", out="bf16", b_col=True,
                                                    act=None, bias=False, sharded=False),
-    # 304 tiles of 512 x 256 on 74 CTA pairs are 4.11 waves: the library takes stream-K by itself (the pairs share
-    # the k-blocks of all tiles evenly); the second entry forces the same tiles whole, five waves, for comparison.
+    # 304 tiles of 512 x 256 on 74 CTA pairs are 4.11 waves. First entry: stream-K (the pairs share the k-blocks of
+    # all tiles evenly; an option, off by default); second: the same tiles whole, five waves, what the option replaces.
     "aux_bf16_8192x4864x8192_stream_k": dict(M=8192, N=4864, K=8192, batch=1, dt="bf16", out="bf16", b_col=False,
-                                             act=None, bias=False, sharded=False),
+                                             act=None, bias=False, sharded=False,
+                                             options={"stream_k": 1, "pair_mode": 2}),
     "aux_bf16_8192x4864x8192_whole_512x256_tiles": dict(M=8192, N=4864, K=8192, batch=1, dt="bf16", out="bf16",
                                                         b_col=False, act=None, bias=False, sharded=False,
                                                         options={"stream_k": 0, "pair_mode": 2}),
-    # The smallest shape of that kind used for the ncu capture: 162 tiles = 2.19 waves.
+    # The smallest shape of that kind, used for the ncu capture: 162 tiles = 2.19 waves.
     "aux_bf16_4608x4608x4096_stream_k": dict(M=4608, N=4608, K=4096, batch=1, dt="bf16", out="bf16", b_col=False,
-                                             act=None, bias=False, sharded=False),
+                                             act=None, bias=False, sharded=False,
+                                             options={"stream_k": 1, "pair_mode": 2}),
     "aux_f64_2048_cube": dict(M=2048, N=2048, K=2048, batch=1, dt="f64", out="f64", b_col=False, act=None, bias=False,
                               sharded=False),
     # The kernel of the row-sharded product (GEMM + forwarder warps) on ONE GPU: rank 0 of 4, whose three "peers" are

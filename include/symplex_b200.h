@@ -208,9 +208,9 @@ int symplex_b200_sync_status(void* stream);
 int symplex_b200_selftest_wait_timeout(const void* A, const void* B, void* C, int32_t limit_ms, void* stream);
 
 /* Process-wide tuning overrides, for tests and experiments: "tile_n" (0 auto, 64/128/256), "pair_mode" (-1 auto,
- * 0 single-CTA tiles, 1 256x256 CTA pairs, 2 512x256 CTA pairs), "stream_k" (-1 auto, 0 never, 1 whenever the 512x256
- * pairs run from the library's own scratch pool: the pairs share the k-blocks of all tiles evenly instead of whole
- * tiles; "stream_k_launches" counts such launches), "f32_fused" (-1 auto, 0, 1), "f32_split_k" (0 auto,
+ * 0 single-CTA tiles, 1 256x256 CTA pairs, 2 512x256 CTA pairs), "stream_k" (0; 1: bf16 problems take the 512x256 pairs with
+ * the k-blocks of all tiles shared evenly among them instead of whole tiles, wherever the library's own scratch pool
+ * serves the call - measured no faster than whole tiles on B200, hence off; "stream_k_launches" counts such launches), "f32_fused" (-1 auto, 0, 1), "f32_split_k" (0 auto,
  * 1, 2, 4), "f32_tile_rows" (0 auto, 128), "group_m" (0 auto), "tma_store" (1, 0), "pipeline_mb" (96),
  * "pipeline" (1, 0), "wait_limit_ms" (2000), "trace" (0, 1: one line per GEMM dispatch on stderr). Only "tile_n"
  * and "trace" can also be preset from the environment (SYMPLEX_B200_TILE, SYMPLEX_B200_TRACE, read once at load);

@@ -375,22 +375,19 @@ static KernelChoice choose_kernel(const Plan& p, int tile_n, int num_sms, int n_
     const double cost0 = (double)((t0 + num_sms - 1) / num_sms) * (128.0 * bn) / eff0;
     const double cost256 = (double)((t256 + pairs - 1) / pairs) * (128.0 * 256.0) / 0.80;
     double cost512 = p.M > 256 ? (double)((t512 + pairs - 1) / pairs) * (256.0 * 256.0) / 0.875 : 1e300;
-    // Stream-K removes the idle part of the last wave. It has two prices: the pairs no longer walk the k-blocks of
-    // neighbouring tiles in step, so fewer of their operand requests meet in L2 (measured: 7-8 % more time per
-    // k-block), and the partial sums make one trip through L2 (about 6 us, an eighth of a tile at K = 4096). Measured
-    // at burst clocks against whole tiles: 4608 x 4608 x 8192 (2.19 waves) +22 %, 8192 x 4864 x 8192 (4.11 waves) +22 %,
-    // 4096^3 (1.73 waves) -7 %, 5120 x 5120 x 8192 (2.70 waves) -4 %: taken when the last wave would leave more than
-    // 15 % of the pair-time unused.
+    // Stream-K (the pairs share the k-blocks of all tiles evenly) is built and tested but never chosen by itself:
+    // measured process by process on shapes whose last wave is mostly idle, it is within +-4 % of the better of the
+    // two whole-tile shapes (4608 x 4608 x 4096, 2.19 waves: 0.134 ms against 0.138 on whole 512 x 256 tiles and 0.134
+    // on 256 x 256 tiles; 8192 x 4864 x 8192, 4.11 waves: 0.481 against 0.476; sustained runs under the power cap:
+    // 0.549 against 0.534). These GEMMs are bound by what the whole chip shares - the L2 -> SM path at burst clocks,
+    // the power limit in long runs - so pairs that idle in the last wave cost far less than their share, and the
+    // extra L2 traffic of stream-K (partial sums, operand requests that no longer coincide) eats the rest.
+    // The option stream_k = 1 takes it wherever it can run.
     const long long nkb = (p.K + 63) / 64;
     const long long sk_setting = opt.stream_k.load(std::memory_order_relaxed);
-    if (sk_ok && sk_setting != 0 && n_peers == 0 && p.M > 256 && (t512 >= pairs || sk_setting > 0) && t512 * nkb >= pairs * 16 &&
-        t512 * nkb <= 0x7fffffffLL) {
-      const double waves = (double)((t512 + pairs - 1) / pairs);
-      const double cost_sk = ((double)t512 / (double)pairs * 1.08 + 0.125 * 64.0 / (double)nkb) * (256.0 * 256.0) / 0.875;
-      if (sk_setting > 0 || ((double)t512 / (waves * pairs) < 0.85 && cost_sk < cost512)) {
-        cost512 = cost_sk;
-        stream_k = true;
-      }
+    if (sk_ok && sk_setting > 0 && n_peers == 0 && p.M > 256 && t512 * nkb >= pairs * 16 && t512 * nkb <= 0x7fffffffLL) {
+      cost512 = 0.0;
+      stream_k = true;
     }
     if (cost512 <= cost256 && cost512 <= cost0) mode = 2;
     else if (cost256 <= cost0) mode = 1;

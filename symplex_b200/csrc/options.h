@@ -14,7 +14,7 @@ struct Options {
   std::atomic<int64_t> f32_fused{-1};      // -1 auto; 0 / 1: fp32 operands split in shared memory instead of by a pre-pass
   std::atomic<int64_t> f32_split_k{0};     // 0 auto; 1 / 2 / 4: CTAs per output tile of the in-kernel-split fp32 kernel
   std::atomic<int64_t> f32_tile_rows{0};   // 0 auto; 128: problems with at most 64 rows also take the 128-row kernel
-  std::atomic<int64_t> stream_k{-1};       // -1 auto; 0 / 1: 512x256 CTA pairs share the k-blocks of all tiles evenly (bf16, pooled scratch)
+  std::atomic<int64_t> stream_k{0};        // 1: the 512x256 CTA pairs share the k-blocks of all tiles evenly wherever that can run (bf16, pooled scratch)
   std::atomic<int64_t> group_m{0};         // 0 auto; tile rows per band of the pair kernels' tile order
   std::atomic<int64_t> tma_store{1};       // 1: epilogues stage C in shared memory and store it by TMA where C qualifies
   std::atomic<int64_t> pipeline_mb{96};    // host-buffer GEMMs: MB of A + C per row chunk of the copy/compute pipeline

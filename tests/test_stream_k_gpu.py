@@ -1,7 +1,8 @@
 """Stream-K of the 512 x 256 CTA-pair kernel: the pairs share the k-blocks of all tiles evenly; a pair whose range ends
 inside a tile leaves raw partial sums in a workspace, the pair holding the tile's last k-block adds them (fixed order).
 
-Checked here: the result against the CPU oracle on sampled rows and against the whole-tile kernel on every element
+It is an option (`stream_k` = 1): on B200 it measured within a few percent of whole tiles either way, so the library
+does not choose it by itself. Checked here: the result against the CPU oracle on sampled rows and against the whole-tile kernel on every element
 (same products, another fp32 summation grouping: a few ulps before the output rounding), bit-identical repeats, one
 kernel launch, every epilogue and both layouts of B, ragged edges, tiles split across many pairs (forced on small
 problems), operands that need the repack pre-pass (the workspace then sits behind the repacked copies), batches, and
@@ -40,21 +41,20 @@ def _oracle_rows(oracle, A, B, rows, b_layout, bias=None, act=_capi.ACT_NONE, bf
     return oracle.bf16_round(ref) if bf16 else ref
 
 
-def test_auto_stream_k_on_a_mostly_idle_last_wave(lib, oracle, set_option):
-    """4608 x 4608: 162 tiles of 512 x 256 on 74 pairs are 2.19 waves - the third wave would keep 14 pairs busy and 60
-    idle; the library picks stream-K by itself. 4096^3 (1.73 waves) stays on whole tiles, which measured faster."""
+def test_stream_k_on_a_mostly_idle_last_wave(lib, oracle, set_option):
+    """4608 x 4608: 162 tiles of 512 x 256 on 74 pairs are 2.19 waves - the third wave keeps 14 pairs busy and 60 idle.
+    Stream-K is an option (it measured no faster than whole tiles on this GPU), so by default it does not run."""
     M = N = 4608
     K = 4096
     A, B = _operands(M, N, K, 21)
-    set_option("stream_k", 0)
     before = _sk_count(lib)
     whole = sx.gemm(A, B)
-    assert _sk_count(lib) == before
-    set_option("stream_k", -1)
+    assert _sk_count(lib) == before, "stream-K must not run unless the option asks for it"
+    set_option("stream_k", 1)
     launches = sx.launch_count()
     got = sx.gemm(A, B)
     assert sx.launch_count() - launches == 1, "stream-K is one kernel launch"
-    assert _sk_count(lib) == before + 1, "4608 x 4608 x 4096 bf16 should take the stream-K variant by itself"
+    assert _sk_count(lib) == before + 1
     again = sx.gemm(A, B)
     sx.sync_status()
     assert torch.equal(got, again), "stream-K must repeat bit for bit"
@@ -65,10 +65,6 @@ def test_auto_stream_k_on_a_mostly_idle_last_wave(lib, oracle, set_option):
     rows = np.sort(np.random.default_rng(2).choice(M, 48, replace=False))
     ref = _oracle_rows(oracle, A, B, rows, sx.ROW_MAJOR)
     assert rel_frobenius(got[torch.from_numpy(rows).to(DEV)].float().cpu().numpy(), ref) <= 1e-2
-    A2, B2 = _operands(4096, 4096, 4096, 26)
-    before = _sk_count(lib)
-    sx.gemm(A2, B2)
-    assert _sk_count(lib) == before
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
