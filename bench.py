@@ -122,10 +122,16 @@ ELEMENTWISE_WORKLOADS = {
     # the f64 twin (what the reference's Python layer calls for float64 NumPy arrays)
     "f3_fused_axpb_f64_64M": dict(n=64 << 20, n_inputs=1, ops=[(2, 0, 0, 1, 0), (0, 2, 0, 1, 1)], consts=[2.0, 1.0],
                                   reduce_op=255, desc="dst = x * 2.0 + 1.0 (float64)", f64=True),
-    # arrays that start 4 bytes off a 16-byte boundary: the plain-load kernel instead of the bulk-copy ring
+    # arrays that all start 4 bytes off a 16-byte boundary (x[1:] of aligned arrays): the bulk-copy ring from the next
+    # boundary on, the element in front of it by the ring kernel's scalar path
     "f3_fused_axpb_store_unaligned_64M": dict(n=64 << 20, n_inputs=1, ops=[(2, 0, 0, 1, 0), (0, 2, 0, 1, 1)],
                                               consts=[2.0, 1.0], reduce_op=255, desc="dst = x * 2.0 + 1.0, unaligned arrays",
                                               misalign=1),
+    # source 4 bytes and destination 8 bytes off: no common boundary, the plain-load kernel
+    "f3_fused_axpb_store_mixed_offsets_64M": dict(n=64 << 20, n_inputs=1, ops=[(2, 0, 0, 1, 0), (0, 2, 0, 1, 1)],
+                                                  consts=[2.0, 1.0], reduce_op=255,
+                                                  desc="dst = x * 2.0 + 1.0, source and destination misaligned differently",
+                                                  misalign=1, misalign_out=2),
 }
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -370,7 +376,8 @@ def main_elementwise(args):
     tdt = torch.float64 if f64 else torch.float32
     mis = int(w.get("misalign", 0))  # elements by which every array is shifted off its 16-byte boundary
     arrays = [(torch.rand(n + mis, device=dev, generator=g, dtype=tdt) * 2 - 1)[mis:] for _ in range(w["n_inputs"])]
-    out = None if reduce else torch.empty(n + mis, device=dev, dtype=tdt)[mis:]
+    mis_out = int(w.get("misalign_out", mis))
+    out = None if reduce else torch.empty(n + mis_out, device=dev, dtype=tdt)[mis_out:]
 
     # Arguments of the C-ABI call are packed once: a step is then one library call = one kernel launch, with
     # a few microseconds of host work (the kernels run 0.1-0.2 ms, so per-step Python work would show).

@@ -2,8 +2,10 @@
 // rust-engine/src/phase3_jit.rs:449-461,676-685) that TensorMatMul traces with element type F64 call.
 //
 // CUDA-core kernel (the fp64 rate of a B200 is the same on and off the tensor cores): 64 x 64 output tile per CTA,
-// 256 threads, 4 x 4 outputs per thread, operands staged through shared memory in k-slabs of 16 with register
-// prefetch of the next slab. The arithmetic is the reference's cache_tiled_dgemm (rust-engine/src/phase3_jit.rs:
+// 256 threads, 4 x 4 outputs per thread (four consecutive rows, four columns 16 apart: the 16 threads of a half-warp
+// then read 16 consecutive doubles of a B row, one conflict-free shared-memory wavefront, where four consecutive
+// columns per thread put the half-warp on four banks), operands staged through shared memory in k-slabs of 16 with
+// register prefetch of the next slab. The arithmetic is the reference's cache_tiled_dgemm (rust-engine/src/phase3_jit.rs:
 // 578-650) element for element: within each block of KC = 128 consecutive k an accumulator starts at 0 and takes
 // acc = acc + a*b with the product and the sum rounded separately (Rust does not contract them), in increasing k;
 // the block's accumulator is then added to C, blocks in increasing k. Neither the reference's M / N tiling nor this
@@ -23,7 +25,7 @@ __global__ void __launch_bounds__(256) dgemm_kernel(const double* __restrict__ A
   __shared__ double sA[DK][DT + 1];  // [k][m]: column reads by the 4 x 4 micro-tile are conflict free
   __shared__ double sB[DK][DT];      // [k][n]
   const int tid = threadIdx.x;
-  const int tx = tid & 15, ty = tid >> 4;  // micro-tile: rows ty*4.., columns tx*4..
+  const int tx = tid & 15, ty = tid >> 4;  // micro-tile: rows ty*4 + i, columns tx + 16*j
   const int m0 = blockIdx.y * DT, n0 = blockIdx.x * DT;
   // loaders: A slab is 64 rows x 16 k (each thread 4 elements of one row), B slab 16 k x 64 n (4 of one k-row)
   const int a_r = tid >> 2, a_k = (tid & 3) * 4;
@@ -50,17 +52,23 @@ __global__ void __launch_bounds__(256) dgemm_kernel(const double* __restrict__ A
     __syncthreads();
     if (k0 + DK < K) fetch(k0 + DK);
     const int kmax = K - k0 < DK ? K - k0 : DK;  // the chain has exactly K links: padding is never multiplied
-    for (int k = 0; k < kmax; ++k) {
+    auto step = [&](int k) {
       double a[4], b[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         a[i] = sA[k][ty * 4 + i];
-        b[i] = sB[k][tx * 4 + i];
+        b[i] = sB[k][tx + 16 * i];
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) blk[i][j] = __dadd_rn(blk[i][j], __dmul_rn(a[i], b[j]));
+    };
+    if (kmax == DK) {  // a whole slab: unrolled, so the loads of the next k run under the arithmetic of this one
+#pragma unroll
+      for (int k = 0; k < DK; ++k) step(k);
+    } else {
+      for (int k = 0; k < kmax; ++k) step(k);
     }
     if ((k0 + DK) % KC == 0 || k0 + DK >= K) {
 #pragma unroll
@@ -79,7 +87,7 @@ __global__ void __launch_bounds__(256) dgemm_kernel(const double* __restrict__ A
     if (r >= M) continue;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int n = n0 + tx * 4 + j;
+      const int n = n0 + tx + 16 * j;
       if (n < N) C[(long long)r * ldc + n] = acc[i][j];
     }
   }

@@ -138,6 +138,7 @@ struct FeKernelArgs {
   double* result;
   int* status;
   int n_ops, reduce_op, n_inputs, stages;
+  int head;  // ring kernel: elements in front of element 0 (at indices -head .. -1) that belong to the arrays too
   FeOp ops[MAXOPS];
 };
 
@@ -422,11 +423,14 @@ __device__ __forceinline__ void fe_grid_reduce(const FeKernelArgs<T, MAXOPS>& P,
   }
 }
 
-// Elements [first, n) one per thread with plain loads: what is left after the last full chunk.
+// Elements [first, n) one per thread with plain loads: what is left after the last full chunk - and, behind them in
+// the same loop, the P.head elements in front of element 0 (arrays that start a few elements before a 16-byte
+// boundary are handed to the ring kernel from that boundary on).
 template <typename T, int MAXOPS>
 __device__ __forceinline__ void fe_scalar_range(const FeKernelArgs<T, MAXOPS>& P, long long first, long long gtid,
                                                 long long nthreads, bool reduce, T& acc) {
-  for (long long t = first + gtid; t < P.n; t += nthreads) {
+  for (long long i = first + gtid; i < P.n + P.head; i += nthreads) {
+    const long long t = i < P.n ? i : i - P.n - P.head;  // -head .. -1
     GlobalLoader<T, 1> ld;
     ld.in = P.in;
     ld.e[0] = t;
@@ -557,10 +561,11 @@ fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P)
 }
 
 // Plain-load kernel for arrays that are not 16-byte aligned and for programs without inputs.
+constexpr int FE_PLAIN_U = 4;  // independent elements per thread and step (8 doubles the registers and halves the occupancy: the same bytes in flight)
 template <typename T, int MAXOPS>
 __global__ void __launch_bounds__(FE_THREADS)
 fused_elementwise_plain_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P) {
-  constexpr int U = 4;
+  constexpr int U = FE_PLAIN_U;
   const bool reduce = P.reduce_op != FE_REDUCE_NONE;
   const long long nt = (long long)gridDim.x * blockDim.x;
   const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -609,6 +614,7 @@ static void fill_args(FeKernelArgs<T, MAXOPS>& a, const FeProgram& prog, const v
   a.reduce_op = reduce_op;
   a.n_inputs = prog.n_inputs;
   a.stages = 0;
+  a.head = 0;
   memcpy(a.ops, prog.ops, sizeof(FeOp) * (size_t)prog.n_ops);
 }
 
@@ -661,7 +667,7 @@ void describe_fused_elementwise(int n_inputs, long long n, int elem_bytes, int n
 
 template <typename T, int U, int MAXOPS>
 static int launch_ring(const FeProgram& prog, const void* const* inputs, long long n, int reduce_op, void* dst,
-                       double* result, void* reduce_scratch, int* status, int num_sms, cudaStream_t stream) {
+                       double* result, void* reduce_scratch, int* status, int num_sms, cudaStream_t stream, int head) {
   auto kern = fused_elementwise_ring_kernel<T, U, MAXOPS>;
   SX_ENSURE_DYN_SMEM(kern, 160 * 1024);  // the largest ring is 2 stages x 16 inputs x 4 KB + barriers
   const RingGeometry geo = ring_geometry(prog.n_inputs, (int)sizeof(T));
@@ -672,6 +678,7 @@ static int launch_ring(const FeProgram& prog, const void* const* inputs, long lo
   auto args = std::make_unique<FeKernelArgs<T, MAXOPS>>();
   fill_args(*args, prog, inputs, n, reduce_op, dst, result, reduce_scratch, status);
   args->stages = geo.stages;
+  args->head = head;
   const long long nchunks = n / (geo.chunk_bytes / (int)sizeof(T));
   const long long blocks = clamp_blocks(nchunks, (long long)num_sms * per_sm);
   kern<<<(unsigned)blocks, FE_THREADS + 32, geo.smem_bytes, stream>>>(*args);
@@ -689,7 +696,7 @@ static int launch_plain(const FeProgram& prog, const void* const* inputs, long l
     return set_last_error(SX_ERR_DRIVER, "occupancy query failed for the fused elementwise kernel");
   auto args = std::make_unique<FeKernelArgs<T, MAXOPS>>();
   fill_args(*args, prog, inputs, n, reduce_op, dst, result, reduce_scratch, status);
-  const long long blocks = clamp_blocks((n + FE_THREADS * 4 - 1) / (FE_THREADS * 4), (long long)num_sms * per_sm);
+  const long long blocks = clamp_blocks((n + FE_THREADS * FE_PLAIN_U - 1) / (FE_THREADS * FE_PLAIN_U), (long long)num_sms * per_sm);
   kern<<<(unsigned)blocks, FE_THREADS, 0, stream>>>(*args);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_last_error(SX_ERR_EXEC, cudaGetErrorString(e));
@@ -707,10 +714,37 @@ static int launch_typed(const FeProgram& prog, const void* const* inputs, long l
     bits |= reinterpret_cast<uintptr_t>(p);
   }
   if (bits % sizeof(T)) return set_last_error(SX_ERR_INVALID, "arrays must be aligned to the element size");
-  const bool ring = bits % 16 == 0 && prog.n_inputs > 0;
+  bool ring = bits % 16 == 0 && prog.n_inputs > 0;
   const bool small = prog.n_ops <= FE_SMALL_OPS;
+  // Arrays that all start the same distance past a 16-byte boundary (slices of aligned arrays, x[1:]): the ring kernel
+  // takes them from the next boundary on and computes the few elements in front of it with its scalar path.
+  int head = 0;
+  const void* shifted[FE_MAX_INPUTS];
+  FeProgram shifted_prog;
+  if (!ring && prog.n_inputs > 0 && prog.n_inputs <= FE_MAX_INPUTS) {
+    const uintptr_t off = reinterpret_cast<uintptr_t>(inputs[prog.input_map[0]]) % 16;
+    bool same = off != 0 && (reduce || reinterpret_cast<uintptr_t>(dst) % 16 == off);
+    for (int i = 1; same && i < prog.n_inputs; ++i)
+      same = reinterpret_cast<uintptr_t>(inputs[prog.input_map[i]]) % 16 == off;
+    const long long h = (long long)((16 - off) / sizeof(T));
+    if (same && n > h) {
+      head = (int)h;
+      shifted_prog = prog;
+      for (int i = 0; i < prog.n_inputs; ++i) {
+        shifted[i] = static_cast<const T*>(inputs[prog.input_map[i]]) + head;
+        shifted_prog.input_map[i] = i;
+      }
+      ring = true;
+    }
+  }
+  const FeProgram& use_prog = head ? shifted_prog : prog;
+  const void* const* use_in = head ? shifted : inputs;
+  void* use_dst = (head && dst) ? static_cast<void*>(static_cast<T*>(dst) + head) : dst;
+  const long long use_n = n - head;
 #define FE_ARGS prog, inputs, n, reduce_op, dst, result, reduce_scratch, status, num_sms, stream
   if (!ring) return small ? launch_plain<T, FE_SMALL_OPS>(FE_ARGS) : launch_plain<T, FE_MAX_OPS>(FE_ARGS);
+#undef FE_ARGS
+#define FE_ARGS use_prog, use_in, use_n, reduce_op, use_dst, result, reduce_scratch, status, num_sms, stream, head
   switch (ring_geometry(prog.n_inputs, (int)sizeof(T)).u) {
     case 4: return small ? launch_ring<T, 4, FE_SMALL_OPS>(FE_ARGS) : launch_ring<T, 4, FE_MAX_OPS>(FE_ARGS);
     case 2: return small ? launch_ring<T, 2, FE_SMALL_OPS>(FE_ARGS) : launch_ring<T, 2, FE_MAX_OPS>(FE_ARGS);

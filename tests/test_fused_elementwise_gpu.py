@@ -76,6 +76,33 @@ def test_unaligned_arrays_take_the_plain_kernel_bitwise(torch_cuda, oracle, name
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("off", [1, 2, 3])
+@pytest.mark.parametrize("n", [2, CHUNK + 5, 3 * CHUNK + 11])
+def test_equally_misaligned_arrays_take_the_ring_kernel_from_the_next_boundary(torch_cuda, oracle, off, n):
+    """Sources and destination all start `off` floats past a 16-byte boundary (x[off:] of aligned arrays): the ring
+    kernel runs from the next boundary on and its scalar path computes the 4 - off elements in front of it."""
+    import symplex_b200 as sx
+    torch = torch_cuda
+    ops, n_in, consts = EXACT_PROGRAMS["bias_relu"]
+    arrays = [_rng(n, 40 + i) for i in range(n_in)]
+    want = oracle.fused_elementwise(ops, arrays, consts)
+    dev = []
+    for a in arrays:
+        t = torch.empty(a.size + off, device="cuda", dtype=torch.float32)[off:]
+        t.copy_(torch.from_numpy(a))
+        dev.append(t)
+    guard = torch.full((n + off + 8,), -7.0, device="cuda", dtype=torch.float32)
+    out = guard[off:off + n]
+    got = sx.fused_elementwise(ops, dev, consts, out=out)
+    sx.sync_status()
+    assert got.data_ptr() == out.data_ptr()
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    assert bool((guard[:off] == -7.0).all()) and bool((guard[off + n:] == -7.0).all()), "wrote outside dst"
+    # the same arrays reduced: the head elements are part of the sum
+    total = float(sx.fused_elementwise(ops, dev, consts, reduce_op=SUM).item())
+    assert abs(total - float(want.astype(np.float64).sum())) <= 1e-5 * max(1.0, float(np.abs(want).astype(np.float64).sum()))
+
+
 def test_libm_ops_within_a_few_ulp(torch_cuda, oracle):
     n = 4 * CHUNK + 3
     x = _rng(n, 30, 0.05, 6.0)
