@@ -108,6 +108,55 @@ repack_kernel(const InT* __restrict__ in, long long ld_in, long long batch_strid
   }
 }
 
+// Rows of 16-bit elements whose pitch or base is not a multiple of 16 bytes -> rows of `ld_out_vec` 16-byte vectors.
+// One thread per output vector: it loads the one or two aligned 16-byte granules that hold its 16 source bytes and
+// shifts them into place (the byte offset inside the granule is even, 0..14), so global memory sees only aligned
+// 16-byte accesses - three memory instructions per 16 bytes where an element-wise copy needs sixteen. A granule is
+// only touched if at least one byte of it belongs to the row, so nothing outside the operand's 16-byte granules is
+// read. Bytes past the end of a row are written as zero.
+__global__ void __launch_bounds__(256)
+repack_rows16_kernel(const uint8_t* __restrict__ in, long long ld_in_bytes, long long batch_stride_in_bytes,
+                     uint4* __restrict__ out, long long ld_out_vec, int rows, long long row_bytes, int batch) {
+  const long long per_mat = (long long)rows * ld_out_vec;
+  const long long total = per_mat * batch;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(i / per_mat);
+    const long long rm = i - (long long)b * per_mat;
+    const int r = (int)(rm / ld_out_vec);
+    const long long o = (rm - (long long)r * ld_out_vec) * 16;  // byte offset inside the row
+    uint32_t res[4] = {0u, 0u, 0u, 0u};
+    if (o < row_bytes) {
+      const uint8_t* row = in + (long long)b * batch_stride_in_bytes + (long long)r * ld_in_bytes;
+      const uintptr_t addr = reinterpret_cast<uintptr_t>(row + o);
+      const unsigned sh = (unsigned)(addr & 15);
+      const uint4* g = reinterpret_cast<const uint4*>(addr - sh);
+      const uint4 v0 = __ldg(g);
+      uint4 v1 = make_uint4(0u, 0u, 0u, 0u);
+      if (sh != 0 && reinterpret_cast<uintptr_t>(row + row_bytes) > reinterpret_cast<uintptr_t>(g + 1)) v1 = __ldg(g + 1);
+      const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+      const unsigned sw = sh >> 2, bits = (sh & 3) * 8;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (sw == (unsigned)q) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) res[k] = __funnelshift_r(w[q + k], w[q + k + 1], bits);
+        }
+      }
+      const long long valid = row_bytes - o;  // source bytes that belong to this vector
+      if (valid < 16) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const long long left = valid - 4 * k;
+          if (left <= 0) res[k] = 0u;
+          else if (left < 4) res[k] &= (1u << (8 * (int)left)) - 1u;
+        }
+      }
+    }
+    out[i] = make_uint4(res[0], res[1], res[2], res[3]);
+  }
+}
+
 static int grid_for(long long work_items) {
   long long blocks = (work_items + 255) / 256;
   const long long cap = 148 * 16;
@@ -135,6 +184,13 @@ int launch_split_tf32_transpose(const float* in, long long ld_in, long long batc
 
 int launch_repack_16(const void* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
                      int rows, int cols, int batch, cudaStream_t stream) {
+  if (ld_out % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(in) % 2 == 0) {
+    const long long vecs = (long long)rows * (ld_out / 8) * batch;
+    repack_rows16_kernel<<<grid_for(vecs), 256, 0, stream>>>(static_cast<const uint8_t*>(in), ld_in * 2,
+                                                            batch_stride_in * 2, static_cast<uint4*>(out), ld_out / 8,
+                                                            rows, (long long)cols * 2, batch);
+    return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+  }
   const long long items = (long long)rows * ld_out * batch;
   repack_kernel<uint16_t, false><<<grid_for(items), 256, 0, stream>>>(
       static_cast<const uint16_t*>(in), ld_in, batch_stride_in, static_cast<uint16_t*>(out), ld_out, rows, cols,

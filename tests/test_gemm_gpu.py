@@ -260,6 +260,34 @@ def test_bf16_ragged_and_unaligned(lib, oracle, shape, b_layout):
     assert rel_frobenius(C, ref) <= TOL_BF16
 
 
+@pytest.mark.parametrize("offset", [1, 2, 3, 5, 7])
+@pytest.mark.parametrize("shape", [(70, 40, 9), (130, 72, 33), (300, 264, 1001), (64, 128, 520)])
+def test_bf16_operands_at_every_misalignment_equal_the_aligned_product(lib, shape, offset):
+    """A and B start `offset` elements (2 bytes each) past a 16-byte boundary, rows of any pitch, a batch of two: the
+    padded copies the library makes (aligned 16-byte loads shifted into place) must hold exactly the operands' values,
+    so the product equals, bit for bit, the one from aligned, padded operands."""
+    M, N, K = shape
+    g = torch.Generator(device=DEV).manual_seed(M + K + offset)
+    A = torch.randn(2, M, K, device=DEV, generator=g).to(torch.bfloat16)
+    B = torch.randn(2, N, K, device=DEV, generator=g).to(torch.bfloat16)  # stored [N, K]
+    bufA = torch.zeros(A.numel() + 16, device=DEV, dtype=torch.bfloat16)
+    bufB = torch.full((B.numel() + 16,), float("nan"), device=DEV, dtype=torch.bfloat16)  # garbage around B
+    Am = bufA[offset:offset + A.numel()].view(2, M, K)
+    Bm = bufB[offset:offset + B.numel()].view(2, N, K)
+    Am.copy_(A)
+    Bm.copy_(B)
+    assert Am.data_ptr() % 16 == (2 * offset) % 16 and Am.is_contiguous()
+    got = _run(Am, Bm, b_layout=sx.COL_MAJOR, out_dtype=torch.float32)
+    Kp = (K + 7) // 8 * 8  # the same values in rows padded to 16 bytes: no copy is made
+    Ap = torch.zeros(2, M, Kp, device=DEV, dtype=torch.bfloat16)
+    Bp = torch.zeros(2, N, Kp, device=DEV, dtype=torch.bfloat16)
+    Ap[:, :, :K] = A
+    Bp[:, :, :K] = B
+    want = _run(Ap, Bp, b_layout=sx.COL_MAJOR, out_dtype=torch.float32)
+    assert torch.equal(got, want)
+    assert torch.isfinite(got).all()
+
+
 ACTS = [("none", 0), ("relu", 1), ("gelu", 2), ("sigmoid", 3), ("tanh", 4), ("silu", 5)]
 
 
