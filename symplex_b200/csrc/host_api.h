@@ -122,9 +122,6 @@ int launch_split_tf32_transpose(const float* in, long long ld_in, long long batc
 // Copy a 2-byte-element matrix into a buffer whose leading dimension is ld_out (zero padded).
 int launch_repack_16(const void* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
                      int rows, int cols, int batch, cudaStream_t stream);
-// fp32 -> bf16 (round to nearest even), same shape conventions as launch_repack_16.
-int launch_f32_to_bf16(const float* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
-                       int rows, int cols, int batch, cudaStream_t stream);
 
 // Double-precision C = A.B in the reference's cache_tiled_dgemm summation order (dgemm.cu). Leading dimensions in elements.
 int launch_dgemm(const double* A, long long lda, const double* B, long long ldb, double* C, long long ldc, int M, int N,

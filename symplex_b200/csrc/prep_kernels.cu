@@ -2,8 +2,8 @@
 //
 //  * split_tf32: the 3xTF32 scheme represents an fp32 value x as hi + lo with hi = tf32(x) and
 //    lo = tf32(x - hi); the GEMM then accumulates hi*hi + hi*lo + lo*hi in fp32 on the tensor cores.
-//  * repack_16 / f32_to_bf16: bring operands whose leading dimension or base address is not a
-//    multiple of 16 bytes into a TMA-compatible padded buffer.
+//  * repack_16: bring 16-bit operands whose leading dimension or base address is not a multiple of
+//    16 bytes into a TMA-compatible padded buffer.
 #include <cuda_bf16.h>
 
 #include "host_api.h"
@@ -82,9 +82,10 @@ split_tf32_transpose_kernel(const float* __restrict__ in, long long ld_in, long 
   }
 }
 
-template <typename InT, bool kToBf16>
+// Element-wise fallback of the padded copy (an output pitch that is not a multiple of 8 elements; not reached from
+// the library's own planning, which always pads to 8).
 __global__ void __launch_bounds__(256)
-repack_kernel(const InT* __restrict__ in, long long ld_in, long long batch_stride_in, uint16_t* __restrict__ out,
+repack_kernel(const uint16_t* __restrict__ in, long long ld_in, long long batch_stride_in, uint16_t* __restrict__ out,
               long long ld_out, int rows, int cols, int batch) {
   const long long per_mat = (long long)rows * ld_out;
   const long long total = per_mat * batch;
@@ -94,17 +95,7 @@ repack_kernel(const InT* __restrict__ in, long long ld_in, long long batch_strid
     const long long rm = i - (long long)b * per_mat;
     const int r = (int)(rm / ld_out);
     const int c = (int)(rm - (long long)r * ld_out);
-    uint16_t v = 0;
-    if (c < cols) {
-      const InT x = in[(long long)b * batch_stride_in + (long long)r * ld_in + c];
-      if constexpr (kToBf16) {
-        __nv_bfloat16 h = __float2bfloat16_rn(x);
-        v = *reinterpret_cast<uint16_t*>(&h);
-      } else {
-        v = x;
-      }
-    }
-    out[i] = v;
+    out[i] = c < cols ? in[(long long)b * batch_stride_in + (long long)r * ld_in + c] : uint16_t(0);
   }
 }
 
@@ -192,18 +183,9 @@ int launch_repack_16(const void* in, long long ld_in, long long batch_stride_in,
     return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
   }
   const long long items = (long long)rows * ld_out * batch;
-  repack_kernel<uint16_t, false><<<grid_for(items), 256, 0, stream>>>(
+  repack_kernel<<<grid_for(items), 256, 0, stream>>>(
       static_cast<const uint16_t*>(in), ld_in, batch_stride_in, static_cast<uint16_t*>(out), ld_out, rows, cols,
       batch);
-  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
-}
-
-int launch_f32_to_bf16(const float* in, long long ld_in, long long batch_stride_in, void* out, long long ld_out,
-                       int rows, int cols, int batch, cudaStream_t stream) {
-  const long long items = (long long)rows * ld_out * batch;
-  repack_kernel<float, true><<<grid_for(items), 256, 0, stream>>>(in, ld_in, batch_stride_in,
-                                                                   static_cast<uint16_t*>(out), ld_out, rows, cols,
-                                                                   batch);
   return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
 }
 
