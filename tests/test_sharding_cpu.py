@@ -92,9 +92,11 @@ def _worker(rank, world, port, M, N, K, chunks, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("chunks", [1, 2])
-def test_two_rank_gloo_pipeline(chunks):
-    world, M, N, K = 2, 512, 48, 40
+@pytest.mark.parametrize("world,chunks", [(2, 1), (2, 2), (8, 2)])
+def test_gloo_pipeline(world, chunks):
+    """The host side of the row-sharded product (row ownership, chunked all-gather, gathered C) on CPU ranks: two
+    ranks, and eight - the largest world the one-box exchange is built for."""
+    M, N, K = 256 * world, 48, 40
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
