@@ -212,7 +212,8 @@ int symplex_b200_selftest_wait_timeout(const void* A, const void* B, void* C, in
  * the k-blocks of all tiles shared evenly among them instead of whole tiles, wherever the library's own scratch pool
  * serves the call - measured no faster than whole tiles on B200, hence off; "stream_k_launches" counts such launches), "f32_fused" (-1 auto, 0, 1), "f32_split_k" (0 auto,
  * 1, 2, 4), "f32_tile_rows" (0 auto, 128), "group_m" (0 auto), "tma_store" (1, 0), "pipeline_mb" (96),
- * "pipeline" (1, 0), "wait_limit_ms" (2000), "trace" (0, 1: one line per GEMM dispatch on stderr). Only "tile_n"
+ * "pipeline" (1, 0), "wait_limit_ms" (2000), "pdl" (1, 0: the GEMM kernels start their set-up while the kernel before
+ * them in the stream drains, and wait for it before touching memory), "trace" (0, 1: one line per GEMM dispatch on stderr). Only "tile_n"
  * and "trace" can also be preset from the environment (SYMPLEX_B200_TILE, SYMPLEX_B200_TRACE, read once at load);
  * the pipeline depth is a compile-time constant of each kernel. set returns SYMPLEX_ERR_INVALID for an unknown
  * name; get returns INT64_MIN for one. */

@@ -29,6 +29,8 @@ Options& options() {
   return o;
 }
 
+bool pdl_enabled() { return options().pdl.load(std::memory_order_relaxed) != 0; }
+
 static std::atomic<int64_t>* option_by_name(const char* name) {
   if (name == nullptr) return nullptr;
   Options& o = options();
@@ -37,7 +39,7 @@ static std::atomic<int64_t>* option_by_name(const char* name) {
       {"tile_n", &o.tile_n}, {"pair_mode", &o.pair_mode}, {"stream_k", &o.stream_k}, {"f32_fused", &o.f32_fused},
       {"f32_split_k", &o.f32_split_k}, {"f32_tile_rows", &o.f32_tile_rows}, {"group_m", &o.group_m},
       {"tma_store", &o.tma_store}, {"pipeline_mb", &o.pipeline_mb}, {"pipeline", &o.pipeline},
-      {"wait_limit_ms", &o.wait_limit_ms}, {"trace", &o.trace}, {"stream_k_launches", &o.stream_k_launches},
+      {"wait_limit_ms", &o.wait_limit_ms}, {"pdl", &o.pdl}, {"trace", &o.trace}, {"stream_k_launches", &o.stream_k_launches},
   };
   for (const Entry& e : table)
     if (strcmp(e.name, name) == 0) return e.v;

@@ -137,6 +137,8 @@ gemm_f32_fused_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if constexpr (kSplit > 1) cluster_sync_all();  // every CTA's barriers are initialised before a peer arrives on them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  pdl_launch_dependents();  // the next kernel in the stream may set itself up on SMs this grid leaves
+  pdl_wait_prior_grids();   // the kernel before this one has completed: its outputs may be this one's operands
 
   const int per = p.m_tiles * p.n_tiles;
   const int total_tiles = p.batch * per;
@@ -413,19 +415,10 @@ int launch_fused(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParam
   using Cfg = FusedCfgT<kSplit>;
   auto kern = gemm_f32_fused_kernel<OutT, kBmn, kSplit>;
   SX_ENSURE_DYN_SMEM(kern, Cfg::DYN_SMEM);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::DYN_SMEM;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = kSplit;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = kSplit > 1 ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+  return launch_kernel_ex(kern, (unsigned)grid, Cfg::THREADS, Cfg::DYN_SMEM, stream, kSplit, pdl_enabled(), tmA, tmB, p) ==
+                 cudaSuccess
+             ? SX_OK
+             : SX_ERR_EXEC;
 }
 
 template <typename OutT, bool kBmn>

@@ -126,6 +126,8 @@ gemm_f32_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  pdl_launch_dependents();  // the next kernel in the stream may set itself up on SMs this grid leaves
+  pdl_wait_prior_grids();   // the kernel before this one has completed: its outputs may be this one's operands
 
   // A tile = one pair of problems (z0, z0 + 1) x one block of 64 columns. With an odd batch the last pair's
   // second half is loaded as zeros (TMA out-of-range fill) and never stored.
@@ -398,8 +400,10 @@ int launch_small(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorM
                  cudaStream_t stream) {
   auto kern = gemm_f32_small_kernel<OutT, kBmn>;
   SX_ENSURE_DYN_SMEM(kern, SmallCfg::DYN_SMEM);
-  kern<<<grid, SmallCfg::THREADS, SmallCfg::DYN_SMEM, stream>>>(tmA, tmB, tmC, p);
-  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+  return launch_kernel_ex(kern, (unsigned)grid, SmallCfg::THREADS, SmallCfg::DYN_SMEM, stream, 1, pdl_enabled(), tmA, tmB,
+                          tmC, p) == cudaSuccess
+             ? SX_OK
+             : SX_ERR_EXEC;
 }
 
 }  // namespace

@@ -209,6 +209,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  pdl_launch_dependents();  // the next kernel in the stream may set itself up on SMs this grid leaves
+  pdl_wait_prior_grids();   // the kernel before this one has completed: its outputs may be this one's operands
 
   const int total_tiles = p.batch * p.m_tiles * p.n_tiles;
   const int nkb = (p.K + BK - 1) / BK;
@@ -669,19 +671,12 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const DstMaps& d
   using Cfg = PairCfg<kMB, kFwd>;
   auto kern = gemm_pair_kernel<OutT, kBmn, kMB, kFwd, kSK>;
   SX_ENSURE_DYN_SMEM(kern, Cfg::DYN_SMEM);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * pairs, 1, 1);
-  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::DYN_SMEM;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, dst, p) == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+  // Row-sharded launches order themselves with flags in peer memory and are left out of the programmatic overlap.
+  const bool pdl = !kFwd && p.n_dst <= 1 && pdl_enabled();
+  return launch_kernel_ex(kern, 2u * (unsigned)pairs, Cfg::THREADS, Cfg::DYN_SMEM, stream, 2, pdl, tmA, tmB, dst, p) ==
+                 cudaSuccess
+             ? SX_OK
+             : SX_ERR_EXEC;
 }
 
 template <typename OutT, bool kBmn>

@@ -94,6 +94,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  pdl_launch_dependents();  // the next kernel in the stream may set itself up on SMs this grid leaves
+  pdl_wait_prior_grids();   // the kernel before this one has completed: its outputs may be this one's operands
 
   const int per = p.m_tiles * p.n_tiles;
   const int total_tiles = p.batch * per;
@@ -258,8 +260,9 @@ int launch_x3(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& 
   using Cfg = X3Cfg<kBN>;
   auto kern = gemm_tf32x3_kernel<OutT, kBN>;
   SX_ENSURE_DYN_SMEM(kern, Cfg::DYN_SMEM);
-  kern<<<grid, 192, Cfg::DYN_SMEM, stream>>>(tmA, tmB, p);
-  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+  return launch_kernel_ex(kern, (unsigned)grid, 192u, Cfg::DYN_SMEM, stream, 1, pdl_enabled(), tmA, tmB, p) == cudaSuccess
+             ? SX_OK
+             : SX_ERR_EXEC;
 }
 
 }  // namespace

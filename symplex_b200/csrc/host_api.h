@@ -23,6 +23,38 @@
 
 namespace sx {
 
+// One launch path for the tcgen05 kernels: an optional cluster of `cluster_x` CTAs and, with `pdl`, the
+// programmatic-stream-serialization attribute (the kernel may start its set-up while the kernel before it in the
+// stream is draining; it waits for that kernel inside, see pdl_wait_prior_grids in sm100_ptx.cuh).
+template <typename Kern, typename... Args>
+inline cudaError_t launch_kernel_ex(Kern kern, unsigned grid, unsigned block, size_t dyn_smem, cudaStream_t stream,
+                                    unsigned cluster_x, bool pdl, const Args&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = dyn_smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+bool pdl_enabled();  // the "pdl" option (capi.cu)
+
+
 // Status codes returned through the C ABI. They mirror the failure classes of the reference's
 // CudaError enum (rust-engine/src/cuda_backend.rs:35-50); TIMEOUT has no counterpart there.
 enum : int {

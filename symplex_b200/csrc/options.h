@@ -20,6 +20,7 @@ struct Options {
   std::atomic<int64_t> pipeline_mb{96};    // host-buffer GEMMs: MB of A + C per row chunk of the copy/compute pipeline
   std::atomic<int64_t> pipeline{1};        // 0: host-buffer GEMMs never chunk
   std::atomic<int64_t> wait_limit_ms{2000};  // bound of every device-side wait of the bf16 kernels
+  std::atomic<int64_t> pdl{1};             // 1: the tcgen05 GEMM kernels are launched as programmatic dependents of the kernel before them in the stream
   std::atomic<int64_t> trace{0};           // 1: one line per GEMM dispatch on stderr
   std::atomic<int64_t> stream_k_launches{0};  // statistic, not a setting: stream-K launches so far (may be set back to 0)
 };

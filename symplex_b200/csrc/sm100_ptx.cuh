@@ -237,6 +237,15 @@ __device__ __forceinline__ void multimem_st_v4(void* mc, const uint4& v) {
 }
 
 // ---------------------------------------------------------------- TMA
+// Programmatic dependent launch. A kernel launched with the programmatic-stream-serialization attribute may start
+// while the kernel before it in the stream is still running: its CTAs are placed on SMs as that kernel's CTAs leave
+// them and run their set-up (barriers, tensor memory, descriptor prefetch); pdl_wait_prior_grids() then holds every
+// thread until the earlier kernel has completed and its writes are visible, so nothing before it may touch global
+// memory. pdl_launch_dependents() is the earlier kernel's side: once every CTA of a grid has executed it (or left),
+// the next kernel's CTAs may be placed. Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
 }
