@@ -288,6 +288,36 @@ def test_bf16_operands_at_every_misalignment_equal_the_aligned_product(lib, shap
     assert torch.isfinite(got).all()
 
 
+@pytest.mark.parametrize("dtype,n", [(torch.bfloat16, 2048), (torch.bfloat16, 640), (torch.float32, 512),
+                                     (torch.float32, 1536)])
+def test_back_to_back_products_that_feed_each_other(lib, set_option, dtype, n):
+    """Each product's output is the next one's A, launched back to back on one stream with no host synchronisation. The
+    kernels start their set-up while their predecessor drains (programmatic dependent launch); they must not read an
+    operand before the kernel that writes it has completed. The chain is compared, bit for bit, with the same chain
+    run with that overlap switched off and a device synchronisation after every product."""
+    g = torch.Generator(device=DEV).manual_seed(n)
+    X = (torch.randn(n, n, device=DEV, generator=g) / 8).to(dtype)
+    W = (torch.randn(n, n, device=DEV, generator=g) / (n ** 0.5)).to(dtype)  # keeps the chain's magnitude level
+
+    def chain(sync):
+        cur = X
+        for _ in range(8):
+            cur = sx.gemm(cur, W, activation="tanh")
+            if sync:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        return cur
+
+    set_option("pdl", 1)
+    fast = [chain(False) for _ in range(3)]
+    sx.sync_status()
+    set_option("pdl", 0)
+    want = chain(True)
+    for got in fast:
+        assert torch.equal(got, want)
+    assert torch.isfinite(want.float()).all() and float(want.float().abs().max()) > 0
+
+
 ACTS = [("none", 0), ("relu", 1), ("gelu", 2), ("sigmoid", 3), ("tanh", 4), ("silu", 5)]
 
 
