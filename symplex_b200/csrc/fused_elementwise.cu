@@ -472,6 +472,8 @@ fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P)
     fence_mbar_init();
   }
   __syncthreads();
+  pdl_launch_dependents();  // the next kernel in the stream may set itself up on SMs this grid leaves
+  pdl_wait_prior_grids();   // the kernel before this one has completed: its outputs may be this one's inputs
   T acc[W];
 #pragma unroll
   for (int w = 0; w < W; ++w) acc[w] = fe_identity<T>(P.reduce_op);
@@ -681,8 +683,8 @@ static int launch_ring(const FeProgram& prog, const void* const* inputs, long lo
   args->head = head;
   const long long nchunks = n / (geo.chunk_bytes / (int)sizeof(T));
   const long long blocks = clamp_blocks(nchunks, (long long)num_sms * per_sm);
-  kern<<<(unsigned)blocks, FE_THREADS + 32, geo.smem_bytes, stream>>>(*args);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_kernel_ex(kern, (unsigned)blocks, FE_THREADS + 32, geo.smem_bytes, stream, 1, pdl_enabled(),
+                                         *args);
   if (e != cudaSuccess) return set_last_error(SX_ERR_EXEC, cudaGetErrorString(e));
   return SX_OK;
 }
