@@ -484,6 +484,7 @@ fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P)
       int stage = 0;
       uint32_t phase = 0, armed = 0, armed_phase = 0;
       bool ok = true;
+      const uint64_t pol = l2_policy_evict_first();  // inputs are read once: their lines should leave L2 first
       for (long long c = blockIdx.x; c < nchunks; c += gridDim.x) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, &abort_flag)) {
           ok = false;
@@ -494,7 +495,7 @@ fused_elementwise_ring_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P)
         armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
         T* dst = ring + (size_t)stage * ni * CHUNK;
         for (int i = 0; i < ni; ++i)
-          bulk_load_1d(dst + (size_t)i * CHUNK, P.in[i] + c * CHUNK, CHUNK * sizeof(T), &full_bar[stage]);
+          bulk_load_1d_hint(dst + (size_t)i * CHUNK, P.in[i] + c * CHUNK, CHUNK * sizeof(T), &full_bar[stage], pol);
         if (++stage == stages) {
           stage = 0;
           phase ^= 1;
