@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 
 #include "host_api.h"
+#include "sm100_ptx.cuh"
 
 namespace sx {
 
@@ -20,6 +21,8 @@ __device__ __forceinline__ float tf32_round(float x) {
 __global__ void __launch_bounds__(256)
 split_tf32_kernel(const float* __restrict__ in, long long ld_in, long long batch_stride_in, float* __restrict__ out,
                   int rows, int cols, int cols_p, int batch) {
+  pdl_launch_dependents();  // the GEMM that follows may set itself up while this pass drains
+  pdl_wait_prior_grids();   // the source may be the output of the kernel before this one
   const int c4n = cols_p >> 2;
   const long long per_mat = (long long)rows * c4n;
   const long long total = per_mat * batch;
@@ -58,6 +61,8 @@ __global__ void __launch_bounds__(256)
 split_tf32_transpose_kernel(const float* __restrict__ in, long long ld_in, long long batch_stride_in,
                             float* __restrict__ out, int rows, int cols, int rows_p) {
   __shared__ float tile[32][33];
+  pdl_launch_dependents();
+  pdl_wait_prior_grids();
   const int b = blockIdx.z;
   const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
@@ -108,6 +113,8 @@ repack_kernel(const uint16_t* __restrict__ in, long long ld_in, long long batch_
 __global__ void __launch_bounds__(256)
 repack_rows16_kernel(const uint8_t* __restrict__ in, long long ld_in_bytes, long long batch_stride_in_bytes,
                      uint4* __restrict__ out, long long ld_out_vec, int rows, long long row_bytes, int batch) {
+  pdl_launch_dependents();
+  pdl_wait_prior_grids();
   const long long per_mat = (long long)rows * ld_out_vec;
   const long long total = per_mat * batch;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -160,8 +167,10 @@ int launch_split_tf32(const float* in, long long ld_in, long long batch_stride_i
                       int cols_p, int batch, cudaStream_t stream) {
   if (cols_p % 4 != 0 || cols_p < cols) return SX_ERR_INVALID;
   const long long items = (long long)rows * (cols_p / 4) * batch;
-  split_tf32_kernel<<<grid_for(items), 256, 0, stream>>>(in, ld_in, batch_stride_in, out, rows, cols, cols_p, batch);
-  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+  return launch_kernel_ex(split_tf32_kernel, (unsigned)grid_for(items), 256u, 0, stream, 1, pdl_enabled(), in, ld_in,
+                          batch_stride_in, out, rows, cols, cols_p, batch) == cudaSuccess
+             ? SX_OK
+             : SX_ERR_EXEC;
 }
 
 int launch_split_tf32_transpose(const float* in, long long ld_in, long long batch_stride_in, float* out, int rows,
@@ -177,10 +186,11 @@ int launch_repack_16(const void* in, long long ld_in, long long batch_stride_in,
                      int rows, int cols, int batch, cudaStream_t stream) {
   if (ld_out % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 && reinterpret_cast<uintptr_t>(in) % 2 == 0) {
     const long long vecs = (long long)rows * (ld_out / 8) * batch;
-    repack_rows16_kernel<<<grid_for(vecs), 256, 0, stream>>>(static_cast<const uint8_t*>(in), ld_in * 2,
-                                                            batch_stride_in * 2, static_cast<uint4*>(out), ld_out / 8,
-                                                            rows, (long long)cols * 2, batch);
-    return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+    return launch_kernel_ex(repack_rows16_kernel, (unsigned)grid_for(vecs), 256u, 0, stream, 1, pdl_enabled(),
+                            static_cast<const uint8_t*>(in), ld_in * 2, batch_stride_in * 2, static_cast<uint4*>(out),
+                            ld_out / 8, rows, (long long)cols * 2, batch) == cudaSuccess
+               ? SX_OK
+               : SX_ERR_EXEC;
   }
   const long long items = (long long)rows * ld_out * batch;
   repack_kernel<<<grid_for(items), 256, 0, stream>>>(

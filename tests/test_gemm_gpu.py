@@ -299,10 +299,14 @@ def test_back_to_back_products_that_feed_each_other(lib, set_option, dtype, n):
     X = (torch.randn(n, n, device=DEV, generator=g) / 8).to(dtype)
     W = (torch.randn(n, n, device=DEV, generator=g) / (n ** 0.5)).to(dtype)  # keeps the chain's magnitude level
 
+    bias0 = torch.zeros(n, device=DEV)
+
     def chain(sync):
         cur = X
-        for _ in range(8):
-            cur = sx.gemm(cur, W, activation="tanh")
+        for i in range(8):
+            # the previous product is this one's A and its residual (plain loads in the epilogue), and a row of it its bias
+            bias = bias0 if i == 0 else cur[0].float().contiguous()
+            cur = sx.gemm(cur, W, activation="tanh", residual=cur, beta=0.25, bias=bias)
             if sync:
                 torch.cuda.synchronize()
         torch.cuda.synchronize()
