@@ -11,6 +11,7 @@
 // the block's accumulator is then added to C, blocks in increasing k. Neither the reference's M / N tiling nor this
 // kernel's changes that order, so the two agree bit for bit.
 #include "host_api.h"
+#include "sm100_ptx.cuh"
 
 namespace sx {
 
@@ -24,6 +25,8 @@ __global__ void __launch_bounds__(256) dgemm_kernel(const double* __restrict__ A
                                                    long long ldc, int M, int N, int K) {
   __shared__ double sA[DK][DT + 1];  // [k][m]: column reads by the 4 x 4 micro-tile are conflict free
   __shared__ double sB[DK][DT];      // [k][n]
+  pdl_launch_dependents();  // the next kernel in the stream may set itself up while this grid drains
+  pdl_wait_prior_grids();   // the operands may be the output of the kernel before this one
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;  // micro-tile: rows ty*4 + i, columns tx + 16*j
   const int m0 = blockIdx.y * DT, n0 = blockIdx.x * DT;
@@ -99,8 +102,16 @@ int launch_dgemm(const double* A, long long lda, const double* B, long long ldb,
   if (M <= 0 || N <= 0 || K <= 0) return SX_ERR_INVALID;
   const dim3 grid((N + DT - 1) / DT, (M + DT - 1) / DT, 1);
   if (grid.y > 65535) return SX_ERR_INVALID;
-  dgemm_kernel<<<grid, 256, 0, stream>>>(A, lda, B, ldb, C, ldc, M, N, K);
-  return cudaGetLastError() == cudaSuccess ? SX_OK : SX_ERR_EXEC;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, dgemm_kernel, A, lda, B, ldb, C, ldc, M, N, K) == cudaSuccess ? SX_OK : SX_ERR_EXEC;
 }
 
 }  // namespace sx

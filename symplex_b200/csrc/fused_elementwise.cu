@@ -569,6 +569,8 @@ template <typename T, int MAXOPS>
 __global__ void __launch_bounds__(FE_THREADS)
 fused_elementwise_plain_kernel(const __grid_constant__ FeKernelArgs<T, MAXOPS> P) {
   constexpr int U = FE_PLAIN_U;
+  pdl_launch_dependents();
+  pdl_wait_prior_grids();
   const bool reduce = P.reduce_op != FE_REDUCE_NONE;
   const long long nt = (long long)gridDim.x * blockDim.x;
   const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -700,8 +702,7 @@ static int launch_plain(const FeProgram& prog, const void* const* inputs, long l
   auto args = std::make_unique<FeKernelArgs<T, MAXOPS>>();
   fill_args(*args, prog, inputs, n, reduce_op, dst, result, reduce_scratch, status);
   const long long blocks = clamp_blocks((n + FE_THREADS * FE_PLAIN_U - 1) / (FE_THREADS * FE_PLAIN_U), (long long)num_sms * per_sm);
-  kern<<<(unsigned)blocks, FE_THREADS, 0, stream>>>(*args);
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_kernel_ex(kern, (unsigned)blocks, FE_THREADS, 0, stream, 1, pdl_enabled(), *args);
   if (e != cudaSuccess) return set_last_error(SX_ERR_EXEC, cudaGetErrorString(e));
   return SX_OK;
 }
