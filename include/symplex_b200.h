@@ -326,6 +326,14 @@ void symplex_b200_abi_sizes(int32_t out[5]);
  * symplex_kernel_args. Writes the first n entries to out (may be NULL) and returns how many there are. */
 int32_t symplex_b200_abi_sizes_ext(int32_t* out, int32_t n);
 
+/* Stream-K work list of CTA pair `pair` of `pairs` for `tiles` output tiles of `k_blocks` k-blocks each, computed on the
+ * host by the iterator the kernel runs (no GPU needed; for tests and tools). items receives up to cap entries of
+ * {tile, first k-block, end k-block, kind} with kind 0 = whole tile, 1 = partial sums left for the tile's owner,
+ * 2 = owner (holds the tile's last k-block, adds the partial sums of contributors[i] lower-numbered pairs). Returns the
+ * number of items the pair has, or -1 for invalid arguments. */
+int32_t symplex_b200_stream_k_items(int32_t pair, int32_t pairs, int32_t tiles, int32_t k_blocks, int32_t* items,
+                                    int32_t cap, int32_t* contributors);
+
 /* Kernels launched by this library on the calling process since load (all threads). */
 uint64_t symplex_b200_launch_count(void);
 

@@ -151,6 +151,8 @@ SIGNATURES = {
     "symplex_b200_selftest_wait_timeout": (c_int, [c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
     "symplex_b200_set_option": (c_int, [c_char_p, c_int64]),
     "symplex_b200_get_option": (c_int64, [c_char_p]),
+    "symplex_b200_stream_k_items": (c_int32, [c_int32, c_int32, c_int32, c_int32, ctypes.POINTER(c_int32), c_int32,
+                                              ctypes.POINTER(c_int32)]),
     "blas_dgemm": (None, [_F32P, _F32P, _F32P, c_size_t, c_size_t, c_size_t]),
     "cache_tiled_dgemm_thin": (None, [_F32P, _F32P, _F32P, c_size_t, c_size_t, c_size_t]),
     "symplex_b200_dgemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,

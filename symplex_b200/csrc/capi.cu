@@ -1271,6 +1271,16 @@ int symplex_cuda_device_info(symplex_device_info* out) {
 
 uint64_t symplex_b200_launch_count(void) { return g_launches.load(); }
 
+int32_t symplex_b200_stream_k_items(int32_t pair, int32_t pairs, int32_t tiles, int32_t k_blocks, int32_t* items,
+                                    int32_t cap, int32_t* contributors) {
+  if (pairs <= 0 || pair < 0 || pair >= pairs || tiles <= 0 || k_blocks <= 0 || cap < 0) return -1;
+  const int n = stream_k_work_items(pair, pairs, tiles, k_blocks, items, cap);
+  if (contributors != nullptr && items != nullptr)
+    for (int i = 0; i < n && i < cap; ++i)
+      contributors[i] = items[4 * i + 3] == 2 ? stream_k_contributors(pair, pairs, tiles, k_blocks, items[4 * i]) : 0;
+  return n;
+}
+
 int32_t symplex_b200_abi_sizes_ext(int32_t* out, int32_t n) {
   const int32_t sizes[] = {(int32_t)sizeof(symplex_gemm_desc),     (int32_t)sizeof(symplex_device_info),
                            (int32_t)sizeof(symplex_fused_op),      (int32_t)sizeof(symplex_b200_target),

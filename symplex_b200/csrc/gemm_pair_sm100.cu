@@ -98,7 +98,7 @@ enum WorkKind : int { WORK_FULL = 0, WORK_PARTIAL = 1, WORK_OWNER = 2 };
 constexpr int SK_GRAIN = 4;  // range boundaries are multiples of this many k-blocks
 
 // First unit (tile * nkb + k-block) of pair q's range; q == pairs gives the end of the line.
-__device__ __forceinline__ long long sk_start(long long total_units, int pairs, int q) {
+__host__ __device__ __forceinline__ long long sk_start(long long total_units, int pairs, int q) {
   if (q >= pairs) return total_units;
   return (total_units * q / pairs) / SK_GRAIN * SK_GRAIN;
 }
@@ -111,7 +111,7 @@ struct PairWork {
   // stream-K: the range's partial first tile (owner) and partial last tile (contributor)
   int own_t, own_k0, part_t, part_k0, part_k1, stage;
 
-  __device__ PairWork(int pair_id, int num_pairs, int total_tiles, int nkb_) : nkb(nkb_) {
+  __host__ __device__ PairWork(int pair_id, int num_pairs, int total_tiles, int nkb_) : nkb(nkb_) {
     kb0 = 0;
     kb1 = nkb;
     kind = WORK_FULL;
@@ -140,8 +140,8 @@ struct PairWork {
     }
     next();
   }
-  __device__ bool valid() const { return t >= 0; }
-  __device__ void next() {
+  __host__ __device__ bool valid() const { return t >= 0; }
+  __host__ __device__ void next() {
     if constexpr (!kSK) {
       t = next_full < end_full ? next_full : -1;
       next_full += stride;
@@ -806,6 +806,29 @@ int launch_gemm_pair(const TcGemmArgs& a, cudaStream_t stream) {
                 : launch_pair_mb<float, false>(mb, tmA, tmB, dmaps, p, pairs, stream);
 }
 
+
+// The work list of one CTA pair, produced on the host by the iterator the kernel's roles run (for tests): up to `cap`
+// items of {tile, first k-block, end k-block, kind}; returns how many the pair has.
+int stream_k_work_items(int pair, int pairs, int tiles, int nkb, int* out, int cap) {
+  int n = 0;
+  for (PairWork<true> w(pair, pairs, tiles, nkb); w.valid(); w.next(), ++n) {
+    if (out != nullptr && n < cap) {
+      out[4 * n + 0] = w.t;
+      out[4 * n + 1] = w.kb0;
+      out[4 * n + 2] = w.kb1;
+      out[4 * n + 3] = w.kind;
+    }
+  }
+  return n;
+}
+// Pairs whose partial sums the owner of `tile` adds (the count the epilogue computes): pairs below `pair` whose range
+// reaches into the tile.
+int stream_k_contributors(int pair, int pairs, int tiles, int nkb, int tile) {
+  const long long total = (long long)tiles * nkb, tile_u0 = (long long)tile * nkb;
+  int n = 0;
+  for (int q = pair - 1; q >= 0 && sk_start(total, pairs, q + 1) > tile_u0; --q) ++n;
+  return n;
+}
 
 size_t stream_k_workspace_bytes(int num_sms) { return (size_t)(num_sms / 2) * 512 * 256 * sizeof(float); }
 int stream_k_flag_words(int num_sms) { return (num_sms / 2) * 2 * PairCfg<2>::EPI_WARPS; }

@@ -114,6 +114,8 @@ struct TcGemmArgs {
 // Stream-K of the 512 x 256 pair kernel: bytes of partial-sum workspace and flag words for a device with num_sms SMs.
 size_t stream_k_workspace_bytes(int num_sms);
 int stream_k_flag_words(int num_sms);
+int stream_k_work_items(int pair, int pairs, int tiles, int nkb, int* out, int cap);
+int stream_k_contributors(int pair, int pairs, int tiles, int nkb, int tile);
 
 int launch_gemm_tc(const TcGemmArgs& a, cudaStream_t stream);
 int pick_bn(long long M, long long N, int batch, int num_sms, int forced);
