@@ -107,6 +107,16 @@ def test_plan_follows_the_dispatch_rules(lib):
     assert planner.compile_matmul(256, 32768, 512, dtype="bf16").optimal_tile == (256, 256, 64)
     assert planner.compile_matmul(2048, 2048, 2048, dtype="bf16").optimal_tile == (256, 256, 64)   # 1 wave, not 2 of 128x128
     assert planner.compile_matmul(512, 512, 512, dtype="bf16").kernel_name == "gemm_tc_kernel"      # 32 small tiles > 4 pairs
+    # stream-K is an option: off, a badly quantised shape takes whole tiles (here the 256x256 ones: 5 waves beat 3 of the
+    # taller tile); on, every CTA pair of the device is busy on the 512x256 tiles and the plan says so
+    off = planner.compile_matmul(4608, 4608, 4096, dtype="bf16", num_sms=148)
+    assert off.optimal_tile == (256, 256, 64) and off.tiles == 18 * 18
+    with _capi.option("stream_k", 1):
+        on = planner.compile_matmul(4608, 4608, 4096, dtype="bf16", num_sms=148)
+        tiny = planner.compile_matmul(1024, 512, 256, dtype="bf16", num_sms=148)  # 16 k-blocks in all: too short to share
+    assert on.optimal_tile == (512, 256, 64) and on.tiles == 9 * 18 and on.grid_dims[0] == 148
+    assert on.estimated_latency_ns < 1.2 * off.estimated_latency_ns
+    assert tiny.grid_dims[0] < 148
     # fewer SMs -> smaller grid
     assert planner.compile_matmul(8192, 8192, 8192, dtype="bf16", num_sms=64).grid_dims[0] == 64
 
